@@ -1,0 +1,235 @@
+// Shared device helpers: the NF4 decode (bit-exact with the reference's arithmetic), and thin
+// wrappers over the sm_100a PTX this library uses (mbarrier, TMA, tcgen05, proxy fences).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "nf4ll.h"
+
+namespace nf4ll {
+
+// ---------------------------------------------------------------------------------------------
+// Host-side error plumbing (definitions in nf4ll_api.cu)
+// ---------------------------------------------------------------------------------------------
+void set_detail(const char* fmt, ...);
+int cuda_fail(cudaError_t err, const char* what);
+int require_sm100();   // NF4LL_OK or NF4LL_ERR_ARCH for the current device
+
+#define NF4LL_CUDA(expr)                                              \
+  do {                                                                \
+    cudaError_t e__ = (expr);                                         \
+    if (e__ != cudaSuccess) return ::nf4ll::cuda_fail(e__, #expr);    \
+  } while (0)
+
+// ---------------------------------------------------------------------------------------------
+// NF4 decode
+// ---------------------------------------------------------------------------------------------
+// The 16 NF4 levels, fp32 (reference solution/k_nf4.py:29-34).
+#define NF4LL_LEVELS                                                                          \
+  -1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,                   \
+      -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,              \
+      0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f, \
+      0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f
+
+// absmax of one quantisation block: code2[q] * scale2 + offset2, the product and the sum rounded
+// separately (reference solution/k_nf4.py:19-21, 47-49; its launcher disables FMA fusion, 180).
+__device__ __forceinline__ float block_absmax(float code, float scale2, float offset2) {
+  return __fadd_rn(__fmul_rn(code, scale2), offset2);
+}
+
+// The 16 possible fp16 values of one quantisation block, fp16(NF4[c] * absmax) for c = 0..15, held
+// as eight byte-plane registers so that four 4-bit codes can be looked up at once with byte
+// permutes: lo[j] has the low bytes of entries 4j..4j+3, hi[j] their high bytes.
+struct BlockTable {
+  uint32_t lo[4];
+  uint32_t hi[4];
+};
+
+__device__ __forceinline__ uint32_t pack_half2_rn(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);   // a -> low half, b -> high half, each round-to-nearest-even
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__device__ __forceinline__ BlockTable make_block_table(float absmax) {
+  constexpr float lv[16] = {NF4LL_LEVELS};
+  BlockTable t;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    // fp32 product rounded once, then rounded to fp16 (reference solution/k_nf4.py:53-54)
+    uint32_t p0 = pack_half2_rn(__fmul_rn(lv[4 * j + 0], absmax), __fmul_rn(lv[4 * j + 1], absmax));
+    uint32_t p1 = pack_half2_rn(__fmul_rn(lv[4 * j + 2], absmax), __fmul_rn(lv[4 * j + 3], absmax));
+    t.lo[j] = __byte_perm(p0, p1, 0x6420);
+    t.hi[j] = __byte_perm(p0, p1, 0x7531);
+  }
+  return t;
+}
+
+// Decode one 32-bit word of packed codes (bytes b0..b3 = elements 0..7, the even element of each
+// byte in its high nibble) into 8 fp16 values, returned as four half2 registers in element order.
+__device__ __forceinline__ uint4 decode_word(const BlockTable& t, uint32_t w) {
+  const uint32_t sel = w & 0x77777777u;                                // low 3 bits of every code
+  const uint32_t pick = ((w >> 1) & 0x44444444u) | 0x32103210u;        // byte i from the upper table if bit 3
+  uint4 out;
+  {
+    const uint32_t la = __byte_perm(t.lo[0], t.lo[1], sel), lb = __byte_perm(t.lo[2], t.lo[3], sel);
+    const uint32_t ha = __byte_perm(t.hi[0], t.hi[1], sel), hb = __byte_perm(t.hi[2], t.hi[3], sel);
+    const uint32_t lo = __byte_perm(la, lb, pick), hi = __byte_perm(ha, hb, pick);
+    // nibble order in the low 16 bits: e1, e0, e3, e2 -> (e0, e1) and (e2, e3)
+    out.x = __byte_perm(lo, hi, 0x4051);
+    out.y = __byte_perm(lo, hi, 0x6273);
+  }
+  {
+    const uint32_t sel2 = sel >> 16, pick2 = pick >> 16;
+    const uint32_t la = __byte_perm(t.lo[0], t.lo[1], sel2), lb = __byte_perm(t.lo[2], t.lo[3], sel2);
+    const uint32_t ha = __byte_perm(t.hi[0], t.hi[1], sel2), hb = __byte_perm(t.hi[2], t.hi[3], sel2);
+    const uint32_t lo = __byte_perm(la, lb, pick2), hi = __byte_perm(ha, hb, pick2);
+    out.z = __byte_perm(lo, hi, 0x4051);
+    out.w = __byte_perm(lo, hi, 0x6273);
+  }
+  return out;
+}
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Every wait on an mbarrier is bounded: after kSpinLimit failed polls (each poll itself suspends
+// for a hardware-chosen interval) the waiter gives up, and the kernel reports it through the
+// status word instead of hanging the GPU. `abort_flag` (shared memory) makes all other waiters of
+// the CTA give up quickly too.
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 63u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
+// --- tensor memory -----------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {   // whole warp
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {                               // whole warp
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {    // whole warp
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// Arrive on an mbarrier once every tcgen05 operation this thread issued so far has completed.
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] . B[smem], fp16 inputs, fp32 accumulate; one thread issues.
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// 32 lanes x 32 consecutive fp32 columns: thread t of the warp gets lane (base lane + t).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+        "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+        "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// --- descriptors -------------------------------------------------------------------------------
+// Shared-memory matrix descriptor of tcgen05.mma: start address, leading and stride byte offsets
+// (all in 16-byte units), descriptor version 1, swizzle mode in bits 61-63.
+constexpr uint64_t kSwizzleNone = 0, kSwizzle128B = 2;
+
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   uint64_t swizzle) {
+  return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(lbo_bytes >> 4) << 16) |
+         (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46) | (swizzle << 61);
+}
+
+// Instruction descriptor for kind::f16 with fp16 A and B and an fp32 accumulator.
+// a_mn / b_mn: 0 = the operand is K-major in shared memory, 1 = MN-major.
+__host__ __device__ constexpr uint32_t make_idesc_f16(int m, int n, int a_mn, int b_mn) {
+  return (1u << 4) | (static_cast<uint32_t>(a_mn) << 15) | (static_cast<uint32_t>(b_mn) << 16) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+}  // namespace nf4ll

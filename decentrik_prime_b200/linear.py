@@ -1,0 +1,226 @@
+"""The NF4 + LoRA linear as Python calls: raw forward / backward_dx / lora_grads for a hand-written
+backward (the reference's model is one autograd node with its own backward,
+solution/fast_qwen.py:1527-1543) and `nf4_lora_linear`, a torch.autograd.Function for ordinary
+modules. All compute happens in libnf4ll.so (include/nf4ll.h); PyTorch only owns the memory and
+the streams. Tensors must be CUDA tensors: nothing here runs on the CPU.
+
+Call-site mapping to the reference (solution/fast_qwen.py):
+  forward      <- _ws_use + torch.mm/addmm on the fp16 workspace (947, 1037, 1080-1098, 1112) and the
+                  LoRA GEMMs + add (943-946; k_rope.py:39-45, 56-58)
+  backward_dx  <- torch.mm(dy, W) (1310, 1320-1327, 1350, 1364), `daq`/`lqx` (1370-1377) and the
+                  masked add in k_norm.py:64-71
+  lora_grads   <- d_bq / d_aq / d_bv / d_av (1369-1374)
+"""
+
+import ctypes
+import threading
+
+import torch
+
+from . import _lib
+from .k_nf4 import PackedLayer
+
+RANK = 16
+
+
+class Nf4Weight:
+    """One NF4 weight W[N, K] on the GPU: views into a PackedLayer's sections plus the shared
+    second-level code table."""
+
+    def __init__(self, packed, qabs, scale2, offset2, code2, rows, cols):
+        for t in (packed, qabs, scale2, offset2, code2):
+            if not t.is_cuda:
+                raise ValueError("NF4 weights must live on the GPU")
+        if code2.dtype != torch.float32 or code2.numel() != 256:
+            raise ValueError("code2 must be 256 fp32 entries")
+        self.packed, self.qabs, self.scale2, self.offset2, self.code2 = packed, qabs, scale2, offset2, code2
+        self.N, self.K = int(rows), int(cols)
+        self.device = packed.device
+        self._c = _lib.Nf4Mat(packed.data_ptr(), qabs.data_ptr(), scale2.data_ptr(), offset2.data_ptr(),
+                              code2.data_ptr(), self.N, self.K)
+
+    @classmethod
+    def from_layer(cls, layer: PackedLayer, name, code2):
+        return cls(*layer.weight(name)[:4], code2, *layer.weight(name)[4:])
+
+    @property
+    def nbytes(self):
+        """Algorithmic bytes of the weight stream: nibbles + absmax codes + scale2 + offset2."""
+        n = self.N * self.K
+        return n // 2 + n // 64 + 2 * 4 * (n // 16384)
+
+
+class _DeviceState(threading.local):
+    def __init__(self):
+        self.ws = {}
+        self.status = {}
+
+
+_state = _DeviceState()
+
+
+def _workspace(device, nbytes):
+    """Per-thread, per-device scratch that grows on demand (the library never allocates). Calls on
+    different streams of the same thread must not overlap while sharing it; pass `workspace=` to
+    forward / backward_dx to use separate buffers."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _state.ws.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _state.ws[key] = ws
+    return ws
+
+
+def status_word(device):
+    """The device status word kernels write when a bounded wait expires (zero = healthy)."""
+    st = _state.status.get(device.index)
+    if st is None:
+        st = torch.zeros(1, dtype=torch.int32, device=device)
+        _state.status[device.index] = st
+    return st
+
+
+def check_status(device=None):
+    """Synchronise the current stream and raise if any kernel reported an expired wait."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    st = status_word(device)
+    _lib.check(_lib.lib().nf4ll_read_status(st.data_ptr(), _lib.current_stream(device)))
+
+
+def _lora_struct(lora, mask, keep_scale):
+    if lora is None:
+        return None, None
+    A16, B16, scale = lora
+    if A16.dtype != torch.float16 or B16.dtype != torch.float16:
+        raise ValueError("LoRA shadows must be fp16")
+    if not (A16.is_contiguous() and B16.is_contiguous()):
+        raise ValueError("LoRA A/B must be contiguous")
+    if mask is not None:
+        if mask.dtype not in (torch.uint8, torch.bool) or mask.stride(-1) != 1:
+            raise ValueError("mask must be uint8/bool with unit inner stride")
+    s = _lib.LoraArgs(A16.data_ptr(), B16.data_ptr(), int(A16.shape[0]), float(scale),
+                      0 if mask is None else mask.data_ptr(), 0 if mask is None else mask.stride(0),
+                      float(keep_scale))
+    return s, ctypes.byref(s)
+
+
+def _check_act(t, cols, what):
+    if t.dtype != torch.float16 or t.dim() != 2 or t.shape[1] != cols or t.stride(1) != 1 or not t.is_cuda:
+        raise ValueError(f"{what} must be a CUDA fp16 matrix [M, {cols}] with unit inner stride")
+
+
+def forward(w: Nf4Weight, x, bias=None, lora=None, mask=None, keep_scale=1.0, out=None, want_t=False,
+            workspace=None):
+    """y = x . W^T (+ bias) + scale * (drop(x) . A^T) . B^T. `lora` = (A16 [16,K], B16 [N,16], scale).
+    Returns (y, t) with t = drop(x) . A^T in fp32 [M,16] when want_t, else None."""
+    _check_act(x, w.K, "x")
+    M = x.shape[0]
+    y = torch.empty(M, w.N, dtype=torch.float16, device=x.device) if out is None else out
+    _check_act(y, w.N, "out")
+    if mask is not None and lora is None:
+        raise ValueError("a dropout mask without a LoRA branch has no meaning")
+    keep, ref = _lora_struct(lora, mask, keep_scale)
+    t = torch.empty(M, RANK, dtype=torch.float32, device=x.device) if (want_t and lora is not None) else None
+    h = _lib.lib()
+    need = h.nf4ll_workspace_bytes(M, w.N, w.K, RANK if lora is not None else 0)
+    ws = _workspace(x.device, need) if workspace is None else workspace
+    _lib.check(h.nf4ll_forward(ctypes.byref(w._c), x.data_ptr(), x.stride(0),
+                               None if bias is None else bias.data_ptr(), ref,
+                               None if t is None else t.data_ptr(), M, y.data_ptr(), y.stride(0),
+                               ws.data_ptr(), ws.numel(), status_word(x.device).data_ptr(),
+                               _lib.current_stream(x.device)))
+    del keep
+    return y, t
+
+
+def backward_dx(w: Nf4Weight, dy, lora=None, mask=None, keep_scale=1.0, out=None, accumulate=False,
+                want_u=False, workspace=None):
+    """dx (+)= dy . W + keep_scale * mask (.) ((scale * dy . B) . A). Returns (dx, u) with
+    u = scale * dy . B in fp32 [M,16] when want_u, else None."""
+    _check_act(dy, w.N, "dy")
+    M = dy.shape[0]
+    if out is None:
+        if accumulate:
+            raise ValueError("accumulate needs an existing dx")
+        out = torch.empty(M, w.K, dtype=torch.float16, device=dy.device)
+    _check_act(out, w.K, "dx")
+    keep, ref = _lora_struct(lora, mask, keep_scale)
+    u = torch.empty(M, RANK, dtype=torch.float32, device=dy.device) if (want_u and lora is not None) else None
+    h = _lib.lib()
+    need = h.nf4ll_workspace_bytes(M, w.N, w.K, RANK if lora is not None else 0)
+    ws = _workspace(dy.device, need) if workspace is None else workspace
+    _lib.check(h.nf4ll_backward_dx(ctypes.byref(w._c), dy.data_ptr(), dy.stride(0), ref,
+                                   None if u is None else u.data_ptr(), M, out.data_ptr(), out.stride(0),
+                                   1 if accumulate else 0, ws.data_ptr(), ws.numel(),
+                                   status_word(dy.device).data_ptr(), _lib.current_stream(dy.device)))
+    del keep
+    return out, u
+
+
+def lora_grads(dy, x, t, u, scale, mask=None, keep_scale=1.0, dA=None, dB=None, accumulate=False):
+    """dA[16,K] (+)= u^T . drop(x), dB[N,16] (+)= scale * dy^T . t, both fp32. dA / dB may be views
+    into a flat gradient bucket; missing ones are allocated (zero-initialised by the call)."""
+    M, K = x.shape
+    N = dy.shape[1]
+    _check_act(x, K, "x")
+    _check_act(dy, N, "dy")
+    if dA is None:
+        dA = torch.empty(RANK, K, dtype=torch.float32, device=x.device)
+        accumulate_a = False
+    else:
+        accumulate_a = accumulate
+    if dB is None:
+        dB = torch.empty(N, RANK, dtype=torch.float32, device=x.device)
+        accumulate_b = False
+    else:
+        accumulate_b = accumulate
+    for g in (dA, dB):
+        if g.dtype != torch.float32 or not g.is_contiguous():
+            raise ValueError("dA/dB must be contiguous fp32")
+    h = _lib.lib()
+    stream = _lib.current_stream(x.device)
+    args = (dy.data_ptr(), dy.stride(0), x.data_ptr(), x.stride(0),
+            None if mask is None else mask.data_ptr(), 0 if mask is None else mask.stride(0),
+            float(keep_scale), t.data_ptr(), u.data_ptr(), float(scale), RANK, M, N, K)
+    if accumulate_a == accumulate_b:
+        _lib.check(h.nf4ll_lora_grads(*args, dA.data_ptr(), dB.data_ptr(), int(accumulate_a), stream))
+    else:
+        _lib.check(h.nf4ll_lora_grads(*args, dA.data_ptr(), None, int(accumulate_a), stream))
+        _lib.check(h.nf4ll_lora_grads(*args, None, dB.data_ptr(), int(accumulate_b), stream))
+    return dA, dB
+
+
+class _Nf4LoraLinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, A, B, w, bias, scale, mask, keep_scale):
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        lora = None
+        if A is not None:
+            lora = (A.detach().half().contiguous(), B.detach().half().contiguous(), scale)
+        m2 = None if mask is None else mask.reshape(-1, mask.shape[-1])
+        y, t = forward(w, x2, bias=bias, lora=lora, mask=m2, keep_scale=keep_scale, want_t=lora is not None)
+        ctx.w, ctx.lora, ctx.mask, ctx.keep_scale, ctx.lead = w, lora, m2, keep_scale, lead
+        ctx.save_for_backward(x2, t)
+        ctx.need_x = x.requires_grad
+        return y.reshape(*lead, w.N)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, t = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.stride(1) != 1:
+            dy2 = dy2.contiguous()
+        dx, u = backward_dx(ctx.w, dy2, lora=ctx.lora, mask=ctx.mask, keep_scale=ctx.keep_scale,
+                            want_u=ctx.lora is not None)
+        dA = dB = None
+        if ctx.lora is not None:
+            dA, dB = lora_grads(dy2, x2, t, u, ctx.lora[2], mask=ctx.mask, keep_scale=ctx.keep_scale)
+        return dx.reshape(*ctx.lead, ctx.w.K), dA, dB, None, None, None, None, None
+
+
+def nf4_lora_linear(x, w: Nf4Weight, bias=None, lora=None, mask=None, keep_scale=1.0):
+    """Differentiable y = NF4Linear(x) + LoRA(x). `lora` = (A fp32 [16,K], B fp32 [N,16], scale) with
+    A and B ordinary parameters: they receive fp32 gradients; W is frozen (no dW)."""
+    A, B, scale = (None, None, 1.0) if lora is None else lora
+    return _Nf4LoraLinearFn.apply(x, A, B, w, bias, scale, mask, keep_scale)

@@ -1,0 +1,145 @@
+/* nf4ll: NF4-quantised frozen linear layer with a fused LoRA branch, for NVIDIA B200 (sm_100a).
+ *
+ * C ABI of libnf4ll.so. Every pointer is a DEVICE pointer unless a comment says otherwise; the
+ * caller owns every buffer. The library allocates nothing, keeps no pointer after a call returns
+ * and has no global mutable state besides a thread-local error-detail string, so it may be called
+ * from several host threads and streams at once. Calls only enqueue work on `stream`
+ * (a cudaStream_t passed as void*); nothing synchronises unless a comment says so.
+ *
+ * Return value: 0, or a negative nf4ll_status code. Codes -10..-19 are caller mistakes (what the
+ * reference reports as ValueError), the others are device or driver failures.
+ *
+ * The weight format is the reference's (solution/k_nf4.py:16-21, 64-95): for W[N,K] row-major,
+ * element e = n*K + k sits in byte e/2 (even element in the HIGH nibble) and dequantises to
+ *   fp16( NF4[nibble] * absmax[e/64] ),  absmax[b] = code2[qabs[b]] * scale2[b/256] + offset2[b/256]
+ * with the product and the sum rounded separately in fp32 and the final product rounded to
+ * nearest-even fp16.
+ */
+#ifndef NF4LL_H_
+#define NF4LL_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NF4LL_VERSION 1
+
+enum nf4ll_status {
+  NF4LL_OK = 0,
+  NF4LL_ERR_NULL = -10,        /* a required pointer is NULL */
+  NF4LL_ERR_SHAPE = -11,       /* a size is not supported (see each call) */
+  NF4LL_ERR_ALIGN = -12,       /* a pointer or leading dimension breaks an alignment rule */
+  NF4LL_ERR_RANK = -13,        /* LoRA rank other than 16 */
+  NF4LL_ERR_WORKSPACE = -14,   /* workspace missing or smaller than nf4ll_workspace_bytes() */
+  NF4LL_ERR_ARCH = -20,        /* current device is not compute capability 10.x */
+  NF4LL_ERR_CUDA = -21,        /* a CUDA runtime / driver call failed (detail string has it) */
+  NF4LL_ERR_DEVICE_WAIT = -22  /* a bounded wait inside a kernel ran out (from nf4ll_read_status) */
+};
+
+/* One NF4 weight W[N,K]: sub-views of a PackedLayer's four sections (reference
+ * solution/k_nf4.py:64-95, PackedLayer / section_views) plus the 256-entry second-level code
+ * table, which the reference passes to every launcher (solution/k_nf4.py:176-205, `code2`).
+ * nib must be 16-byte aligned; N*K must be a multiple of 16384 and K a multiple of 64. */
+typedef struct nf4ll_mat {
+  const uint8_t* nib;     /* N*K/2 bytes  */
+  const uint8_t* qabs;    /* N*K/64 bytes */
+  const float* scale2;    /* N*K/16384    */
+  const float* offset2;   /* N*K/16384    */
+  const float* code2;     /* 256          */
+  int64_t N, K;
+} nf4ll_mat;
+
+/* The LoRA branch of one linear: fp16 shadows of lora_A [r,K] and lora_B [N,r] (reference
+ * solution/fast_qwen.py:452, 686-692), scale = alpha/r (fast_qwen.py:93, 225), and the dropout
+ * keep-mask of the LoRA input (uint8 [M,K], non-zero = keep; reference solution/k_norm.py:10-11,
+ * 49-53) with keep_scale = 1/float32(1-p) (fast_qwen.py:370). mask may be NULL (no dropout). */
+typedef struct nf4ll_lora {
+  const void* A;          /* __half [r,K] row-major */
+  const void* B;          /* __half [N,r] row-major */
+  int32_t r;              /* must be 16 */
+  float scale;
+  const uint8_t* mask;    /* [M, ld_mask] or NULL */
+  int64_t ld_mask;
+  float keep_scale;
+} nf4ll_lora;
+
+int nf4ll_version(void);
+
+/* Static description of a status code. */
+const char* nf4ll_error_string(int code);
+
+/* What exactly failed in the calling thread's last failing call ("" if nothing). Thread-local. */
+const char* nf4ll_last_error_detail(void);
+
+/* Standalone dequantisation of n_qblocks blocks of 64 weights into fp16.
+ * Replaces the reference's nf4_layer_dequant_kernel and its launcher dequant_tensors
+ * (solution/k_nf4.py:40-57, 176-181); the NF4 level table is a compile-time constant here.
+ * nib and out must be 16-byte aligned. scale2/offset2 are indexed from the first block given, so a
+ * sub-range must start on a multiple of 256 blocks (the reference's dequant_range guarantees 1024). */
+int nf4ll_dequant(const uint8_t* nib, const uint8_t* qabs, const float* scale2, const float* offset2,
+                  const float* code2, int64_t n_qblocks, void* out_f16, void* stream);
+
+/* Bytes of scratch that nf4ll_forward / nf4ll_backward_dx need for M rows against W[N,K] with LoRA
+ * rank r (0 = no LoRA). The scratch holds the fp16 rank-r operand of the fused LoRA step, split-K
+ * partial sums and tile counters. Always a multiple of 256; the workspace must be 256-byte aligned. */
+int64_t nf4ll_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t r);
+
+/* Forward:  y[M,N] = x[M,K] . W^T (+ bias) + scale * (drop(x) . A^T) . B^T,  drop(x) = fp16(x * mask * keep_scale)
+ * in ONE pass over the NF4 bytes: tiles of W are dequantised into shared memory and fed to
+ * tcgen05 MMAs (fp32 accumulation in tensor memory); bias and the LoRA term are added to the fp32
+ * accumulator before the single rounding to fp16.
+ * Replaces, per projection, the reference's dequant into the fp16 workspace + cuBLAS GEMM + LoRA
+ * GEMMs + LoRA add: solution/fast_qwen.py:716-750 (_ws_load/_ws_use), 943-947, 1037, 1080-1098,
+ * 1112 and solution/k_rope.py:39-45, 56-58.
+ * x [M,ldx] fp16, y [M,ldy] fp16, bias fp16 [N] or NULL, lora NULL = no LoRA branch.
+ * t_out: optional fp32 [M,16] = drop(x) . A^T (unscaled), kept for nf4ll_lora_grads.
+ * ldx, ldy multiples of 8; x, y 16-byte aligned. status: optional device int32, set non-zero if a
+ * bounded wait in the kernel expires (never reset by the library). */
+int nf4ll_forward(const nf4ll_mat* W, const void* x, int64_t ldx, const void* bias,
+                  const nf4ll_lora* lora, void* t_out, int64_t M, void* y, int64_t ldy,
+                  void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
+
+/* Backward-dX:  dx[M,K] (+)= dy[M,N] . W + keep_scale * mask (.) ((scale * dy . B) . A)
+ * reading the same NF4 bytes (the contraction runs over N; no fp16 W and no W^T is materialised).
+ * Replaces solution/fast_qwen.py:1310, 1320-1327, 1333-1338, 1350, 1364 (cuBLAS NN GEMMs on the
+ * workspace), 1370/1373 (`daq`, `dav`), 1376-1377 (`lqx`, `lvx`) and the masked add in
+ * solution/k_norm.py:64-71. accumulate != 0 adds to the existing dx (gate + up, q + k + v).
+ * u_out: optional fp32 [M,16] = scale * dy . B, kept for nf4ll_lora_grads. */
+int nf4ll_backward_dx(const nf4ll_mat* W, const void* dy, int64_t lddy, const nf4ll_lora* lora,
+                      void* u_out, int64_t M, void* dx, int64_t lddx, int32_t accumulate,
+                      void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
+
+/* Rank-r projection on its own:  t32[M,r] = drop(x)[M,K] . A^T  and  t16 = fp16(scale * t32).
+ * a_kmajor = 1: A is [r,K] row-major (lora_A);  0: A is [K,r] row-major (lora_B, for u = dy . B),
+ * and then t32 carries the scale too (u = scale * dy . B, as the reference's `daq`).
+ * Replaces solution/fast_qwen.py:943-944 and 1370/1373. Either output may be NULL.
+ * mask, when given, must be 16-byte aligned with ld_mask a multiple of 16. */
+int nf4ll_lora_down(const void* x, int64_t ldx, const uint8_t* mask, int64_t ld_mask,
+                    float keep_scale, const void* A, int32_t a_kmajor, float scale, int32_t r,
+                    int64_t M, int64_t K, void* t32, void* t16, void* stream);
+
+/* LoRA gradients, fp32:  dA[r,K] (+)= u^T . drop(x),   dB[N,r] (+)= scale * dy^T . t
+ * with t, u the fp32 [M,r] outputs of nf4ll_forward / nf4ll_backward_dx. fp32 t/u and fp32
+ * accumulation keep dA/dB within 2e-2 of an fp32 reference, which the reference's fp16 GEMM outputs
+ * (solution/fast_qwen.py:1369-1374) do not. dA, dB may point into a flat all-reduce bucket.
+ * Either of dA/dB may be NULL to skip it. */
+int nf4ll_lora_grads(const void* dy, int64_t lddy, const void* x, int64_t ldx, const uint8_t* mask,
+                     int64_t ld_mask, float keep_scale, const void* t32, const void* u32,
+                     float scale, int32_t r, int64_t M, int64_t N, int64_t K,
+                     void* dA, void* dB, int32_t accumulate, void* stream);
+
+/* Synchronise `stream`, copy the device status word to the host and return NF4LL_OK or
+ * NF4LL_ERR_DEVICE_WAIT (detail string carries the raw word). */
+int nf4ll_read_status(const int32_t* status, void* stream);
+
+/* Testing and tuning hook; no counterpart in the reference. Forces the tile shape (bm_tiles 1|2 =
+ * 128|256 rows, bn 128|256 columns) and the split count of the contraction for the calling
+ * thread's next nf4ll_forward / nf4ll_backward_dx calls; zeros restore the built-in heuristic. */
+void nf4ll_tune_override(int32_t bm_tiles, int32_t bn, int32_t splits);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NF4LL_H_ */
