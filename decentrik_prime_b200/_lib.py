@@ -90,6 +90,7 @@ SIGNATURES = {
     "nf4ll_lora_grads": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _f32, _vp, _vp, _f32, _i32, _i64, _i64, _i64,
                                 _vp, _vp, _i32, _vp]),
     "nf4ll_tune_override": (None, [_i32, _i32, _i32]),
+    "nf4ll_kernel_events": (None, [_vp, _vp]),
     "nf4ll_read_status": (_i32, [_vp, _vp]),
 }
 

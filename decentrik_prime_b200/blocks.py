@@ -1,0 +1,167 @@
+"""Projections and blocks built from the fused NF4 + LoRA linear, with a hand-written backward in
+the style of the reference's layer loop (solution/fast_qwen.py:1017-1123 forward, 1232-1384
+backward): activations are saved explicitly, dX flows through `backward_dx`, and the LoRA
+gradients land, in fp32, in views of one flat bucket that a data-parallel run all-reduces once per
+step (the reference returns them as a flat list, fast_qwen.py:1383, 1543).
+"""
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+from . import k_nf4, linear, quantize
+
+
+class GradBucket:
+    """One flat fp32 buffer for every LoRA gradient of a model; projections own views of it."""
+
+    def __init__(self, numel, device):
+        self.flat = torch.zeros(numel, dtype=torch.float32, device=device)
+        self._at = 0
+
+    def take(self, *shape):
+        n = math.prod(shape)
+        view = self.flat[self._at:self._at + n].view(*shape)
+        self._at += n
+        return view
+
+    def zero_(self):
+        self.flat.zero_()
+
+    def all_reduce(self, group=None):
+        """Sum over data-parallel ranks: the only exchange step of the path."""
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(self.flat, group=group)
+        return self.flat
+
+
+def lora_grad_numel(n_out, n_in, rank=linear.RANK):
+    return rank * n_in + n_out * rank
+
+
+class Projection:
+    """One q/k/v/o/gate/up/down projection: frozen NF4 weight, optional fp16 bias, optional LoRA
+    (fp32 master A [16,K], B [N,16] with fp16 shadows refreshed by `refresh16`, as the reference's
+    `_refresh_lora16`, solution/fast_qwen.py:686-692)."""
+
+    def __init__(self, weight: linear.Nf4Weight, bias=None, lora=False, alpha=32.0, bucket=None, seed=0,
+                 b_std=0.01):
+        self.w, self.bias = weight, bias
+        self.has_lora = bool(lora)
+        self.scale = alpha / linear.RANK
+        dev = weight.device
+        if self.has_lora:
+            gen = torch.Generator().manual_seed(seed)
+            bound = 1.0 / math.sqrt(weight.K)          # kaiming_uniform(a=sqrt(5)), PEFT's lora_A init
+            self.A = ((torch.rand(linear.RANK, weight.K, generator=gen) * 2 - 1) * bound).to(dev)
+            self.B = (torch.randn(weight.N, linear.RANK, generator=gen) * b_std).to(dev)
+            self.A16 = torch.empty_like(self.A, dtype=torch.float16)
+            self.B16 = torch.empty_like(self.B, dtype=torch.float16)
+            self.refresh16()
+            if bucket is not None:
+                self.dA, self.dB = bucket.take(linear.RANK, weight.K), bucket.take(weight.N, linear.RANK)
+            else:
+                self.dA = torch.zeros(linear.RANK, weight.K, dtype=torch.float32, device=dev)
+                self.dB = torch.zeros(weight.N, linear.RANK, dtype=torch.float32, device=dev)
+        self._saved = None
+
+    def refresh16(self):
+        self.A16.copy_(self.A)
+        self.B16.copy_(self.B)
+
+    @property
+    def lora(self):
+        return (self.A16, self.B16, self.scale) if self.has_lora else None
+
+    def flops(self, M):
+        """Algorithmic FLOPs of forward + backward-dX (+ dA, dB): 4MNK + 6Mr(N+K)."""
+        f = 4 * M * self.w.N * self.w.K
+        if self.has_lora:
+            f += 6 * M * linear.RANK * (self.w.N + self.w.K)
+        return f
+
+    def forward(self, x, mask=None, keep_scale=1.0, out=None, save=True):
+        y, t = linear.forward(self.w, x, bias=self.bias, lora=self.lora, mask=mask if self.has_lora else None,
+                              keep_scale=keep_scale, out=out, want_t=self.has_lora and save)
+        if save:
+            self._saved = (x, mask if self.has_lora else None, keep_scale, t)
+        return y
+
+    def backward(self, dy, out=None, accumulate=False, need_dx=True, accumulate_grads=False):
+        """dx (optionally accumulated into `out`) and, with LoRA, dA/dB into this projection's views."""
+        x, mask, keep_scale, t = self._saved
+        dx = None
+        u = None
+        if need_dx:
+            dx, u = linear.backward_dx(self.w, dy, lora=self.lora, mask=mask, keep_scale=keep_scale, out=out,
+                                       accumulate=accumulate, want_u=self.has_lora)
+        elif self.has_lora:
+            # layer 0 of the reference needs no d(input), only LoRA gradients (fast_qwen.py:1363-1364)
+            u = torch.empty(dy.shape[0], linear.RANK, dtype=torch.float32, device=dy.device)
+            from . import _lib
+            _lib.check(_lib.lib().nf4ll_lora_down(dy.data_ptr(), dy.stride(0), None, 0, 1.0, self.B16.data_ptr(), 0,
+                                                  self.scale, linear.RANK, dy.shape[0], self.w.N, u.data_ptr(), None,
+                                                  _lib.current_stream(dy.device)))
+        if self.has_lora:
+            linear.lora_grads(dy, x, t, u, self.scale, mask=mask, keep_scale=keep_scale, dA=self.dA, dB=self.dB,
+                              accumulate=accumulate_grads)
+        self._saved = None
+        return dx
+
+
+def make_projection(n_out, n_in, seed, device, lora=False, bias=False, bucket=None, code2=None):
+    """A projection with a seeded synthetic NF4 weight ~ N(0, 0.02) (BASELINE config 0 construction)."""
+    lin = quantize.random_nf4_weight(n_out, n_in, seed=seed, device=device, code2=code2)
+    layer, c2 = k_nf4.repack_layer({"w": lin}, torch.device(device), names=("w",))
+    w = linear.Nf4Weight.from_layer(layer, "w", c2)
+    w._layer = layer          # keep the flat buffer alive
+    b = None
+    if bias:
+        gen = torch.Generator().manual_seed(seed + 1)
+        b = (torch.randn(n_out, generator=gen) * 0.1).half().to(device)
+    return Projection(w, bias=b, lora=lora, bucket=bucket, seed=seed + 2)
+
+
+class MlpBlock:
+    """gate/up/down of one decoder layer with LoRA on every projection (BASELINE config 1). The
+    SiLU-gated product between up and down is plain PyTorch, as that configuration states."""
+
+    def __init__(self, hidden, inter, seed, device, lora=True, bucket=None):
+        self.hidden, self.inter = hidden, inter
+        self.gate = make_projection(inter, hidden, seed * 10 + 1, device, lora=lora, bucket=bucket)
+        self.up = make_projection(inter, hidden, seed * 10 + 2, device, lora=lora, bucket=bucket)
+        self.down = make_projection(hidden, inter, seed * 10 + 3, device, lora=lora, bucket=bucket)
+        self.projections = (self.gate, self.up, self.down)
+        self._saved = None
+
+    @staticmethod
+    def grad_numel(hidden, inter):
+        return 2 * lora_grad_numel(inter, hidden) + lora_grad_numel(hidden, inter)
+
+    def flops(self, M):
+        return sum(p.flops(M) for p in self.projections)
+
+    def forward(self, x, masks=(None, None, None), keep_scale=1.0):
+        g = self.gate.forward(x, masks[0], keep_scale)
+        u = self.up.forward(x, masks[1], keep_scale)
+        h = F.silu(g) * u
+        y = self.down.forward(h, masks[2], keep_scale)
+        self._saved = (g, u)
+        return y
+
+    def backward(self, dy, need_dx=True):
+        g, u = self._saved
+        dh = self.down.backward(dy)
+        gf = g.float()
+        sig = torch.sigmoid(gf)
+        dhf = dh.float()
+        du = (dhf * gf * sig).half()
+        dg = (dhf * u.float() * sig * (1.0 + gf * (1.0 - sig))).half()
+        dx = self.gate.backward(dg, need_dx=need_dx)
+        # d(input) of gate and up are summed into one buffer (the reference adds them in fp16,
+        # solution/fast_qwen.py:1320-1323; here the add happens on the fp32 accumulator)
+        dx = self.up.backward(du, out=dx, accumulate=need_dx, need_dx=need_dx)
+        self._saved = None
+        return dx

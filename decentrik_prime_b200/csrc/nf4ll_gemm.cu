@@ -535,6 +535,7 @@ struct Plan {
 };
 
 static thread_local int g_force_bm = 0, g_force_bn = 0, g_force_splits = 0;
+static thread_local cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;
 
 static int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
 
@@ -696,7 +697,12 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
   }
   CUtensorMap map;
   if (int rc = make_act_map(&map, act, M, KC, ldact)) return rc;
-  return mode == kFwd ? launch<kFwd>(map, p, pl, stream) : launch<kBwd>(map, p, pl, stream);
+  cudaEvent_t ev0 = g_ev_start, ev1 = g_ev_stop;
+  g_ev_start = g_ev_stop = nullptr;
+  if (ev0) NF4LL_CUDA(cudaEventRecord(ev0, stream));
+  const int rc = mode == kFwd ? launch<kFwd>(map, p, pl, stream) : launch<kBwd>(map, p, pl, stream);
+  if (rc == NF4LL_OK && ev1) NF4LL_CUDA(cudaEventRecord(ev1, stream));
+  return rc;
 }
 
 }  // namespace nf4ll
@@ -733,4 +739,12 @@ extern "C" void nf4ll_tune_override(int32_t bm_tiles, int32_t bn, int32_t splits
   nf4ll::g_force_bm = (bm_tiles == 1 || bm_tiles == 2) ? bm_tiles : 0;
   nf4ll::g_force_bn = (bn == 128 || bn == 256) ? bn : 0;
   nf4ll::g_force_splits = splits > 0 ? splits : 0;
+}
+
+// Measurement hook (no counterpart in the reference): the calling thread's NEXT nf4ll_forward /
+// nf4ll_backward_dx records `start` immediately before and `stop` immediately after its tensor-core
+// kernel on the call's stream (the rank-16 prologue kernel stays outside the pair). One-shot.
+extern "C" void nf4ll_kernel_events(void* start, void* stop) {
+  nf4ll::g_ev_start = static_cast<cudaEvent_t>(start);
+  nf4ll::g_ev_stop = static_cast<cudaEvent_t>(stop);
 }

@@ -139,6 +139,12 @@ int nf4ll_read_status(const int32_t* status, void* stream);
  * thread's next nf4ll_forward / nf4ll_backward_dx calls; zeros restore the built-in heuristic. */
 void nf4ll_tune_override(int32_t bm_tiles, int32_t bn, int32_t splits);
 
+/* Measurement hook; no counterpart in the reference. The calling thread's NEXT nf4ll_forward /
+ * nf4ll_backward_dx records the CUDA events `start` / `stop` (cudaEvent_t as void*) right before /
+ * after its tensor-core kernel on the call's stream, leaving the small rank-16 prologue kernel
+ * outside the pair. One-shot: the pair is forgotten after that call. */
+void nf4ll_kernel_events(void* start, void* stop);
+
 #ifdef __cplusplus
 }
 #endif
