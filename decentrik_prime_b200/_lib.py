@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB_PATH = os.path.join(HERE, "libnf4ll.so")
-SOURCES = ("nf4ll_api.cu", "nf4ll_dequant.cu", "nf4ll_gemm.cu", "nf4ll_lora.cu")
+SOURCES = ("nf4ll_api.cu", "nf4ll_dequant.cu", "nf4ll_gemm.cu", "nf4ll_lora.cu", "nf4ll_swiglu.cu")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "--fmad=true", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "-shared"]
@@ -71,7 +71,7 @@ class LoraArgs(ctypes.Structure):
     """struct nf4ll_lora (include/nf4ll.h)."""
     _fields_ = [("A", ctypes.c_void_p), ("B", ctypes.c_void_p), ("r", ctypes.c_int32),
                 ("scale", ctypes.c_float), ("mask", ctypes.c_void_p), ("ld_mask", ctypes.c_int64),
-                ("keep_scale", ctypes.c_float)]
+                ("keep_scale", ctypes.c_float), ("Bt", ctypes.c_void_p)]
 
 
 _vp, _i64, _i32, _f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_float
@@ -86,11 +86,13 @@ SIGNATURES = {
     "nf4ll_workspace_bytes": (_i64, [_i64, _i64, _i64, _i32]),
     "nf4ll_forward": (_i32, [_MAT, _vp, _i64, _vp, _LORA, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp]),
     "nf4ll_backward_dx": (_i32, [_MAT, _vp, _i64, _LORA, _vp, _i64, _vp, _i64, _i32, _vp, _i64, _vp, _vp]),
-    "nf4ll_lora_down": (_i32, [_vp, _i64, _vp, _i64, _f32, _vp, _i32, _f32, _i32, _i64, _i64, _vp, _vp, _vp]),
+    "nf4ll_lora_down": (_i32, [_vp, _i64, _vp, _i64, _f32, _vp, _f32, _i32, _i64, _i64, _vp, _vp, _vp]),
     "nf4ll_lora_grads": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _f32, _vp, _vp, _f32, _i32, _i64, _i64, _i64,
                                 _vp, _vp, _i32, _vp]),
     "nf4ll_tune_override": (None, [_i32, _i32, _i32]),
     "nf4ll_kernel_events": (None, [_vp, _vp]),
+    "nf4ll_swiglu_forward": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _vp]),
+    "nf4ll_swiglu_backward": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "nf4ll_read_status": (_i32, [_vp, _vp]),
 }
 

@@ -59,6 +59,7 @@ class Projection:
             self.B = (torch.randn(weight.N, linear.RANK, generator=gen) * b_std).to(dev)
             self.A16 = torch.empty_like(self.A, dtype=torch.float16)
             self.B16 = torch.empty_like(self.B, dtype=torch.float16)
+            self.B16t = torch.empty(linear.RANK, weight.N, dtype=torch.float16, device=dev)
             self.refresh16()
             if bucket is not None:
                 self.dA, self.dB = bucket.take(linear.RANK, weight.K), bucket.take(weight.N, linear.RANK)
@@ -70,10 +71,11 @@ class Projection:
     def refresh16(self):
         self.A16.copy_(self.A)
         self.B16.copy_(self.B)
+        self.B16t.copy_(self.B.t())
 
     @property
     def lora(self):
-        return (self.A16, self.B16, self.scale) if self.has_lora else None
+        return (self.A16, self.B16, self.scale, self.B16t) if self.has_lora else None
 
     def flops(self, M):
         """Algorithmic FLOPs of forward + backward-dX (+ dA, dB): 4MNK + 6Mr(N+K)."""
@@ -101,9 +103,10 @@ class Projection:
             # layer 0 of the reference needs no d(input), only LoRA gradients (fast_qwen.py:1363-1364)
             u = torch.empty(dy.shape[0], linear.RANK, dtype=torch.float32, device=dy.device)
             from . import _lib
-            _lib.check(_lib.lib().nf4ll_lora_down(dy.data_ptr(), dy.stride(0), None, 0, 1.0, self.B16.data_ptr(), 0,
-                                                  self.scale, linear.RANK, dy.shape[0], self.w.N, u.data_ptr(), None,
+            _lib.check(_lib.lib().nf4ll_lora_down(dy.data_ptr(), dy.stride(0), None, 0, 1.0, self.B16t.data_ptr(),
+                                                  1.0, linear.RANK, dy.shape[0], self.w.N, u.data_ptr(), None,
                                                   _lib.current_stream(dy.device)))
+            u.mul_(self.scale)
         if self.has_lora:
             linear.lora_grads(dy, x, t, u, self.scale, mask=mask, keep_scale=keep_scale, dA=self.dA, dB=self.dB,
                               accumulate=accumulate_grads)
@@ -126,10 +129,12 @@ def make_projection(n_out, n_in, seed, device, lora=False, bias=False, bucket=No
 
 class MlpBlock:
     """gate/up/down of one decoder layer with LoRA on every projection (BASELINE config 1). The
-    SiLU-gated product between up and down is plain PyTorch, as that configuration states."""
+    SiLU-gated product between up and down is either the library's fused kernel pair (the
+    counterpart of the reference's gated_silu kernels) or plain PyTorch ops (fused_glue=False)."""
 
-    def __init__(self, hidden, inter, seed, device, lora=True, bucket=None):
+    def __init__(self, hidden, inter, seed, device, lora=True, bucket=None, fused_glue=True):
         self.hidden, self.inter = hidden, inter
+        self.fused_glue = fused_glue      # library SwiGLU kernels (reference k_mlp.py) or plain PyTorch
         self.gate = make_projection(inter, hidden, seed * 10 + 1, device, lora=lora, bucket=bucket)
         self.up = make_projection(inter, hidden, seed * 10 + 2, device, lora=lora, bucket=bucket)
         self.down = make_projection(hidden, inter, seed * 10 + 3, device, lora=lora, bucket=bucket)
@@ -146,7 +151,7 @@ class MlpBlock:
     def forward(self, x, masks=(None, None, None), keep_scale=1.0):
         g = self.gate.forward(x, masks[0], keep_scale)
         u = self.up.forward(x, masks[1], keep_scale)
-        h = F.silu(g) * u
+        h = linear.swiglu_forward(g, u) if self.fused_glue else F.silu(g.float()).mul_(u.float()).half()
         y = self.down.forward(h, masks[2], keep_scale)
         self._saved = (g, u)
         return y
@@ -154,11 +159,14 @@ class MlpBlock:
     def backward(self, dy, need_dx=True):
         g, u = self._saved
         dh = self.down.backward(dy)
-        gf = g.float()
-        sig = torch.sigmoid(gf)
-        dhf = dh.float()
-        du = (dhf * gf * sig).half()
-        dg = (dhf * u.float() * sig * (1.0 + gf * (1.0 - sig))).half()
+        if self.fused_glue:
+            dg, du = linear.swiglu_backward(g, u, dh, inplace=True)
+        else:
+            gf = g.float()
+            sig = torch.sigmoid(gf)
+            dhf = dh.float()
+            du = (dhf * gf * sig).half()
+            dg = (dhf * u.float() * sig * (1.0 + gf * (1.0 - sig))).half()
         dx = self.gate.backward(dg, need_dx=need_dx)
         # d(input) of gate and up are summed into one buffer (the reference adds them in fp16,
         # solution/fast_qwen.py:1320-1323; here the add happens on the fp32 accumulator)

@@ -530,8 +530,8 @@ static int make_act_map(CUtensorMap* map, const void* base, int64_t rows, int64_
 struct Plan {
   int bm_tiles, bn, splits;
   int64_t tiles_m, tiles_o, m_pad;
-  int64_t left_bytes, counter_bytes, partial_bytes;
-  int64_t total() const { return left_bytes + counter_bytes + partial_bytes; }
+  int64_t left_bytes, bt_bytes, counter_bytes, partial_bytes;
+  int64_t total() const { return left_bytes + bt_bytes + counter_bytes + partial_bytes; }
 };
 
 static thread_local int g_force_bm = 0, g_force_bn = 0, g_force_splits = 0;
@@ -564,6 +564,7 @@ static Plan make_plan(int64_t M, int64_t NO, int64_t KC, int r, int sms) {
   if (splits > nkb) splits = static_cast<int>(nkb > 0 ? nkb : 1);
   pl.splits = splits;
   pl.left_bytes = r > 0 ? align256(M * r * 2) : 0;
+  pl.bt_bytes = r > 0 ? align256(KC * r * 2) : 0;      // room for lora_B transposed (backward only uses it)
   pl.counter_bytes = splits > 1 ? align256(tiles * 4) : 0;
   pl.partial_bytes = splits > 1 ? align256(static_cast<int64_t>(splits) * pl.m_pad * NO * 4) : 0;
   return pl;
@@ -627,7 +628,8 @@ static int check_lora(const nf4ll_lora* l, const char* who, bool need_mask_ld, i
   if (!l) return NF4LL_OK;
   if (l->r != 16) { set_detail("%s: LoRA rank %d", who, l->r); return NF4LL_ERR_RANK; }
   if (!l->A || !l->B) { set_detail("%s: LoRA A/B null", who); return NF4LL_ERR_NULL; }
-  if ((reinterpret_cast<uintptr_t>(l->A) & 15) || (reinterpret_cast<uintptr_t>(l->B) & 15)) {
+  if ((reinterpret_cast<uintptr_t>(l->A) & 15) || (reinterpret_cast<uintptr_t>(l->B) & 15) ||
+      (reinterpret_cast<uintptr_t>(l->Bt) & 15)) {
     set_detail("%s: LoRA A/B must be 16-byte aligned", who);
     return NF4LL_ERR_ALIGN;
   }
@@ -638,8 +640,10 @@ static int check_lora(const nf4ll_lora* l, const char* who, bool need_mask_ld, i
   return NF4LL_OK;
 }
 
-int lora_down_launch(const void* x, int64_t ldx, const uint8_t* mask, int64_t ld_mask, float keep_scale, const void* A,
-                     int a_kmajor, float scale, int64_t M, int64_t K, void* t32, void* t16, cudaStream_t stream);
+int lora_down_launch(const void* act, int64_t ldact, const uint8_t* mask, int64_t ld_mask, float keep_scale,
+                     const void* R, float t32_scale, float t16_scale, int64_t M, int64_t C, void* t32, void* t16,
+                     cudaStream_t stream);
+int transpose_n16_launch(const void* B, void* Bt, int64_t N, cudaStream_t stream);
 
 static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact, const void* bias,
                     const nf4ll_lora* lora, void* side_out, int64_t M, void* out, int64_t ldo, int accumulate,
@@ -679,20 +683,27 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
     __half* left = reinterpret_cast<__half*>(ws);
     // rank-16 projection of the activation: T = drop(x).A^T (forward) or U = dy.B (backward)
     if (mode == kFwd) {
-      if (int rc = lora_down_launch(act, ldact, lora->mask, lora->ld_mask, lora->keep_scale, lora->A, 1, lora->scale, M,
-                                    W->K, side_out, left, stream)) return rc;
+      if (int rc = lora_down_launch(act, ldact, lora->mask, lora->ld_mask, lora->keep_scale, lora->A, 1.0f, lora->scale,
+                                    M, W->K, side_out, left, stream)) return rc;
       p.lora_right = static_cast<const __half*>(lora->B);
     } else {
+      const void* bt = lora->Bt;
+      if (!bt) {
+        void* tmp = ws + pl.left_bytes;
+        if (int rc = transpose_n16_launch(lora->B, tmp, W->N, stream)) return rc;
+        bt = tmp;
+      }
       // u = scale * dy.B: fp16 for the tensor core here, fp32 (side_out) for the dA kernel later
-      if (int rc = lora_down_launch(act, ldact, nullptr, 0, 1.0f, lora->B, 0, lora->scale, M, W->N, side_out, left, stream)) return rc;
+      if (int rc = lora_down_launch(act, ldact, nullptr, 0, 1.0f, bt, lora->scale, lora->scale, M, W->N, side_out, left,
+                                    stream)) return rc;
       p.lora_right = static_cast<const __half*>(lora->A);
       p.mask = lora->mask; p.ld_mask = lora->ld_mask; p.keep_scale = lora->keep_scale;
     }
     p.lora_left = left;
   }
   if (pl.splits > 1) {
-    p.counters = reinterpret_cast<int*>(ws + pl.left_bytes);
-    p.partial = reinterpret_cast<float*>(ws + pl.left_bytes + pl.counter_bytes);
+    p.counters = reinterpret_cast<int*>(ws + pl.left_bytes + pl.bt_bytes);
+    p.partial = reinterpret_cast<float*>(ws + pl.left_bytes + pl.bt_bytes + pl.counter_bytes);
     NF4LL_CUDA(cudaMemsetAsync(p.counters, 0, pl.counter_bytes, stream));
   }
   CUtensorMap map;

@@ -1,166 +1,265 @@
-// The skinny (rank-16) LoRA products around the fused linear:
-//   lora_down   t[M,16]  = drop(x)[M,K] . A^T            (forward: T;  backward: U = dy . B)
+// The skinny (rank-16) LoRA products around the fused linear, as small tensor-core GEMMs:
+//   lora_down   t[M,16]  = drop(x)[M,C] . R^T,  R = lora_A [16,C]      (forward: T)
+//                                               R = lora_B^T [16,C]    (backward: U = dy . B)
 //   lora_grads  dA[16,K] (+)= u^T . drop(x),  dB[N,16] (+)= scale * dy^T . t
-// Replaces solution/fast_qwen.py:943-944 and 1369-1374 of the reference. All accumulation is fp32,
-// and t / u are kept in fp32 between the passes: the reference rounds them (and dA/dB) to fp16,
-// which costs up to 0.08 absolute error on gradients of magnitude ~100.
+// Replaces solution/fast_qwen.py:943-944 and 1369-1374 of the reference. Accumulation is fp32 and
+// t / u stay fp32 between the passes (split into fp16 hi + lo parts where they feed a tensor-core
+// operand): the reference rounds them (and dA/dB) to fp16, which costs up to 0.08 absolute error on
+// gradients of magnitude ~100.
 //
-// These are bandwidth-bound streaming passes over x / dy (16 multiply-adds per element read).
+// Both kernels are bandwidth-bound passes over x / dy (32 multiply-adds per fp16 element read), so
+// they use warp-level mma.sync.m16n8k16 with operands loaded straight from global memory with
+// 128-bit loads; there is nothing for TMA staging or tensor memory to win here.
 #include "nf4ll_common.cuh"
 
 namespace nf4ll {
 
-// drop(x) for 8 packed fp16 values: fp16(x * keep_scale) where the mask byte is non-zero, else 0
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// drop(x) on 8 packed fp16 values: fp16(x * keep_scale) where the mask byte is non-zero, else 0
 // (reference solution/k_norm.py:49-53: scale in fp32, then one rounding to fp16).
-__device__ __forceinline__ void load_dropped8(const __half* xp, const uint8_t* mp, float keep_scale, float (&f)[8]) {
-  const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xp));
-  const __half2* h = reinterpret_cast<const __half2*>(&raw);
+__device__ __forceinline__ uint4 drop8(uint4 raw, uint2 m, float keep_scale) {
+  uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  const uint32_t mw[2] = {m.x, m.y};
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const float2 v = __half22float2(h[j]);
-    f[2 * j] = v.x;
-    f[2 * j + 1] = v.y;
+    const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+    const bool k0 = ((mw[j >> 1] >> ((2 * j & 3) * 8)) & 0xffu) != 0;
+    const bool k1 = ((mw[j >> 1] >> (((2 * j + 1) & 3) * 8)) & 0xffu) != 0;
+    w[j] = pack_half2_rn(k0 ? v.x * keep_scale : 0.f, k1 ? v.y * keep_scale : 0.f);
   }
-  if (mp) {
-    const uint2 m = __ldg(reinterpret_cast<const uint2*>(mp));
-    const uint32_t mw[2] = {m.x, m.y};
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const bool keep = ((mw[j >> 2] >> ((j & 3) * 8)) & 0xffu) != 0;
-      f[j] = keep ? __half2float(__float2half_rn(f[j] * keep_scale)) : 0.0f;
-    }
-  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Row reduction: t[M,16] = drop(act)[M,C] . R^T with R [16,C] row-major fp16.
+// One CTA = 16 rows, 8 warps; warp w takes the 32-column chunks w, w+8, ... of the contraction and
+// the partial 16x16 results are summed through shared memory. Per chunk a lane issues two 128-bit
+// loads of act (rows g and g+8) and two of R (rank rows g and g+8); a lane's 8 consecutive columns
+// are fed to two MMAs with the SAME column-to-slot assignment on both operands, so no shuffle or
+// shared-memory transpose is needed: out^T[16 ranks, 8 rows] = R[16, k] . act^T[k, 8 rows].
+// ---------------------------------------------------------------------------------------------
 constexpr int kDownWarps = 8;
 
-// One warp per row. A_KMAJOR: A is [16, K] (lora_A); otherwise A is [K, 16] (lora_B read as dy's
-// right factor). Lane l takes columns 8*(32*step + l) .. +7.
-template <bool A_KMAJOR>
 __global__ void __launch_bounds__(kDownWarps * 32)
-lora_down_kernel(const __half* __restrict__ x, int64_t ldx, const uint8_t* __restrict__ mask, int64_t ld_mask,
-                 float keep_scale, const __half* __restrict__ A, float scale, int64_t M, int64_t K,
+lora_down_kernel(const __half* __restrict__ act, int64_t ldact, const uint8_t* __restrict__ mask, int64_t ld_mask,
+                 float keep_scale, const __half* __restrict__ R, float t32_scale, float t16_scale, int64_t M, int64_t C,
                  float* __restrict__ t32, __half* __restrict__ t16) {
-  const int lane = threadIdx.x & 31;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * kDownWarps + (threadIdx.x >> 5);
-  if (row >= M) return;
-  float acc[16];
-#pragma unroll
-  for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-  const __half* xr = x + row * ldx;
-  const uint8_t* mr = mask ? mask + row * ld_mask : nullptr;
-  for (int64_t k = lane * 8; k < K; k += 256) {
-    float f[8];
-    load_dropped8(xr + k, mr ? mr + k : nullptr, keep_scale, f);
-    if (A_KMAJOR) {
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(A + j * K + k));
-        const __half2* h = reinterpret_cast<const __half2*>(&raw);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 a = __half22float2(h[i]);
-          acc[j] = fmaf(f[2 * i], a.x, acc[j]);
-          acc[j] = fmaf(f[2 * i + 1], a.y, acc[j]);
-        }
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const uint4* ap = reinterpret_cast<const uint4*>(A + (k + i) * 16);
-        const uint4 r0 = __ldg(ap), r1 = __ldg(ap + 1);
-        const __half2* h0 = reinterpret_cast<const __half2*>(&r0);
-        const __half2* h1 = reinterpret_cast<const __half2*>(&r1);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 a = __half22float2(h0[j]), b = __half22float2(h1[j]);
-          acc[2 * j] = fmaf(f[i], a.x, acc[2 * j]);
-          acc[2 * j + 1] = fmaf(f[i], a.y, acc[2 * j + 1]);
-          acc[8 + 2 * j] = fmaf(f[i], b.x, acc[8 + 2 * j]);
-          acc[8 + 2 * j + 1] = fmaf(f[i], b.y, acc[8 + 2 * j + 1]);
-        }
-      }
+  __shared__ float part[kDownWarps][16][17];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int64_t m0 = static_cast<int64_t>(blockIdx.x) * 16;
+  const int64_t row0 = m0 + g, row1 = m0 + g + 8;
+  const bool ok0 = row0 < M, ok1 = row1 < M;
+  const __half* a0p = act + (ok0 ? row0 : 0) * ldact;
+  const __half* a1p = act + (ok1 ? row1 : 0) * ldact;
+  const uint8_t* m0p = mask ? mask + (ok0 ? row0 : 0) * ld_mask : nullptr;
+  const uint8_t* m1p = mask ? mask + (ok1 ? row1 : 0) * ld_mask : nullptr;
+  const __half* r0p = R + static_cast<int64_t>(g) * C;
+  const __half* r1p = R + static_cast<int64_t>(g + 8) * C;
+  float c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int64_t k = static_cast<int64_t>(warp) * 32 + t * 8; k < C; k += kDownWarps * 32) {
+    uint4 x0 = ok0 ? __ldg(reinterpret_cast<const uint4*>(a0p + k)) : zero;
+    uint4 x1 = ok1 ? __ldg(reinterpret_cast<const uint4*>(a1p + k)) : zero;
+    const uint4 ra = __ldg(reinterpret_cast<const uint4*>(r0p + k));
+    const uint4 rb = __ldg(reinterpret_cast<const uint4*>(r1p + k));
+    if (mask) {
+      x0 = drop8(x0, __ldg(reinterpret_cast<const uint2*>(m0p + k)), keep_scale);
+      x1 = drop8(x1, __ldg(reinterpret_cast<const uint2*>(m1p + k)), keep_scale);
     }
+    // columns k..k+3 -> MMA slots (2t, 2t+1, 2t+8, 2t+9) of the first MMA, k+4..k+7 of the second
+    mma16816(c0, ra.x, rb.x, ra.y, rb.y, x0.x, x0.y);
+    mma16816(c0, ra.z, rb.z, ra.w, rb.w, x0.z, x0.w);
+    mma16816(c1, ra.x, rb.x, ra.y, rb.y, x1.x, x1.y);
+    mma16816(c1, ra.z, rb.z, ra.w, rb.w, x1.z, x1.w);
   }
-#pragma unroll
-  for (int j = 0; j < 16; ++j) {
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
-  }
-  if (lane < 16) {
+  // accumulator layout: c[0], c[1] = (rank g, rows 2t, 2t+1); c[2], c[3] = (rank g+8, same rows)
+  part[warp][2 * t][g] = c0[0];      part[warp][2 * t + 1][g] = c0[1];
+  part[warp][2 * t][g + 8] = c0[2];  part[warp][2 * t + 1][g + 8] = c0[3];
+  part[warp][8 + 2 * t][g] = c1[0];      part[warp][8 + 2 * t + 1][g] = c1[1];
+  part[warp][8 + 2 * t][g + 8] = c1[2];  part[warp][8 + 2 * t + 1][g + 8] = c1[3];
+  __syncthreads();
+  const int row = threadIdx.x >> 4, j = threadIdx.x & 15;
+  if (m0 + row < M) {
     float v = 0.f;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) v = (lane == j) ? acc[j] : v;
-    if (t32) t32[row * 16 + lane] = A_KMAJOR ? v : v * scale;   // T unscaled; U carries the scale
-    if (t16) t16[row * 16 + lane] = __float2half_rn(v * scale);
+    for (int w = 0; w < kDownWarps; ++w) v += part[w][row][j];
+    if (t32) t32[(m0 + row) * 16 + j] = v * t32_scale;
+    if (t16) t16[(m0 + row) * 16 + j] = __float2half_rn(v * t16_scale);
   }
 }
 
-int lora_down_launch(const void* x, int64_t ldx, const uint8_t* mask, int64_t ld_mask, float keep_scale, const void* A,
-                     int a_kmajor, float scale, int64_t M, int64_t K, void* t32, void* t16, cudaStream_t stream) {
-  if (M == 0) return NF4LL_OK;
-  const unsigned blocks = static_cast<unsigned>((M + kDownWarps - 1) / kDownWarps);
-  if (a_kmajor) {
-    lora_down_kernel<true><<<blocks, kDownWarps * 32, 0, stream>>>(
-        static_cast<const __half*>(x), ldx, mask, ld_mask, keep_scale, static_cast<const __half*>(A), scale, M, K,
-        static_cast<float*>(t32), static_cast<__half*>(t16));
-  } else {
-    lora_down_kernel<false><<<blocks, kDownWarps * 32, 0, stream>>>(
-        static_cast<const __half*>(x), ldx, mask, ld_mask, keep_scale, static_cast<const __half*>(A), scale, M, K,
-        static_cast<float*>(t32), static_cast<__half*>(t16));
+// B[N,16] -> Bt[16,N] (fp16), for callers that do not keep a transposed shadow of lora_B.
+__global__ void transpose_n16_kernel(const __half* __restrict__ B, __half* __restrict__ Bt, int64_t N) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < N * 16) {
+    const int64_t n = i >> 4;
+    const int j = static_cast<int>(i & 15);
+    Bt[j * N + n] = B[i];
   }
+}
+
+int transpose_n16_launch(const void* B, void* Bt, int64_t N, cudaStream_t stream) {
+  const int64_t total = N * 16;
+  transpose_n16_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+      static_cast<const __half*>(B), static_cast<__half*>(Bt), N);
   NF4LL_CUDA(cudaGetLastError());
   return NF4LL_OK;
 }
 
-// out[j, col] (+)= scale * sum_m side[m, j] * drop(act)[m, col]   for j < 16
-// One CTA: 512 columns (2 per thread) x a chunk of kGradRows rows; partial sums are added to the
-// output with fp32 atomics. out index = j * ld_j + col * ld_col, which covers dA[16,K] (ld_j = K,
-// ld_col = 1) and dB[N,16] (ld_j = 1, ld_col = 16).
-constexpr int kGradThreads = 256;
-constexpr int kGradRows = 64;
+// R is [16,C] row-major. t32 = t32_scale * (drop(act) . R^T), t16 = fp16(t16_scale * (...)).
+int lora_down_launch(const void* act, int64_t ldact, const uint8_t* mask, int64_t ld_mask, float keep_scale,
+                     const void* R, float t32_scale, float t16_scale, int64_t M, int64_t C, void* t32, void* t16,
+                     cudaStream_t stream) {
+  if (M == 0) return NF4LL_OK;
+  lora_down_kernel<<<static_cast<unsigned>((M + 15) / 16), kDownWarps * 32, 0, stream>>>(
+      static_cast<const __half*>(act), ldact, mask, ld_mask, keep_scale, static_cast<const __half*>(R), t32_scale,
+      t16_scale, M, C, static_cast<float*>(t32), static_cast<__half*>(t16));
+  NF4LL_CUDA(cudaGetLastError());
+  return NF4LL_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Column reduction: out[c][j] (+)= scale * sum_m drop(act)[m][c] * side[m][j]   (j < 16)
+// as out^T[16, C] = side^T[16, M] . drop(act)[M, C]. One CTA = 64 columns x a range of rows, 4
+// warps. Per 64-row stage the act tile goes to shared memory (dropout applied on the way), side
+// goes there transposed and split into fp16 hi + lo parts (two MMAs recover ~22 mantissa bits),
+// warp w contracts rows 16w..16w+15 of the stage against all 64 columns (ldmatrix.trans delivers the
+// row-major act tile as the MMA's k-by-n operand). Row ranges of different CTAs are combined with
+// fp32 atomics, so the summation order across ranges is not fixed.
+// out index = j * ld_j + c * ld_c: dA[16,K] uses (K, 1), dB[N,16] uses (1, 16).
+// ---------------------------------------------------------------------------------------------
+constexpr int kGradThreads = 128;
+constexpr int kGradCols = 64;
+constexpr int kGradStage = 64;
+constexpr int kActStride = 72;     // halves per shared row: 144 B keeps ldmatrix rows on distinct banks
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
 
 __global__ void __launch_bounds__(kGradThreads)
 lora_grad_kernel(const __half* __restrict__ act, int64_t ldact, const uint8_t* __restrict__ mask, int64_t ld_mask,
-                 float keep_scale, const float* __restrict__ side, float scale, int64_t M, int64_t C,
-                 float* __restrict__ out, int64_t ld_j, int64_t ld_col) {
-  __shared__ float s_side[kGradRows][16];
-  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * kGradRows;
-  const int rows = static_cast<int>(M - r0 < kGradRows ? M - r0 : kGradRows);
-  for (int i = threadIdx.x; i < rows * 16; i += kGradThreads) s_side[i >> 4][i & 15] = side[r0 * 16 + i];
+                 float keep_scale, const float* __restrict__ side, float scale, int64_t M, int64_t C, int64_t rows_per_cta,
+                 float* __restrict__ out, int64_t ld_j, int64_t ld_c) {
+  __shared__ __align__(16) __half s_act[kGradStage][kActStride];
+  __shared__ __align__(16) __half s_hi[16][kActStride];
+  __shared__ __align__(16) __half s_lo[16][kActStride];
+  __shared__ float s_red[4][16][kGradCols + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int64_t c0 = static_cast<int64_t>(blockIdx.x) * kGradCols;
+  const int64_t r_begin = static_cast<int64_t>(blockIdx.y) * rows_per_cta;
+  const int64_t r_end = (r_begin + rows_per_cta < M) ? r_begin + rows_per_cta : M;
+  float acc[8][4];
+#pragma unroll
+  for (int n = 0; n < 8; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+
+  for (int64_t r0 = r_begin; r0 < r_end; r0 += kGradStage) {
+    // stage the act tile: 64 rows x 8 chunks of 8 columns = 512 chunks over 128 threads
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = threadIdx.x + i * kGradThreads;
+      const int r = idx >> 3, ch = idx & 7;
+      const int64_t row = r0 + r, col = c0 + ch * 8;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (row < r_end && col < C) {
+        v = __ldg(reinterpret_cast<const uint4*>(act + row * ldact + col));
+        if (mask) v = drop8(v, __ldg(reinterpret_cast<const uint2*>(mask + row * ld_mask + col)), keep_scale);
+      }
+      *reinterpret_cast<uint4*>(&s_act[r][ch * 8]) = v;
+    }
+    // stage side transposed, split into hi + lo: 64 rows x 16 = 1024 values over 128 threads
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = threadIdx.x + i * kGradThreads;
+      const int r = idx >> 4, j = idx & 15;
+      const float v = (r0 + r < r_end) ? __ldg(side + (r0 + r) * 16 + j) : 0.f;
+      const __half hi = __float2half_rn(v);
+      s_hi[j][r] = hi;
+      s_lo[j][r] = __float2half_rn(v - __half2float(hi));
+    }
+    __syncthreads();
+    const int kb = warp * 16;      // this warp's 16 rows of the stage
+    const uint32_t ah0 = *reinterpret_cast<const uint32_t*>(&s_hi[g][kb + 2 * t]);
+    const uint32_t ah1 = *reinterpret_cast<const uint32_t*>(&s_hi[g + 8][kb + 2 * t]);
+    const uint32_t ah2 = *reinterpret_cast<const uint32_t*>(&s_hi[g][kb + 2 * t + 8]);
+    const uint32_t ah3 = *reinterpret_cast<const uint32_t*>(&s_hi[g + 8][kb + 2 * t + 8]);
+    const uint32_t al0 = *reinterpret_cast<const uint32_t*>(&s_lo[g][kb + 2 * t]);
+    const uint32_t al1 = *reinterpret_cast<const uint32_t*>(&s_lo[g + 8][kb + 2 * t]);
+    const uint32_t al2 = *reinterpret_cast<const uint32_t*>(&s_lo[g][kb + 2 * t + 8]);
+    const uint32_t al3 = *reinterpret_cast<const uint32_t*>(&s_lo[g + 8][kb + 2 * t + 8]);
+#pragma unroll
+    for (int np = 0; np < 4; ++np) {     // pairs of 8-column tiles
+      // matrices: (k 0-7, n 0-7), (k 8-15, n 0-7), (k 0-7, n 8-15), (k 8-15, n 8-15) of this pair
+      const int mrow = kb + ((lane >> 3) & 1) * 8 + (lane & 7);
+      const int mcol = np * 16 + (lane >> 4) * 8;
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4_trans(smem_u32(&s_act[mrow][mcol]), b0, b1, b2, b3);
+      mma16816(acc[2 * np], ah0, ah1, ah2, ah3, b0, b1);
+      mma16816(acc[2 * np], al0, al1, al2, al3, b0, b1);
+      mma16816(acc[2 * np + 1], ah0, ah1, ah2, ah3, b2, b3);
+      mma16816(acc[2 * np + 1], al0, al1, al2, al3, b2, b3);
+    }
+    __syncthreads();
+  }
+  // combine the four warps' row slices, then add into the output
+#pragma unroll
+  for (int n = 0; n < 8; ++n) {
+    s_red[warp][g][n * 8 + 2 * t] = acc[n][0];
+    s_red[warp][g][n * 8 + 2 * t + 1] = acc[n][1];
+    s_red[warp][g + 8][n * 8 + 2 * t] = acc[n][2];
+    s_red[warp][g + 8][n * 8 + 2 * t + 1] = acc[n][3];
+  }
   __syncthreads();
-  const int64_t col = (static_cast<int64_t>(blockIdx.x) * kGradThreads + threadIdx.x) * 2;
-  if (col >= C) return;
-  float a0[16], a1[16];
-#pragma unroll
-  for (int j = 0; j < 16; ++j) a0[j] = a1[j] = 0.f;
-  for (int r = 0; r < rows; ++r) {
-    const __half2 h = *reinterpret_cast<const __half2*>(act + (r0 + r) * ldact + col);
-    float2 v = __half22float2(h);
-    if (mask) {
-      const uint8_t* mp = mask + (r0 + r) * ld_mask + col;
-      v.x = mp[0] ? __half2float(__float2half_rn(v.x * keep_scale)) : 0.f;
-      v.y = mp[1] ? __half2float(__float2half_rn(v.y * keep_scale)) : 0.f;
-    }
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float sj = s_side[r][j];
-      a0[j] = fmaf(sj, v.x, a0[j]);
-      a1[j] = fmaf(sj, v.y, a1[j]);
+  for (int idx = threadIdx.x; idx < 16 * kGradCols; idx += kGradThreads) {
+    // dA (ld_c == 1): consecutive threads take consecutive columns; dB (ld_j == 1): consecutive ranks
+    const int j = (ld_c == 1) ? idx / kGradCols : idx % 16;
+    const int c = (ld_c == 1) ? idx % kGradCols : idx / 16;
+    if (c0 + c < C) {
+      const float v = s_red[0][j][c] + s_red[1][j][c] + s_red[2][j][c] + s_red[3][j][c];
+      atomicAdd(out + j * ld_j + (c0 + c) * ld_c, v * scale);
     }
   }
-#pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    atomicAdd(out + j * ld_j + col * ld_col, a0[j] * scale);
-    atomicAdd(out + j * ld_j + (col + 1) * ld_col, a1[j] * scale);
-  }
+}
+
+static int lora_grad_launch(const void* act, int64_t ldact, const uint8_t* mask, int64_t ld_mask, float keep_scale,
+                            const void* side, float scale, int64_t M, int64_t C, void* out, int64_t ld_j, int64_t ld_c,
+                            cudaStream_t stream) {
+  int dev = 0, sms = 148;
+  NF4LL_CUDA(cudaGetDevice(&dev));
+  NF4LL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int64_t col_tiles = (C + kGradCols - 1) / kGradCols;
+  const int64_t stages = (M + kGradStage - 1) / kGradStage;
+  int64_t msplit = (4 * static_cast<int64_t>(sms) + col_tiles - 1) / col_tiles;    // about four CTAs per SM
+  if (msplit > stages) msplit = stages;
+  if (msplit < 1) msplit = 1;
+  const int64_t rows_per = (stages + msplit - 1) / msplit * kGradStage;
+  msplit = (M + rows_per - 1) / rows_per;
+  dim3 grid(static_cast<unsigned>(col_tiles), static_cast<unsigned>(msplit));
+  lora_grad_kernel<<<grid, kGradThreads, 0, stream>>>(static_cast<const __half*>(act), ldact, mask, ld_mask, keep_scale,
+                                                      static_cast<const float*>(side), scale, M, C, rows_per,
+                                                      static_cast<float*>(out), ld_j, ld_c);
+  NF4LL_CUDA(cudaGetLastError());
+  return NF4LL_OK;
 }
 
 }  // namespace nf4ll
 
 extern "C" int nf4ll_lora_down(const void* x, int64_t ldx, const uint8_t* mask, int64_t ld_mask, float keep_scale,
-                               const void* A, int32_t a_kmajor, float scale, int32_t r, int64_t M, int64_t K, void* t32,
-                               void* t16, void* stream) {
+                               const void* A, float scale, int32_t r, int64_t M, int64_t K, void* t32, void* t16,
+                               void* stream) {
   using namespace nf4ll;
   if (r != 16) { set_detail("nf4ll_lora_down: rank %d", r); return NF4LL_ERR_RANK; }
   if (!x || !A) { set_detail("nf4ll_lora_down: null pointer"); return NF4LL_ERR_NULL; }
@@ -171,7 +270,7 @@ extern "C" int nf4ll_lora_down(const void* x, int64_t ldx, const uint8_t* mask, 
     return NF4LL_ERR_ALIGN;
   }
   if (int rc = require_sm100()) return rc;
-  return lora_down_launch(x, ldx, mask, ld_mask, keep_scale, A, a_kmajor, scale, M, K, t32, t16, static_cast<cudaStream_t>(stream));
+  return lora_down_launch(x, ldx, mask, ld_mask, keep_scale, A, 1.0f, scale, M, K, t32, t16, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int nf4ll_lora_grads(const void* dy, int64_t lddy, const void* x, int64_t ldx, const uint8_t* mask,
@@ -181,39 +280,29 @@ extern "C" int nf4ll_lora_grads(const void* dy, int64_t lddy, const void* x, int
   using namespace nf4ll;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   if (r != 16) { set_detail("nf4ll_lora_grads: rank %d", r); return NF4LL_ERR_RANK; }
-  if (M < 0 || N <= 0 || K <= 0 || (N & 1) || (K & 1)) {
-    set_detail("nf4ll_lora_grads: M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
+  if (M < 0 || N <= 0 || K <= 0 || (N % 8) || (K % 8)) {
+    set_detail("nf4ll_lora_grads: M=%lld N=%lld K=%lld (N, K multiples of 8)", (long long)M, (long long)N, (long long)K);
     return NF4LL_ERR_SHAPE;
   }
   if (dA && (!x || !u32)) { set_detail("nf4ll_lora_grads: dA needs x and u"); return NF4LL_ERR_NULL; }
   if (dB && (!dy || !t32)) { set_detail("nf4ll_lora_grads: dB needs dy and t"); return NF4LL_ERR_NULL; }
-  if ((dA && ((reinterpret_cast<uintptr_t>(x) & 3) || (ldx & 1))) || (dB && ((reinterpret_cast<uintptr_t>(dy) & 3) || (lddy & 1)))) {
-    set_detail("nf4ll_lora_grads: activations must be 4-byte aligned with even leading dimensions");
+  if ((dA && ((reinterpret_cast<uintptr_t>(x) & 15) || (ldx % 8))) || (dB && ((reinterpret_cast<uintptr_t>(dy) & 15) || (lddy % 8))) ||
+      (dA && mask && ((reinterpret_cast<uintptr_t>(mask) & 15) || ld_mask % 16))) {
+    set_detail("nf4ll_lora_grads: activations 16-byte aligned with leading dimensions multiples of 8; mask 16-byte aligned, ld_mask multiple of 16");
     return NF4LL_ERR_ALIGN;
   }
   if (int rc = require_sm100()) return rc;
-  const unsigned row_chunks = static_cast<unsigned>((M + kGradRows - 1) / kGradRows);
   if (dA) {
     if (!accumulate) NF4LL_CUDA(cudaMemsetAsync(dA, 0, sizeof(float) * 16 * K, stream));
-    if (M > 0) {
-      dim3 grid(static_cast<unsigned>((K / 2 + kGradThreads - 1) / kGradThreads), row_chunks);
-      // dA = u^T . drop(x); u already carries the LoRA scale (reference solution/fast_qwen.py:1370-1371)
-      lora_grad_kernel<<<grid, kGradThreads, 0, stream>>>(static_cast<const __half*>(x), ldx, mask, ld_mask, keep_scale,
-                                                          static_cast<const float*>(u32), 1.0f, M, K,
-                                                          static_cast<float*>(dA), K, 1);
-      NF4LL_CUDA(cudaGetLastError());
-    }
+    // dA = u^T . drop(x); u already carries the LoRA scale (reference solution/fast_qwen.py:1370-1371)
+    if (M > 0)
+      if (int rc = lora_grad_launch(x, ldx, mask, ld_mask, keep_scale, u32, 1.0f, M, K, dA, K, 1, stream)) return rc;
   }
   if (dB) {
     if (!accumulate) NF4LL_CUDA(cudaMemsetAsync(dB, 0, sizeof(float) * 16 * N, stream));
-    if (M > 0) {
-      dim3 grid(static_cast<unsigned>((N / 2 + kGradThreads - 1) / kGradThreads), row_chunks);
-      // dB = scale * dy^T . t (reference solution/fast_qwen.py:1369)
-      lora_grad_kernel<<<grid, kGradThreads, 0, stream>>>(static_cast<const __half*>(dy), lddy, nullptr, 0, 1.0f,
-                                                          static_cast<const float*>(t32), scale, M, N,
-                                                          static_cast<float*>(dB), 1, 16);
-      NF4LL_CUDA(cudaGetLastError());
-    }
+    // dB = scale * dy^T . t (reference solution/fast_qwen.py:1369)
+    if (M > 0)
+      if (int rc = lora_grad_launch(dy, lddy, nullptr, 0, 1.0f, t32, scale, M, N, dB, 1, 16, stream)) return rc;
   }
   return NF4LL_OK;
 }

@@ -90,7 +90,10 @@ def check_status(device=None):
 def _lora_struct(lora, mask, keep_scale):
     if lora is None:
         return None, None
-    A16, B16, scale = lora
+    A16, B16, scale = lora[:3]
+    Bt = lora[3] if len(lora) > 3 else None
+    if Bt is not None and (Bt.dtype != torch.float16 or not Bt.is_contiguous() or Bt.shape != (A16.shape[0], B16.shape[0])):
+        raise ValueError("transposed lora_B shadow must be contiguous fp16 [16, N]")
     if A16.dtype != torch.float16 or B16.dtype != torch.float16:
         raise ValueError("LoRA shadows must be fp16")
     if not (A16.is_contiguous() and B16.is_contiguous()):
@@ -100,7 +103,7 @@ def _lora_struct(lora, mask, keep_scale):
             raise ValueError("mask must be uint8/bool with unit inner stride")
     s = _lib.LoraArgs(A16.data_ptr(), B16.data_ptr(), int(A16.shape[0]), float(scale),
                       0 if mask is None else mask.data_ptr(), 0 if mask is None else mask.stride(0),
-                      float(keep_scale))
+                      float(keep_scale), 0 if Bt is None else Bt.data_ptr())
     return s, ctypes.byref(s)
 
 
@@ -111,7 +114,8 @@ def _check_act(t, cols, what):
 
 def forward(w: Nf4Weight, x, bias=None, lora=None, mask=None, keep_scale=1.0, out=None, want_t=False,
             workspace=None):
-    """y = x . W^T (+ bias) + scale * (drop(x) . A^T) . B^T. `lora` = (A16 [16,K], B16 [N,16], scale).
+    """y = x . W^T (+ bias) + scale * (drop(x) . A^T) . B^T. `lora` = (A16 [16,K], B16 [N,16], scale) or
+    (A16, B16, scale, B16t [16,N]) when the caller keeps a transposed shadow of lora_B for the backward.
     Returns (y, t) with t = drop(x) . A^T in fp32 [M,16] when want_t, else None."""
     _check_act(x, w.K, "x")
     M = x.shape[0]
@@ -224,3 +228,29 @@ def nf4_lora_linear(x, w: Nf4Weight, bias=None, lora=None, mask=None, keep_scale
     A and B ordinary parameters: they receive fp32 gradients; W is frozen (no dW)."""
     A, B, scale = (None, None, 1.0) if lora is None else lora
     return _Nf4LoraLinearFn.apply(x, A, B, w, bias, scale, mask, keep_scale)
+
+
+def swiglu_forward(g, u, out=None):
+    """h = fp16(silu(g) * u) in fp32 math (reference solution/k_mlp.py:21-29)."""
+    M, I = g.shape
+    _check_act(g, I, "g")
+    _check_act(u, I, "u")
+    h = torch.empty(M, I, dtype=torch.float16, device=g.device) if out is None else out
+    _check_act(h, I, "h")
+    _lib.check(_lib.lib().nf4ll_swiglu_forward(g.data_ptr(), g.stride(0), u.data_ptr(), u.stride(0), h.data_ptr(),
+                                               h.stride(0), M, I, _lib.current_stream(g.device)))
+    return h
+
+
+def swiglu_backward(g, u, dh, inplace=True):
+    """(dg, du) from dh; with inplace=True they overwrite g and u, as the reference overwrites its
+    fused [gate | up] buffer (solution/k_mlp.py:32-47)."""
+    M, I = g.shape
+    for t, name in ((g, "g"), (u, "u"), (dh, "dh")):
+        _check_act(t, I, name)
+    dg = g if inplace else torch.empty_like(g)
+    du = u if inplace else torch.empty_like(u)
+    _lib.check(_lib.lib().nf4ll_swiglu_backward(g.data_ptr(), g.stride(0), u.data_ptr(), u.stride(0), dh.data_ptr(),
+                                                dh.stride(0), dg.data_ptr(), dg.stride(0), du.data_ptr(), du.stride(0),
+                                                M, I, _lib.current_stream(g.device)))
+    return dg, du

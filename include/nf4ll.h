@@ -63,6 +63,8 @@ typedef struct nf4ll_lora {
   const uint8_t* mask;    /* [M, ld_mask] or NULL */
   int64_t ld_mask;
   float keep_scale;
+  const void* Bt;         /* optional __half [r,N]: lora_B transposed, read by nf4ll_backward_dx; when NULL
+                             the call transposes B into its workspace first */
 } nf4ll_lora;
 
 int nf4ll_version(void);
@@ -111,13 +113,12 @@ int nf4ll_backward_dx(const nf4ll_mat* W, const void* dy, int64_t lddy, const nf
                       void* u_out, int64_t M, void* dx, int64_t lddx, int32_t accumulate,
                       void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
 
-/* Rank-r projection on its own:  t32[M,r] = drop(x)[M,K] . A^T  and  t16 = fp16(scale * t32).
- * a_kmajor = 1: A is [r,K] row-major (lora_A);  0: A is [K,r] row-major (lora_B, for u = dy . B),
- * and then t32 carries the scale too (u = scale * dy . B, as the reference's `daq`).
- * Replaces solution/fast_qwen.py:943-944 and 1370/1373. Either output may be NULL.
- * mask, when given, must be 16-byte aligned with ld_mask a multiple of 16. */
+/* Rank-r projection on its own:  t32[M,r] = drop(x)[M,K] . A^T  and  t16 = fp16(scale * t32), with A
+ * [r,K] row-major fp16 (lora_A; or lora_B transposed, to get dy . B). A small tensor-core GEMM that
+ * streams x once. Replaces solution/fast_qwen.py:943-944 and 1370/1373. Either output may be NULL.
+ * K a multiple of 8; mask, when given, 16-byte aligned with ld_mask a multiple of 16. */
 int nf4ll_lora_down(const void* x, int64_t ldx, const uint8_t* mask, int64_t ld_mask,
-                    float keep_scale, const void* A, int32_t a_kmajor, float scale, int32_t r,
+                    float keep_scale, const void* A, float scale, int32_t r,
                     int64_t M, int64_t K, void* t32, void* t16, void* stream);
 
 /* LoRA gradients, fp32:  dA[r,K] (+)= u^T . drop(x),   dB[N,r] (+)= scale * dy^T . t
@@ -129,6 +130,17 @@ int nf4ll_lora_grads(const void* dy, int64_t lddy, const void* x, int64_t ldx, c
                      int64_t ld_mask, float keep_scale, const void* t32, const void* u32,
                      float scale, int32_t r, int64_t M, int64_t N, int64_t K,
                      void* dA, void* dB, int32_t accumulate, void* stream);
+
+/* SiLU-gated product between the up and down projections, fp32 math on fp16 matrices [M,I]:
+ *   h = fp16(silu(g) * u);   backward: du = dh * silu(g), dg = (dh * u) * sig * (1 + g * (1 - sig)).
+ * Same arithmetic as the reference's gated_silu_fwd/bwd kernels (solution/k_mlp.py:21-47), which is
+ * the step between two calls of this library in an MLP block. dg / du may alias g / u.
+ * I a multiple of 8; pointers 16-byte aligned; leading dimensions multiples of 8. */
+int nf4ll_swiglu_forward(const void* g, int64_t ldg, const void* u, int64_t ldu, void* h, int64_t ldh,
+                         int64_t M, int64_t I, void* stream);
+int nf4ll_swiglu_backward(const void* g, int64_t ldg, const void* u, int64_t ldu, const void* dh,
+                          int64_t lddh, void* dg, int64_t lddg, void* du, int64_t lddu, int64_t M,
+                          int64_t I, void* stream);
 
 /* Synchronise `stream`, copy the device status word to the host and return NF4LL_OK or
  * NF4LL_ERR_DEVICE_WAIT (detail string carries the raw word). */

@@ -52,7 +52,7 @@ def test_validation_needs_no_gpu(handle):
         _lib.check(-12)
     with pytest.raises(_lib.Nf4llError):
         _lib.check(-21)
-    assert handle.nf4ll_lora_down(16, 64, None, 0, 1.0, 16, 1, 2.0, 8, 4, 64, None, None, None) == -13
+    assert handle.nf4ll_lora_down(16, 64, None, 0, 1.0, 16, 2.0, 8, 4, 64, None, None, None) == -13
 
 
 def test_workspace_bytes_plan(handle):

@@ -151,3 +151,41 @@ def test_rejects_bad_arguments():
         linear.forward(d.w, d.x, lora=(d.A16[:8], d.B16[:, :8].contiguous(), 2.0))      # rank 8
     with pytest.raises(ValueError):
         linear.forward(d.w, d.x, workspace=torch.empty(16, dtype=torch.uint8, device="cuda"), lora=d.lora)
+
+
+def test_swiglu_kernels_match_fp32_reference():
+    """The gated-SiLU glue between up and down against a plain PyTorch fp32 statement of the
+    reference's arithmetic (solution/k_mlp.py:21-47); fp16 outputs, so tolerance is one fp16 ulp."""
+    gen = torch.Generator().manual_seed(3)
+    M, I = 77, 8960
+    g = (torch.randn(M, I, generator=gen) * 2).half().cuda()
+    u = torch.randn(M, I, generator=gen).half().cuda()
+    dh = torch.randn(M, I, generator=gen).half().cuda()
+    h = linear.swiglu_forward(g, u)
+    gf, uf, df = g.float(), u.float(), dh.float()
+    sig = torch.sigmoid(gf)
+    torch.testing.assert_close(h.float(), (gf * sig * uf).half().float(), atol=2e-3, rtol=2e-3)
+    dg, du = linear.swiglu_backward(g, u, dh, inplace=False)
+    torch.testing.assert_close(du.float(), (df * gf * sig).half().float(), atol=2e-3, rtol=2e-3)
+    torch.testing.assert_close(dg.float(), (df * uf * sig * (1 + gf * (1 - sig))).half().float(), atol=2e-3, rtol=2e-3)
+    g2, u2 = g.clone(), u.clone()
+    linear.swiglu_backward(g2, u2, dh, inplace=True)
+    assert torch.equal(g2, dg) and torch.equal(u2, du)
+
+
+def test_mlp_block_fused_glue_matches_pytorch_glue():
+    from decentrik_prime_b200 import blocks
+    outs = []
+    for fused in (True, False):
+        blk = blocks.MlpBlock(256, 512, seed=9, device=torch.device("cuda"), fused_glue=fused)
+        gen = torch.Generator().manual_seed(1)
+        x = torch.randn(200, 256, generator=gen).half().cuda()
+        dy = torch.randn(200, 256, generator=gen).half().cuda()
+        masks = [(torch.rand(200, k, generator=gen) >= 0.05).to(torch.uint8).cuda() for k in (256, 256, 512)]
+        y = blk.forward(x, masks, 1.0 / 0.95)
+        dx = blk.backward(dy)
+        outs.append((y.float(), dx.float(), blk.down.dA.clone(), blk.gate.dB.clone()))
+    linear.check_status()
+    for a, b in zip(*outs):
+        err, rel = nf4_oracle.errors(a, b)
+        assert rel <= 2e-3, (err, rel)
