@@ -9,12 +9,14 @@
 // solution/k_norm.py:64-71). No fp16 copy of W is ever written to global memory.
 //
 // One CTA computes a (BM_TILES*128) x BN output tile. Roles by warp:
-//   warp 0        TMA producer: 128x64 fp16 activation boxes (128-byte swizzle) into a ring
+//   warp 0        TMA producer: 128x64 fp16 activation boxes (128-byte swizzle) and the tile's packed
+//                 4-bit codes (BN quantisation blocks x 32 bytes) into shared-memory rings
 //   warp 1        allocates tensor memory; one lane issues every tcgen05.mma and commit
-//   warps 2-3     stage the two rank-16 LoRA operands in shared memory (canonical no-swizzle layout)
+//   warps 2-3     stage the two rank-16 LoRA operands (canonical no-swizzle layout), then recover the
+//                 fp32 absmax of every block of each stage (code2[q] * scale2 + offset2) into shared memory
 //   warps 4..     BN threads: each owns one 64-weight quantisation block per ring stage: 2 x 128-bit
-//                 loads of codes, block table in registers, 8 x 128-bit swizzled shared stores;
-//                 afterwards the same warps drain tensor memory (epilogue)
+//                 shared loads of codes, block table in registers, 8 x 128-bit swizzled shared
+//                 stores; afterwards the same warps drain tensor memory (epilogue)
 // The weight tile in shared memory is the same in both directions: rows of 64 consecutive weights of
 // one W row (= one quantisation block, 128 bytes), 8 rows per 1024-byte swizzle atom. Forward reads
 // it as a K-major B operand (contraction along the row), backward as an MN-major one (contraction
@@ -52,21 +54,28 @@ struct GemmParams {
   int* counters;           // one per output tile when splits > 1 (zero on entry, zero on exit)
   int64_t m_pad;
   int32_t* status;
+  int debug;               // timing experiments only: bit 0 skips the decode, bit 1 skips the MMAs
 };
 
 template <int BM_TILES, int BN>
 struct TileCfg {
-  static constexpr int kStages = (BM_TILES == 2 && BN == 256) ? 3 : 4;
+  static constexpr int kStages = (BN == 256) ? 3 : 4;
   static constexpr int kDequantWarps = BN / 32;
   static constexpr int kThreads = 32 * (4 + kDequantWarps);
   static constexpr int kABytes = BM_TILES * 128 * 128;   // per stage: 128 rows x 64 fp16 per M tile
-  static constexpr int kBBytes = BN * 128;               // per stage: BN quantisation blocks
+  static constexpr int kBBytes = BN * 128;               // per stage: BN dequantised quantisation blocks
+  static constexpr int kNibBytes = BN * 32;              // per stage: their packed codes
+  static constexpr int kAbsBytes = BN * 4;               // per stage: their fp32 absmax
   static constexpr int kLoraLeftBytes = BM_TILES * 128 * 32;
   static constexpr int kLoraRightBytes = BN * 32;
   static constexpr int kTmemCols = BM_TILES * BN;        // 128, 256 or 512: a power of two >= 32
-  static constexpr int kSmemBytes = 1024 /* alignment slack */ + kStages * (kABytes + kBBytes) + kLoraLeftBytes +
-                                    kLoraRightBytes + 1024 /* code2 */ + 256 /* barriers */;
+  static constexpr int kSmemBytes = 1024 /* alignment slack */ + kStages * (kABytes + kBBytes + kNibBytes + kAbsBytes) +
+                                    1024 /* code2 */ + 512 /* barriers */;
+  // the LoRA operands are only read by the very first MMAs: they borrow the last activation stage
+  static_assert(kLoraLeftBytes + kLoraRightBytes <= kABytes, "LoRA operands must fit one activation stage");
 };
+
+constexpr int kFixSlots = 8;     // 16 KB slots of the split-K fix-up ring (fits every tile shape's operand rings)
 
 struct Abort {
   volatile int* flag;
@@ -83,19 +92,33 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, con
   return false;
 }
 
-// Decode one quantisation block (32 bytes of codes) into one 128-byte row of a 128B-swizzled tile.
-__device__ __forceinline__ void dequant_block_to_smem(uint8_t* row_base, int key, uint4 c0, uint4 c1, float absmax) {
+__device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+
+// Decode one quantisation block (32 bytes of codes) into one 128-byte row of a 128B-swizzled tile
+// (row_addr: shared-memory address of the row; key: row index modulo 8).
+__device__ __forceinline__ void dequant_block_to_smem(uint32_t row_addr, int key, const uint4& c0, const uint4& c1, float absmax) {
   const BlockTable t = make_block_table(absmax);
   const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    *reinterpret_cast<uint4*>(row_base + ((j ^ key) << 4)) = decode_word(t, w[j]);
-  }
+  for (int j = 0; j < 8; ++j) sts128(row_addr + ((j ^ key) << 4), decode_word(t, w[j]));
 }
 
 template <int MODE, int BM_TILES, int BN>
 __global__ void __launch_bounds__(TileCfg<BM_TILES, BN>::kThreads, 1)
-nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const GemmParams p) {
+nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_constant__ CUtensorMap tmap_nib,
+                const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
   using Cfg = TileCfg<BM_TILES, BN>;
   constexpr int S = Cfg::kStages;
   constexpr int NDW = Cfg::kDequantWarps;
@@ -104,19 +127,27 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const GemmParams p
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;                                   // [S][BM_TILES][128 rows][128 B]
   uint8_t* sB = sA + S * Cfg::kABytes;                  // [S][BN rows][128 B]
-  uint8_t* sLL = sB + S * Cfg::kBBytes;                 // LoRA left operand  [BM_TILES][128 x 16]
-  uint8_t* sLR = sLL + Cfg::kLoraLeftBytes;             // LoRA right operand [BN x 16] or [16 x BN]
-  float* sCode2 = reinterpret_cast<float*>(sLR + Cfg::kLoraRightBytes);
+  uint8_t* sNib = sB + S * Cfg::kBBytes;                // [S][BN blocks][32 B] packed codes
+  uint8_t* sAbs = sNib + S * Cfg::kNibBytes;            // [S][BN] fp32 absmax
+  float* sCode2 = reinterpret_cast<float*>(sAbs + S * Cfg::kAbsBytes);
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sCode2) + 1024);
+  uint8_t* sLL = sA + (S - 1) * Cfg::kABytes;           // LoRA left operand  [BM_TILES][128 x 16] (borrowed stage)
+  uint8_t* sLR = sLL + Cfg::kLoraLeftBytes;             // LoRA right operand [BN x 16] or [16 x BN]
   // barrier slots
-  uint64_t* full_a = bars;            // [S] TMA bytes landed
+  uint64_t* full_a = bars;            // [S] activation boxes landed
   uint64_t* full_b = bars + S;        // [S] dequantised tile written (one arrive per dequant warp)
   uint64_t* empty = bars + 2 * S;     // [S] MMAs that read the stage have completed
-  uint64_t* lora_full = bars + 3 * S;
+  uint64_t* nib_full = bars + 3 * S;  // [S] packed codes landed and absmax written
+  uint64_t* nib_empty = bars + 4 * S; // [S] dequant warps have read codes and absmax
+  uint64_t* lora_full = bars + 5 * S;
   uint64_t* acc_full = lora_full + 1;
   uint64_t* pre_full = lora_full + 2;
   uint64_t* pre_done = lora_full + 3;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(lora_full + 4);
+  uint64_t* lora_done = lora_full + 4;
+  uint64_t* fix_go = lora_full + 5;
+  uint64_t* fx_full = lora_full + 6;              // [kFixSlots] split-K fix-up ring
+  uint64_t* fx_empty = fx_full + kFixSlots;       // [kFixSlots]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fx_empty + kFixSlots);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* last_flag = abort_flag + 1;
 
@@ -141,6 +172,14 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const GemmParams p
       mbar_init(smem_u32(full_a + s), 1);
       mbar_init(smem_u32(full_b + s), NDW);
       mbar_init(smem_u32(empty + s), 1);
+      mbar_init(smem_u32(nib_full + s), 3);        // TMA expect_tx arrive + the two absmax warps
+      mbar_init(smem_u32(nib_empty + s), NDW);
+    }
+    mbar_init(smem_u32(lora_done), 1);
+    mbar_init(smem_u32(fix_go), 1);
+    for (int i = 0; i < kFixSlots; ++i) {
+      mbar_init(smem_u32(fx_full + i), 1);
+      mbar_init(smem_u32(fx_empty + i), NDW);
     }
     mbar_init(smem_u32(lora_full), 2);
     mbar_init(smem_u32(acc_full), 1);
@@ -164,22 +203,59 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const GemmParams p
     // ----------------------------------------------------------------------------- TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tmap_act);
+      tma_prefetch_desc(&tmap_nib);
       int issued = 0;
       for (int i = 0; i < nkb; ++i, ++issued) {
         const int s = i % S;
-        if (!wait_or_abort(smem_u32(empty + s), ((i / S) & 1) ^ 1, ab, 0x0101)) break;
+        const uint32_t free_parity = ((i / S) & 1) ^ 1;
+        const int kb = kb_begin + i;
+        // packed codes first (the dequant warps need them a whole stage before the MMA needs anything)
+        if (!wait_or_abort(smem_u32(nib_empty + s), free_parity, ab, 0x0102)) break;
+        mbar_arrive_expect_tx(smem_u32(nib_full + s), Cfg::kNibBytes);
+        if (MODE == kFwd) {
+          tma_load_2d(smem_u32(sNib + s * Cfg::kNibBytes), &tmap_nib, kb * 32, static_cast<int>(o0), smem_u32(nib_full + s));
+        } else {
+          tma_load_2d(smem_u32(sNib + s * Cfg::kNibBytes), &tmap_nib, static_cast<int>(o0 / 2), kb * 64, smem_u32(nib_full + s));
+        }
+        if (!wait_or_abort(smem_u32(empty + s), free_parity, ab, 0x0101)) break;
+        if (lora_here && i == S - 1) {
+          // the last activation stage is lent to the LoRA operands until the rank-16 MMAs have read them
+          if (!wait_or_abort(smem_u32(lora_done), 0, ab, 0x0103)) break;
+        }
         mbar_arrive_expect_tx(smem_u32(full_a + s), Cfg::kABytes);
 #pragma unroll
         for (int mt = 0; mt < BM_TILES; ++mt) {
-          tma_load_2d(smem_u32(sA + s * Cfg::kABytes + mt * 16384), &tmap_act, (kb_begin + i) * 64,
+          tma_load_2d(smem_u32(sA + s * Cfg::kABytes + mt * 16384), &tmap_act, kb * 64,
                       static_cast<int>(m0 + mt * 128), smem_u32(full_a + s));
+        }
+      }
+      if (p.splits > 1 && !*abort_flag && !(p.debug & 4)) {
+        // split-K: if this CTA turns out to be the last of its tile, stream all slabs back in
+        if (wait_or_abort(smem_u32(fix_go), 0, ab, 0x0104) && *last_flag) {
+          fence_proxy_async_all();     // the other splits' slab writes were observed through ordinary loads / atomics
+          int n = 0;
+          bool fine = true;
+          for (int mt = 0; fine && mt < BM_TILES; ++mt) {
+            for (int cb = 0; fine && cb < BN / 32; ++cb) {
+              const int64_t col0 = o0 + cb * 32;
+              if (col0 >= p.NO) break;
+              for (int sp = 0; sp < p.splits; ++sp, ++n) {
+                const int slot = n % kFixSlots;
+                if (!wait_or_abort(smem_u32(fx_empty + slot), ((n / kFixSlots) & 1) ^ 1, ab, 0x0105)) { fine = false; break; }
+                mbar_arrive_expect_tx(smem_u32(fx_full + slot), 16384);
+                tma_load_2d(smem_u32(smem) + slot * 16384, &tmap_out, static_cast<int>(col0),
+                            static_cast<int>(static_cast<int64_t>(sp) * p.m_pad + m0 + mt * 128), smem_u32(fx_full + slot));
+              }
+            }
+          }
         }
       }
       if (*abort_flag) {
         // give copies still in flight a bounded chance to land before the CTA goes away
-        for (int i = (issued > S ? issued - S : 0); i < issued; ++i) {
-          const uint32_t bar = smem_u32(full_a + (i % S)), ph = (i / S) & 1;
-          for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(bar, ph); ++spin) {}
+        for (int i = (issued > S ? issued - S : 0); i <= issued && i < nkb; ++i) {
+          const uint32_t ph = (i / S) & 1;
+          for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(smem_u32(full_a + (i % S)), ph); ++spin) {}
+          for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(smem_u32(nib_full + (i % S)), ph); ++spin) {}
         }
       }
     }
@@ -200,6 +276,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const GemmParams p
             const uint64_t ldesc = make_smem_desc(smem_u32(sLL + mt * 4096), 128, 256, kSwizzleNone);
             tc_mma_f16(tmem_base + mt * BN, ldesc, rdesc, idesc_main, 0u);
           }
+          tc_commit(smem_u32(lora_done));     // the borrowed activation stage may be overwritten after this
           if (premask) {
             tc_commit(smem_u32(pre_full));
             ok = wait_or_abort(smem_u32(pre_done), 0, ab, 0x0202);
@@ -226,7 +303,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const GemmParams p
 #pragma unroll
           for (int mt = 0; mt < BM_TILES; ++mt) {
             const uint64_t adesc = make_smem_desc(a_base + mt * 16384 + kk * 32, 16, 1024, kSwizzle128B);
-            tc_mma_f16(tmem_base + mt * BN, adesc, bdesc, idesc_main, (lora_here || i > 0 || kk > 0) ? 1u : 0u);
+            if (!(p.debug & 2)) tc_mma_f16(tmem_base + mt * BN, adesc, bdesc, idesc_main, (lora_here || i > 0 || kk > 0) ? 1u : 0u);
           }
         }
         tc_commit(smem_u32(empty + s));     // frees the stage once these MMAs have read it
@@ -269,6 +346,56 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const GemmParams p
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(lora_full));
+    }
+    // absmax of the stage's BN quantisation blocks: code2[q] * scale2 + offset2, rounded separately
+    {
+      constexpr int PER = BN / 64;                 // blocks per helper thread
+      const int t = threadIdx.x - 64;
+      int64_t qb[PER], qstep;
+#pragma unroll
+      for (int e = 0; e < PER; ++e) {
+        const int d = t + e * 64;
+        if (MODE == kFwd) {
+          int64_t n = o0 + d;
+          if (n >= p.N) n = p.N - 1;               // tail rows: any valid block; their output is never stored
+          qb[e] = (n * p.K) / 64 + kb_begin;
+        } else {
+          constexpr int SUB = BN / 64;
+          const int j = d % SUB, r = d / SUB;
+          int64_t kcol = o0 + j * 64;
+          if (kcol >= p.K) kcol = 0;
+          qb[e] = ((static_cast<int64_t>(kb_begin) * 64 + r) * p.K + kcol) / 64;
+        }
+      }
+      qstep = (MODE == kFwd) ? 1 : p.K;
+      uint32_t qc[PER];
+      float s2[PER], o2[PER];
+#pragma unroll
+      for (int e = 0; e < PER; ++e) {
+        qc[e] = 0; s2[e] = 0.f; o2[e] = 0.f;
+        if (nkb > 0) { qc[e] = __ldg(p.qabs + qb[e]); s2[e] = __ldg(p.scale2 + (qb[e] >> 8)); o2[e] = __ldg(p.offset2 + (qb[e] >> 8)); }
+      }
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % S;
+        uint32_t nq[PER];
+        float ns2[PER], no2[PER];
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {          // next stage's codes and scales, in flight during this stage
+          nq[e] = qc[e]; ns2[e] = s2[e]; no2[e] = o2[e];
+          if (i + 1 < nkb) {
+            const int64_t nb = qb[e] + qstep;
+            nq[e] = __ldg(p.qabs + nb); ns2[e] = __ldg(p.scale2 + (nb >> 8)); no2[e] = __ldg(p.offset2 + (nb >> 8));
+          }
+        }
+        if (!wait_or_abort(smem_u32(nib_empty + s), ((i / S) & 1) ^ 1, ab, 0x0401)) break;
+        float* dst = reinterpret_cast<float*>(sAbs + s * Cfg::kAbsBytes);
+#pragma unroll
+        for (int e = 0; e < PER; ++e) dst[t + e * 64] = block_absmax(sCode2[qc[e]], s2[e], o2[e]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(nib_full + s));
+#pragma unroll
+        for (int e = 0; e < PER; ++e) { qc[e] = nq[e]; s2[e] = ns2[e]; o2[e] = no2[e]; qb[e] += qstep; }
+      }
     }
   } else {
     // ----------------------------------------------------------------------------- dequant, then epilogue
@@ -315,111 +442,138 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const GemmParams p
     }
 
     // --- dequantise one block per stage
-    int64_t byte_off, qb, byte_step, qb_step;
-    uint8_t* row_off_base;       // offset of this thread's 128-byte row inside a B stage
+    uint32_t nib_off, row_off;     // this thread's 32 bytes of codes / 128-byte output row inside a stage
     int key;
     if (MODE == kFwd) {
-      int64_t n = o0 + d;
-      if (n >= p.N) n = p.N - 1;                       // tail rows decode valid memory; never stored
-      const int64_t e = n * p.K + static_cast<int64_t>(kb_begin) * 64;
-      byte_off = e >> 1; qb = e >> 6; byte_step = 32; qb_step = 1;
-      row_off_base = sB + d * 128;
+      nib_off = d * 32;
+      row_off = d * 128;
       key = d & 7;
     } else {
       constexpr int SUB = BN / 64;
       const int j = d % SUB, r = d / SUB;              // sub-tile (64 output columns) and row in the stage
-      int64_t kcol = o0 + j * 64;
-      if (kcol >= p.K) kcol = 0;
-      const int64_t e = (static_cast<int64_t>(kb_begin) * 64 + r) * p.K + kcol;
-      byte_off = e >> 1; qb = e >> 6; byte_step = 32 * p.K; qb_step = p.K;
-      row_off_base = sB + j * 8192 + r * 128;
+      nib_off = r * (BN / 2) + j * 32;
+      row_off = j * 8192 + r * 128;
       key = r & 7;
     }
-    uint4 c0 = make_uint4(0, 0, 0, 0), c1 = c0;
-    uint32_t qcode = 0;
-    float s2 = 0.f, o2 = 0.f;
-    if (nkb > 0) {
-      const uint4* src = reinterpret_cast<const uint4*>(p.nib + byte_off);
-      c0 = __ldg(src); c1 = __ldg(src + 1);
-      qcode = __ldg(p.qabs + qb); s2 = __ldg(p.scale2 + (qb >> 8)); o2 = __ldg(p.offset2 + (qb >> 8));
-    }
+    const uint32_t nib_base = smem_u32(sNib) + nib_off, abs_base = smem_u32(sAbs) + d * 4, b_base = smem_u32(sB) + row_off;
     for (int i = 0; ok && i < nkb; ++i) {
       const int s = i % S;
-      // prefetch the next block's codes and scales into registers (latency hidden by this block's decode)
-      uint4 n0 = c0, n1 = c1;
-      uint32_t nq = qcode;
-      float ns2 = s2, no2 = o2;
-      if (i + 1 < nkb) {
-        const int64_t bo = byte_off + byte_step, nqb = qb + qb_step;
-        const uint4* src = reinterpret_cast<const uint4*>(p.nib + bo);
-        n0 = __ldg(src); n1 = __ldg(src + 1);
-        nq = __ldg(p.qabs + nqb); ns2 = __ldg(p.scale2 + (nqb >> 8)); no2 = __ldg(p.offset2 + (nqb >> 8));
-      }
-      if (i + 4 < nkb) {
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.nib + byte_off + 4 * byte_step));
-      }
-      if (!wait_or_abort(smem_u32(empty + s), ((i / S) & 1) ^ 1, ab, 0x0302)) { ok = false; break; }
-      const float absmax = block_absmax(sCode2[qcode], s2, o2);
-      dequant_block_to_smem(row_off_base + s * Cfg::kBBytes, key, c0, c1, absmax);
+      const uint32_t ph = (i / S) & 1;
+      if (!wait_or_abort(smem_u32(nib_full + s), ph, ab, 0x0304)) { ok = false; break; }
+      const uint4 c0 = lds128(nib_base + s * Cfg::kNibBytes), c1 = lds128(nib_base + s * Cfg::kNibBytes + 16);
+      const float absmax = lds_f32(abs_base + s * Cfg::kAbsBytes);
+      if (!wait_or_abort(smem_u32(empty + s), ph ^ 1, ab, 0x0302)) { ok = false; break; }
+      if (!(p.debug & 1)) dequant_block_to_smem(b_base + s * Cfg::kBBytes, key, c0, c1, absmax);
       fence_proxy_async_smem();      // generic-proxy stores -> visible to the tensor core's async proxy
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(full_b + s));
-      c0 = n0; c1 = n1; qcode = nq; s2 = ns2; o2 = no2;
-      byte_off += byte_step; qb += qb_step;
-    }
-
-    // --- epilogue: tensor memory -> registers -> global
-    if (ok) ok = wait_or_abort(smem_u32(acc_full), 0, ab, 0x0303);
-    const bool direct = (p.splits == 1);
-    if (ok) {
-      tc_fence_after();
-      constexpr int kChunks = BM_TILES * (BN / 32);
-      float* slab = direct ? nullptr : p.partial + static_cast<int64_t>(split) * p.m_pad * p.NO;
-      for (int u = ew >> 2; u < kChunks; u += NDW / 4) {
-        const int mt = u / (BN / 32), c = u % (BN / 32);
-        const int64_t row = m0 + mt * 128 + q * 32 + lane;
-        const int64_t col0 = o0 + c * 32;
-        uint32_t v[32];
-        __syncwarp();
-        tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + mt * BN + c * 32, v);
-        tmem_ld_wait();
-        if (direct) {
-          if (row < p.M && col0 < p.NO) {
-            __half* dst = p.out + row * p.ldo + col0;
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              float f[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[g * 8 + j]);
-              if (MODE == kFwd && p.bias) {
-                const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + g * 8));
-                const __half2* bh = reinterpret_cast<const __half2*>(&b);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) { const float2 bf = __half22float2(bh[j]); f[2 * j] += bf.x; f[2 * j + 1] += bf.y; }
-              }
-              if (MODE == kBwd && p.accumulate) {
-                const uint4 o = *reinterpret_cast<const uint4*>(dst + g * 8);
-                const __half2* oh = reinterpret_cast<const __half2*>(&o);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) { const float2 of = __half22float2(oh[j]); f[2 * j] += of.x; f[2 * j + 1] += of.y; }
-              }
-              uint4 o;
-              o.x = pack_half2_rn(f[0], f[1]); o.y = pack_half2_rn(f[2], f[3]);
-              o.z = pack_half2_rn(f[4], f[5]); o.w = pack_half2_rn(f[6], f[7]);
-              *reinterpret_cast<uint4*>(dst + g * 8) = o;
-            }
-          }
-        } else if (col0 < p.NO) {
-          // rows beyond M still fit: the slab has m_pad rows
-          float4* dst = reinterpret_cast<float4*>(slab + row * p.NO + col0);
-#pragma unroll
-          for (int g = 0; g < 8; ++g)
-            dst[g] = make_float4(__uint_as_float(v[4 * g]), __uint_as_float(v[4 * g + 1]), __uint_as_float(v[4 * g + 2]),
-                                 __uint_as_float(v[4 * g + 3]));
-        }
+      if (lane == 0) {
+        mbar_arrive(smem_u32(full_b + s));
+        mbar_arrive(smem_u32(nib_empty + s));      // codes and absmax of this stage are in registers / consumed
       }
     }
-    if (!direct) {
+
+    // --- epilogue: tensor memory -> registers -> swizzled shared staging -> TMA store.
+    // The operand rings are idle once the accumulator is complete, so they serve as staging space:
+    // each group of four warps (one per tensor-memory lane quarter) owns 64 KB of it and drains one
+    // 128-row accumulator at a time in boxes of 128 rows x 128 bytes.
+    if (ok) ok = wait_or_abort(smem_u32(acc_full), 0, ab, 0x0303);
+    const bool direct = (p.splits == 1);
+    if (ok && !(p.debug & 4)) {
+      tc_fence_after();
+      constexpr int G = NDW / 4;                       // warp groups
+      const int grp = ew >> 2;
+      const int bar_id = 2 + grp;
+      const uint32_t stage = smem_u32(smem) + grp * 65536;
+      const int r_in = q * 32 + lane;                  // row inside the 128-row accumulator
+      const uint32_t row_addr = stage + r_in * 128;
+      const int key = r_in & 7;
+      const bool leader = (q == 0 && lane == 0);
+      for (int mt = grp; mt < BM_TILES; mt += G) {
+        const uint32_t tacc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + mt * BN;
+        const int row_g = static_cast<int>(m0 + mt * 128);
+        if (direct) {
+          // fp16 output: boxes of 64 columns
+#pragma unroll 1
+          for (int cb = 0; cb < BN / 64; ++cb) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              const int c = cb * 2 + half;
+              const int64_t col0 = o0 + c * 32;
+              uint32_t v[32];
+              __syncwarp();
+              tmem_ld32(tacc + c * 32, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int g8 = 0; g8 < 4; ++g8) {
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[g8 * 8 + j]);
+                if (MODE == kFwd && p.bias && col0 < p.NO) {
+                  const uint4 bb = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + g8 * 8));
+                  const __half2* bh = reinterpret_cast<const __half2*>(&bb);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) { const float2 bf = __half22float2(bh[j]); f[2 * j] += bf.x; f[2 * j + 1] += bf.y; }
+                }
+                uint4 o;
+                o.x = pack_half2_rn(f[0], f[1]); o.y = pack_half2_rn(f[2], f[3]);
+                o.z = pack_half2_rn(f[4], f[5]); o.w = pack_half2_rn(f[6], f[7]);
+                sts128(row_addr + cb * 16384 + (((half * 4 + g8) ^ key) << 4), o);
+              }
+            }
+          }
+          fence_proxy_async_smem();
+          named_barrier(bar_id, 128);
+          if (leader) {
+            for (int cb = 0; cb < BN / 64; ++cb) {
+              const int64_t col0 = o0 + cb * 64;
+              if (col0 >= p.NO) break;
+              // rows past M and columns past NO are clipped by the tensor map
+              if (MODE == kBwd && p.accumulate) tma_reduce_add_2d(&tmap_out, stage + cb * 16384, static_cast<int>(col0), row_g);
+              else tma_store_2d(&tmap_out, stage + cb * 16384, static_cast<int>(col0), row_g);
+            }
+            bulk_commit();
+            bulk_wait_read_all();
+          }
+          if (mt + G < BM_TILES) named_barrier(bar_id, 128);      // staging is reused by the next accumulator
+        } else {
+          // fp32 partial sums into this split's slab: boxes of 32 columns, four per round
+          const int slab_row = static_cast<int>(static_cast<int64_t>(split) * p.m_pad + m0 + mt * 128);
+#pragma unroll 1
+          for (int round = 0; round < BN / 128; ++round) {
+#pragma unroll 1
+            for (int b4 = 0; b4 < 4; ++b4) {
+              const int c = round * 4 + b4;
+              uint32_t v[32];
+              __syncwarp();
+              tmem_ld32(tacc + c * 32, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                sts128(row_addr + b4 * 16384 + ((j ^ key) << 4), make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+            }
+            fence_proxy_async_smem();
+            named_barrier(bar_id, 128);
+            if (leader) {
+              for (int b4 = 0; b4 < 4; ++b4) {
+                const int64_t col0 = o0 + (round * 4 + b4) * 32;
+                if (col0 >= p.NO) break;
+                tma_store_2d(&tmap_out, stage + b4 * 16384, static_cast<int>(col0), slab_row);
+              }
+              bulk_commit();
+              bulk_wait_read_all();
+            }
+            named_barrier(bar_id, 128);
+          }
+        }
+      }
+      if (!direct && leader) {
+        // the slab must be complete and visible to other CTAs' ordinary loads before the tile counter moves
+        bulk_wait_all();
+        fence_proxy_async_all();
+        __threadfence();
+      }
+    }
+    if (!direct && !(p.debug & 4)) {
       // split-K fix-up: the last CTA of this output tile to finish sums all slabs in split order
       // (deterministic) and writes the fp16 result. Every dequant thread takes both barriers, also
       // after a failed wait, so that nobody is left behind at a barrier.
@@ -430,45 +584,66 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const GemmParams p
         const int prev = atomicAdd(counter, 1);
         if (prev == p.splits - 1) { *last_flag = 1; *counter = 0; }
         __threadfence();
+        mbar_arrive(smem_u32(fix_go));       // tells warp 0 whether to stream the slabs back in
       }
       asm volatile("bar.sync 1, %0;" ::"r"(NDW * 32) : "memory");
       if (*last_flag && !*abort_flag) {
-        // thread d: 8 consecutive columns (c8 = d % (BN/8)), rows strided by NDW*32/(BN/8)
-        constexpr int CPR = BN / 8;                    // 16-byte output chunks per tile row
-        constexpr int RSTEP = (NDW * 32) / CPR;
-        const int c8 = d % CPR;
-        const int64_t col = o0 + c8 * 8;
-        if (col < p.NO) {
-          float bf[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-          if (MODE == kFwd && p.bias) {
-            const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
-            const __half2* bh = reinterpret_cast<const __half2*>(&b);
+        // Warp 0 streams every split's 128-row x 32-column fp32 box of this tile through a ring of
+        // 16 KB shared-memory slots (TMA loads, several in flight); these threads add the boxes up in
+        // split order, then round once to fp16. Thread = one row, CPT consecutive columns of the box.
+        constexpr int PARTS = (NDW * 32) / 128;         // threads per box row
+        constexpr int CPT = 32 / PARTS;                 // columns per thread
+        const int r_in = d & 127, part = d >> 7;
+        const uint32_t ring = smem_u32(smem);
+        int n = 0;
+        bool fine = true;
+        for (int mt = 0; fine && mt < BM_TILES; ++mt) {
+          const int64_t row = m0 + mt * 128 + r_in;
+          for (int cb = 0; fine && cb < BN / 32; ++cb) {
+            const int64_t col = o0 + cb * 32 + part * CPT;
+            if (o0 + cb * 32 >= p.NO) break;
+            float f[CPT];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) { const float2 t2 = __half22float2(bh[j]); bf[2 * j] = t2.x; bf[2 * j + 1] = t2.y; }
-          }
-          for (int r = d / CPR; r < BM_TILES * 128; r += RSTEP) {
-            const int64_t row = m0 + r;
-            if (row >= p.M) break;
-            float f[8];
+            for (int j = 0; j < CPT; ++j) f[j] = 0.f;
+            if (MODE == kFwd && p.bias) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = bf[j];
-            for (int sp = 0; sp < p.splits; ++sp) {
-              const float4* src = reinterpret_cast<const float4*>(p.partial + (static_cast<int64_t>(sp) * p.m_pad + row) * p.NO + col);
-              const float4 a = __ldcg(src), b = __ldcg(src + 1);
-              f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
-              f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+              for (int j8 = 0; j8 < CPT / 8; ++j8) {
+                const uint4 bb = __ldg(reinterpret_cast<const uint4*>(p.bias + col + j8 * 8));
+                const __half2* bh = reinterpret_cast<const __half2*>(&bb);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { const float2 t2 = __half22float2(bh[j]); f[j8 * 8 + 2 * j] = t2.x; f[j8 * 8 + 2 * j + 1] = t2.y; }
+              }
             }
-            __half* dst = p.out + row * p.ldo + col;
-            if (MODE == kBwd && p.accumulate) {
-              const uint4 o = *reinterpret_cast<const uint4*>(dst);
-              const __half2* oh = reinterpret_cast<const __half2*>(&o);
+            for (int sp = 0; sp < p.splits; ++sp, ++n) {
+              const int slot = n % kFixSlots;
+              if (!wait_or_abort(smem_u32(fx_full + slot), (n / kFixSlots) & 1, ab, 0x0305)) { fine = false; break; }
+              const uint32_t src = ring + slot * 16384 + r_in * 128;
 #pragma unroll
-              for (int j = 0; j < 4; ++j) { const float2 of = __half22float2(oh[j]); f[2 * j] += of.x; f[2 * j + 1] += of.y; }
+              for (int j = 0; j < CPT / 4; ++j) {
+                const uint4 v = lds128(src + (((part * (CPT / 4) + j) ^ (r_in & 7)) << 4));
+                f[4 * j] += __uint_as_float(v.x); f[4 * j + 1] += __uint_as_float(v.y);
+                f[4 * j + 2] += __uint_as_float(v.z); f[4 * j + 3] += __uint_as_float(v.w);
+              }
+              __syncwarp();
+              if (lane == 0) mbar_arrive(smem_u32(fx_empty + slot));
             }
-            uint4 o;
-            o.x = pack_half2_rn(f[0], f[1]); o.y = pack_half2_rn(f[2], f[3]);
-            o.z = pack_half2_rn(f[4], f[5]); o.w = pack_half2_rn(f[6], f[7]);
-            *reinterpret_cast<uint4*>(dst) = o;
+            if (fine && row < p.M) {
+              __half* dst = p.out + row * p.ldo + col;
+#pragma unroll
+              for (int j8 = 0; j8 < CPT / 8; ++j8) {
+                float* g8 = f + j8 * 8;
+                if (MODE == kBwd && p.accumulate) {
+                  const uint4 o = *reinterpret_cast<const uint4*>(dst + j8 * 8);
+                  const __half2* oh = reinterpret_cast<const __half2*>(&o);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) { const float2 of = __half22float2(oh[j]); g8[2 * j] += of.x; g8[2 * j + 1] += of.y; }
+                }
+                uint4 o;
+                o.x = pack_half2_rn(g8[0], g8[1]); o.y = pack_half2_rn(g8[2], g8[3]);
+                o.z = pack_half2_rn(g8[4], g8[5]); o.w = pack_half2_rn(g8[6], g8[7]);
+                *reinterpret_cast<uint4*>(dst + j8 * 8) = o;
+              }
+            }
           }
         }
       }
@@ -507,21 +682,43 @@ static int get_encode_fn(EncodeTiledFn* out) {
   return NF4LL_OK;
 }
 
-// 2-D map over a row-major fp16 matrix [rows, cols] with leading dimension ld: boxes of 64 columns
-// (128 bytes, the swizzle span) x 128 rows, zero fill outside.
-static int make_act_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld) {
-  EncodeTiledFn enc;
+// 2-D map over a row-major matrix [rows, cols] with leading dimension ld (elements): boxes of 128
+// rows x 128 bytes (the swizzle span: 64 fp16 or 32 fp32 columns); loads zero-fill outside the
+// matrix, stores are clipped to it.
+static int make_tile_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, bool f32) {
+  EncodeTiledFn enc = nullptr;
   if (int rc = get_encode_fn(&enc)) return rc;
+  const int esz = f32 ? 4 : 2;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-  const cuuint32_t box[2] = {64, 128};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * esz};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / esz), 128};
   const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUresult r = enc(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_detail("cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld cols=%lld ld=%lld)", static_cast<int>(r),
                static_cast<long long>(rows), static_cast<long long>(cols), static_cast<long long>(ld));
+    return NF4LL_ERR_CUDA;
+  }
+  return NF4LL_OK;
+}
+
+// 2-D map over the packed codes of W[N,K] seen as bytes [N, K/2]. Forward boxes: BN rows x 32 bytes
+// (one quantisation block per row); backward boxes: 64 rows x BN/2 bytes. No swizzle, zero fill.
+static int make_nib_map(CUtensorMap* map, const void* nib, int64_t N, int64_t K, int mode, int bn) {
+  EncodeTiledFn enc = nullptr;
+  if (int rc = get_encode_fn(&enc)) return rc;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K / 2), static_cast<cuuint64_t>(N)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K / 2)};
+  const cuuint32_t box[2] = {mode == kFwd ? 32u : static_cast<cuuint32_t>(bn / 2), mode == kFwd ? static_cast<cuuint32_t>(bn) : 64u};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(nib), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_detail("cuTensorMapEncodeTiled (codes) failed with CUresult %d (N=%lld K=%lld)", static_cast<int>(r),
+               static_cast<long long>(N), static_cast<long long>(K));
     return NF4LL_ERR_CUDA;
   }
   return NF4LL_OK;
@@ -535,6 +732,7 @@ struct Plan {
 };
 
 static thread_local int g_force_bm = 0, g_force_bn = 0, g_force_splits = 0;
+static thread_local int g_debug = 0;
 static thread_local cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;
 
 static int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
@@ -579,22 +777,24 @@ static int device_sms(int* sms) {
 }
 
 template <int MODE, int BM_TILES, int BN>
-static int launch_cfg(const CUtensorMap& map, const GemmParams& p, const Plan& pl, cudaStream_t stream) {
+static int launch_cfg(const CUtensorMap& map, const CUtensorMap& nib_map, const CUtensorMap& out_map, const GemmParams& p,
+                      const Plan& pl, cudaStream_t stream) {
   using Cfg = TileCfg<BM_TILES, BN>;
   auto kernel = nf4_gemm_kernel<MODE, BM_TILES, BN>;
   NF4LL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
   dim3 grid(static_cast<unsigned>(pl.tiles_o), static_cast<unsigned>(pl.tiles_m), static_cast<unsigned>(pl.splits));
-  kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map, p);
+  kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map, nib_map, out_map, p);
   NF4LL_CUDA(cudaGetLastError());
   return NF4LL_OK;
 }
 
 template <int MODE>
-static int launch(const CUtensorMap& map, const GemmParams& p, const Plan& pl, cudaStream_t stream) {
-  if (pl.bm_tiles == 2 && pl.bn == 256) return launch_cfg<MODE, 2, 256>(map, p, pl, stream);
-  if (pl.bm_tiles == 1 && pl.bn == 256) return launch_cfg<MODE, 1, 256>(map, p, pl, stream);
-  if (pl.bm_tiles == 2 && pl.bn == 128) return launch_cfg<MODE, 2, 128>(map, p, pl, stream);
-  return launch_cfg<MODE, 1, 128>(map, p, pl, stream);
+static int launch(const CUtensorMap& map, const CUtensorMap& nib_map, const CUtensorMap& out_map, const GemmParams& p,
+                  const Plan& pl, cudaStream_t stream) {
+  if (pl.bm_tiles == 2 && pl.bn == 256) return launch_cfg<MODE, 2, 256>(map, nib_map, out_map, p, pl, stream);
+  if (pl.bm_tiles == 1 && pl.bn == 256) return launch_cfg<MODE, 1, 256>(map, nib_map, out_map, p, pl, stream);
+  if (pl.bm_tiles == 2 && pl.bn == 128) return launch_cfg<MODE, 2, 128>(map, nib_map, out_map, p, pl, stream);
+  return launch_cfg<MODE, 1, 128>(map, nib_map, out_map, p, pl, stream);
 }
 
 static int check_mat(const nf4ll_mat* W, const char* who) {
@@ -678,7 +878,7 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
   p.bias = static_cast<const __half*>(bias);
   p.accumulate = accumulate;
   p.has_lora = lora != nullptr;
-  p.splits = pl.splits; p.m_pad = pl.m_pad; p.status = status;
+  p.splits = pl.splits; p.m_pad = pl.m_pad; p.status = status; p.debug = g_debug;
   if (lora) {
     __half* left = reinterpret_cast<__half*>(ws);
     // rank-16 projection of the activation: T = drop(x).A^T (forward) or U = dy.B (backward)
@@ -707,11 +907,19 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
     NF4LL_CUDA(cudaMemsetAsync(p.counters, 0, pl.counter_bytes, stream));
   }
   CUtensorMap map;
-  if (int rc = make_act_map(&map, act, M, KC, ldact)) return rc;
+  if (int rc = make_tile_map(&map, act, M, KC, ldact, false)) return rc;
+  CUtensorMap out_map;
+  if (pl.splits == 1) {
+    if (int rc = make_tile_map(&out_map, out, M, NO, ldo, false)) return rc;
+  } else {
+    if (int rc = make_tile_map(&out_map, p.partial, static_cast<int64_t>(pl.splits) * pl.m_pad, NO, NO, true)) return rc;
+  }
+  CUtensorMap nib_map;
+  if (int rc = make_nib_map(&nib_map, W->nib, W->N, W->K, mode, pl.bn)) return rc;
   cudaEvent_t ev0 = g_ev_start, ev1 = g_ev_stop;
   g_ev_start = g_ev_stop = nullptr;
   if (ev0) NF4LL_CUDA(cudaEventRecord(ev0, stream));
-  const int rc = mode == kFwd ? launch<kFwd>(map, p, pl, stream) : launch<kBwd>(map, p, pl, stream);
+  const int rc = mode == kFwd ? launch<kFwd>(map, nib_map, out_map, p, pl, stream) : launch<kBwd>(map, nib_map, out_map, p, pl, stream);
   if (rc == NF4LL_OK && ev1) NF4LL_CUDA(cudaEventRecord(ev1, stream));
   return rc;
 }
@@ -759,3 +967,5 @@ extern "C" void nf4ll_kernel_events(void* start, void* stop) {
   nf4ll::g_ev_start = static_cast<cudaEvent_t>(start);
   nf4ll::g_ev_stop = static_cast<cudaEvent_t>(stop);
 }
+
+extern "C" void nf4ll_debug_flags(int32_t flags) { nf4ll::g_debug = flags; }
