@@ -167,7 +167,11 @@ __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bu
 // all committed groups have completed, writes included
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// bar.sync is an ALIGNED barrier: every lane of a warp has to execute it together. Code that lets one
+// elected lane do extra work first (issue a TMA store, wait for it) must therefore reconverge
+// explicitly, or the other lanes' early arrival releases the barrier before the elected lane is done.
 __device__ __forceinline__ void named_barrier(int id, int threads) {
+  __syncwarp();
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 

@@ -195,6 +195,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
     tmem_relinquish();
   }
   tc_fence_before();
+  __syncwarp();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
@@ -578,7 +579,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
       // (deterministic) and writes the fp16 result. Every dequant thread takes both barriers, also
       // after a failed wait, so that nobody is left behind at a barrier.
       __threadfence();
-      asm volatile("bar.sync 1, %0;" ::"r"(NDW * 32) : "memory");
+      named_barrier(1, NDW * 32);
       int* counter = p.counters + (static_cast<int64_t>(tile_m) * gridDim.x + tile_o);
       if (d == 0) {
         const int prev = atomicAdd(counter, 1);
@@ -586,7 +587,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
         __threadfence();
         mbar_arrive(smem_u32(fix_go));       // tells warp 0 whether to stream the slabs back in
       }
-      asm volatile("bar.sync 1, %0;" ::"r"(NDW * 32) : "memory");
+      named_barrier(1, NDW * 32);
       if (*last_flag && !*abort_flag) {
         // Warp 0 streams every split's 128-row x 32-column fp32 box of this tile through a ring of
         // 16 KB shared-memory slots (TMA loads, several in flight); these threads add the boxes up in
@@ -652,6 +653,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
 
   // ------------------------------------------------------------------------------- teardown
   tc_fence_before();
+  __syncwarp();          // single-lane roles (TMA producer, MMA issuer) rejoin their warps first
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();

@@ -1,8 +1,9 @@
 /* nf4ll: NF4-quantised frozen linear layer with a fused LoRA branch, for NVIDIA B200 (sm_100a).
  *
  * C ABI of libnf4ll.so. Every pointer is a DEVICE pointer unless a comment says otherwise; the
- * caller owns every buffer. The library allocates nothing, keeps no pointer after a call returns
- * and has no global mutable state besides a thread-local error-detail string, so it may be called
+ * caller owns every buffer. The library allocates nothing, keeps no caller pointer after a call
+ * returns and has no global mutable state besides thread-local settings (error detail, test hooks)
+ * and the cached address of its built-in scratch (nf4ll_forward_static), so it may be called
  * from several host threads and streams at once. Calls only enqueue work on `stream`
  * (a cudaStream_t passed as void*); nothing synchronises unless a comment says so.
  *
