@@ -971,3 +971,65 @@ extern "C" void nf4ll_kernel_events(void* start, void* stop) {
 }
 
 extern "C" void nf4ll_debug_flags(int32_t flags) { nf4ll::g_debug = flags; }
+
+// ---------------------------------------------------------------------------------------------
+// Forward without a caller-supplied workspace.
+//
+// Some callers cannot hand over scratch memory: a plugin host that forbids device allocations after
+// start-up, an inference server whose memory pool is sealed once its budget is committed, or code
+// that runs where cudaMalloc is illegal. For them the scratch of nf4ll_forward lives in a fixed
+// array in this library's device image. The array exists once per GPU that loads the library (each
+// such GPU gives up NF4LL_STATIC_SCRATCH_BYTES until the process exits), so its size is a
+// compromise: it covers one BASELINE config-0 forward (M = 2048 against a 1536 x 1536 weight with
+// LoRA, including split-K partial sums) and nothing much larger.
+//
+// In host code the array's name is only a handle; the device address is asked from the runtime
+// once per device (with that device current) and cached.
+// ---------------------------------------------------------------------------------------------
+namespace nf4ll {
+
+static __device__ __align__(256) unsigned char g_static_scratch[NF4LL_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+static void* g_static_scratch_addr[kMaxDevices];      // written once per device with the same value by any thread
+
+static int static_scratch_for_current_device(void** out) {
+  int dev = 0;
+  NF4LL_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) {
+    set_detail("nf4ll_forward_static: device index %d is beyond the %d devices this entry point tracks", dev, kMaxDevices);
+    return NF4LL_ERR_SHAPE;
+  }
+  void* ptr = __atomic_load_n(&g_static_scratch_addr[dev], __ATOMIC_ACQUIRE);
+  if (!ptr) {
+    NF4LL_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    if (!ptr || (reinterpret_cast<uintptr_t>(ptr) & 255)) {
+      set_detail("nf4ll_forward_static: runtime returned an unusable address for the built-in scratch");
+      return NF4LL_ERR_CUDA;
+    }
+    __atomic_store_n(&g_static_scratch_addr[dev], ptr, __ATOMIC_RELEASE);
+  }
+  *out = ptr;
+  return NF4LL_OK;
+}
+
+}  // namespace nf4ll
+
+extern "C" int nf4ll_forward_static(const nf4ll_mat* W, const void* x, int64_t ldx, const void* bias,
+                                    const nf4ll_lora* lora, void* t_out, int64_t M, void* y, int64_t ldy, int32_t* status,
+                                    void* stream) {
+  using namespace nf4ll;
+  if (!W) { set_detail("nf4ll_forward_static: null weight"); return NF4LL_ERR_NULL; }
+  const int64_t need = nf4ll_workspace_bytes(M, W->N, W->K, lora ? lora->r : 0);
+  if (need > static_cast<int64_t>(NF4LL_STATIC_SCRATCH_BYTES)) {
+    set_detail("nf4ll_forward_static: this problem needs %lld bytes of scratch, the built-in buffer holds %lld; "
+               "use nf4ll_forward with a workspace of your own",
+               static_cast<long long>(need), static_cast<long long>(NF4LL_STATIC_SCRATCH_BYTES));
+    return NF4LL_ERR_WORKSPACE;
+  }
+  void* scratch = nullptr;
+  if (int rc = static_scratch_for_current_device(&scratch)) return rc;
+  // Whatever the previous call left in the buffer is harmless: the tile counters are cleared on the
+  // stream before every launch that uses them, and every other byte is written before it is read.
+  return run_gemm(kFwd, W, x, ldx, bias, lora, t_out, M, y, ldy, 0, scratch, NF4LL_STATIC_SCRATCH_BYTES, status, stream);
+}

@@ -104,6 +104,24 @@ int nf4ll_forward(const nf4ll_mat* W, const void* x, int64_t ldx, const void* bi
                   const nf4ll_lora* lora, void* t_out, int64_t M, void* y, int64_t ldy,
                   void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
 
+/* Size of the scratch buffer built into the library for nf4ll_forward_static. */
+#define NF4LL_STATIC_SCRATCH_BYTES (40 * 1024 * 1024)
+
+/* nf4ll_forward for callers that can neither allocate device memory nor pass a workspace - a plugin
+ * host that bans allocations after start-up, a server whose memory pool is already sealed. It has no
+ * counterpart in the reference. Same arguments and results as nf4ll_forward minus the workspace:
+ * scratch comes from a fixed NF4LL_STATIC_SCRATCH_BYTES array inside the library's device image
+ * (every GPU that loads the library holds that much until the process exits). Problems whose
+ * nf4ll_workspace_bytes() exceeds it are refused with NF4LL_ERR_WORKSPACE; one config-0 forward
+ * (M = 2048, 1536 x 1536, LoRA) fits. The call itself performs no allocation. The first call on
+ * each device looks the array's device address up (that device must be current) and should happen
+ * before any stream capture starts. All calls on a device share the one buffer, which keeps
+ * whatever the last call wrote: the library clears the parts that must start at zero, but two calls
+ * that overlap in time on the GPU (different streams) race on it - serialise them. */
+int nf4ll_forward_static(const nf4ll_mat* W, const void* x, int64_t ldx, const void* bias,
+                         const nf4ll_lora* lora, void* t_out, int64_t M, void* y, int64_t ldy,
+                         int32_t* status, void* stream);
+
 /* Backward-dX:  dx[M,K] (+)= dy[M,N] . W + keep_scale * mask (.) ((scale * dy . B) . A)
  * reading the same NF4 bytes (the contraction runs over N; no fp16 W and no W^T is materialised).
  * Replaces solution/fast_qwen.py:1310, 1320-1327, 1333-1338, 1350, 1364 (cuBLAS NN GEMMs on the
