@@ -44,7 +44,8 @@ struct GemmParams {
   const __half* bias;      // forward only, may be null
   int accumulate;          // backward: out += result
   int has_lora;
-  const __half* lora_left;   // [M,16] fp16: s.T (forward) or s.U (backward)
+  const float* lora_left;    // [M,16] fp32: T (forward) or s.U (backward)
+  float left_scale;          // applied when the left operand is rounded to fp16: s (forward) or 1 (backward)
   const __half* lora_right;  // forward: B[N,16]; backward: A[16,K]
   const uint8_t* mask;       // backward only: keep-mask of the LoRA input [M, ld_mask], may be null
   int64_t ld_mask;
@@ -319,11 +320,19 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
     // ----------------------------------------------------------------------------- LoRA operand staging
     if (lora_here) {
       const int t = threadIdx.x - 64;   // 0..63
-      // left: rows m0.. of lora_left[M,16]; chunk (row, h) -> (row/8)*256 + h*128 + (row%8)*16
+      // left: rows m0.. of lora_left[M,16] (fp32), scaled and rounded to fp16 here;
+      // chunk (row, h) -> (row/8)*256 + h*128 + (row%8)*16
       for (int c = t; c < BM_TILES * 128 * 2; c += 64) {
         const int row = c >> 1, h = c & 1;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (m0 + row < p.M) v = __ldg(reinterpret_cast<const uint4*>(p.lora_left + (m0 + row) * 16 + h * 8));
+        if (m0 + row < p.M) {
+          const float4* src = reinterpret_cast<const float4*>(p.lora_left + (m0 + row) * 16 + h * 8);
+          const float4 a = __ldg(src), b = __ldg(src + 1);
+          v.x = pack_half2_rn(a.x * p.left_scale, a.y * p.left_scale);
+          v.y = pack_half2_rn(a.z * p.left_scale, a.w * p.left_scale);
+          v.z = pack_half2_rn(b.x * p.left_scale, b.y * p.left_scale);
+          v.w = pack_half2_rn(b.z * p.left_scale, b.w * p.left_scale);
+        }
         const int mt = row >> 7, r = row & 127;
         *reinterpret_cast<uint4*>(sLL + mt * 4096 + (r >> 3) * 256 + h * 128 + (r & 7) * 16) = v;
       }
@@ -763,7 +772,7 @@ static Plan make_plan(int64_t M, int64_t NO, int64_t KC, int r, int sms) {
   if (g_force_splits) splits = g_force_splits;
   if (splits > nkb) splits = static_cast<int>(nkb > 0 ? nkb : 1);
   pl.splits = splits;
-  pl.left_bytes = r > 0 ? align256(M * r * 2) : 0;
+  pl.left_bytes = r > 0 ? align256(M * r * 4) : 0;      // fp32 rank-16 projection when the caller does not keep it
   pl.bt_bytes = r > 0 ? align256(KC * r * 2) : 0;      // room for lora_B transposed (backward only uses it)
   pl.counter_bytes = splits > 1 ? align256(tiles * 4) : 0;
   pl.partial_bytes = splits > 1 ? align256(static_cast<int64_t>(splits) * pl.m_pad * NO * 4) : 0;
@@ -843,8 +852,7 @@ static int check_lora(const nf4ll_lora* l, const char* who, bool need_mask_ld, i
 }
 
 int lora_down_launch(const void* act, int64_t ldact, const uint8_t* mask, int64_t ld_mask, float keep_scale,
-                     const void* R, float t32_scale, float t16_scale, int64_t M, int64_t C, void* t32, void* t16,
-                     cudaStream_t stream);
+                     const void* R, float scale, int64_t M, int64_t C, void* t32, cudaStream_t stream);
 int transpose_n16_launch(const void* B, void* Bt, int64_t N, cudaStream_t stream);
 
 static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact, const void* bias,
@@ -882,12 +890,14 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
   p.has_lora = lora != nullptr;
   p.splits = pl.splits; p.m_pad = pl.m_pad; p.status = status; p.debug = g_debug;
   if (lora) {
-    __half* left = reinterpret_cast<__half*>(ws);
-    // rank-16 projection of the activation: T = drop(x).A^T (forward) or U = dy.B (backward)
+    // rank-16 projection of the activation, fp32: T = drop(x).A^T (forward) or U = s.dy.B (backward);
+    // it lands in the caller's t_out / u_out when given, else in the workspace
+    float* left = side_out ? static_cast<float*>(side_out) : reinterpret_cast<float*>(ws);
     if (mode == kFwd) {
-      if (int rc = lora_down_launch(act, ldact, lora->mask, lora->ld_mask, lora->keep_scale, lora->A, 1.0f, lora->scale,
-                                    M, W->K, side_out, left, stream)) return rc;
+      if (int rc = lora_down_launch(act, ldact, lora->mask, lora->ld_mask, lora->keep_scale, lora->A, 1.0f, M, W->K, left,
+                                    stream)) return rc;
       p.lora_right = static_cast<const __half*>(lora->B);
+      p.left_scale = lora->scale;
     } else {
       const void* bt = lora->Bt;
       if (!bt) {
@@ -895,10 +905,9 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
         if (int rc = transpose_n16_launch(lora->B, tmp, W->N, stream)) return rc;
         bt = tmp;
       }
-      // u = scale * dy.B: fp16 for the tensor core here, fp32 (side_out) for the dA kernel later
-      if (int rc = lora_down_launch(act, ldact, nullptr, 0, 1.0f, bt, lora->scale, lora->scale, M, W->N, side_out, left,
-                                    stream)) return rc;
+      if (int rc = lora_down_launch(act, ldact, nullptr, 0, 1.0f, bt, lora->scale, M, W->N, left, stream)) return rc;
       p.lora_right = static_cast<const __half*>(lora->A);
+      p.left_scale = 1.0f;
       p.mask = lora->mask; p.ld_mask = lora->ld_mask; p.keep_scale = lora->keep_scale;
     }
     p.lora_left = left;

@@ -38,62 +38,86 @@ __device__ __forceinline__ uint4 drop8(uint4 raw, uint2 m, float keep_scale) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Row reduction: t[M,16] = drop(act)[M,C] . R^T with R [16,C] row-major fp16.
-// One CTA = 16 rows, 8 warps; warp w takes the 32-column chunks w, w+8, ... of the contraction and
-// the partial 16x16 results are summed through shared memory. Per chunk a lane issues two 128-bit
-// loads of act (rows g and g+8) and two of R (rank rows g and g+8); a lane's 8 consecutive columns
-// are fed to two MMAs with the SAME column-to-slot assignment on both operands, so no shuffle or
-// shared-memory transpose is needed: out^T[16 ranks, 8 rows] = R[16, k] . act^T[k, 8 rows].
+// Row reduction: t[M,16] += scale * drop(act)[M,C] . R^T with R [16,C] row-major fp16.
+// One CTA = 32 rows x a range of the contraction, 8 warps; warp w takes the 32-column chunks
+// w, w+8, ... of the range. Per chunk a lane issues four 128-bit loads of act (rows g, g+8, g+16,
+// g+24) and two of R (rank rows g and g+8); a lane's 8 consecutive columns feed two MMAs with the
+// SAME column-to-slot assignment on both operands, so no shuffle or shared-memory transpose is
+// needed: out^T[16 ranks, 8 rows] = R[16, k] . act^T[k, 8 rows]. The warps' partial 16x32 results
+// are summed through shared memory and added to t with fp32 atomics (t is zeroed by the launcher),
+// which lets the contraction be split over enough CTAs to keep every SM's loads in flight.
 // ---------------------------------------------------------------------------------------------
 constexpr int kDownWarps = 8;
+constexpr int kDownRows = 32;
 
 __global__ void __launch_bounds__(kDownWarps * 32)
 lora_down_kernel(const __half* __restrict__ act, int64_t ldact, const uint8_t* __restrict__ mask, int64_t ld_mask,
-                 float keep_scale, const __half* __restrict__ R, float t32_scale, float t16_scale, int64_t M, int64_t C,
-                 float* __restrict__ t32, __half* __restrict__ t16) {
-  __shared__ float part[kDownWarps][16][17];
+                 float keep_scale, const __half* __restrict__ R, float scale, int64_t M, int64_t C, int64_t c_per_cta,
+                 float* __restrict__ t32) {
+  __shared__ float part[kDownWarps][kDownRows][17];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int64_t m0 = static_cast<int64_t>(blockIdx.x) * 16;
-  const int64_t row0 = m0 + g, row1 = m0 + g + 8;
-  const bool ok0 = row0 < M, ok1 = row1 < M;
-  const __half* a0p = act + (ok0 ? row0 : 0) * ldact;
-  const __half* a1p = act + (ok1 ? row1 : 0) * ldact;
-  const uint8_t* m0p = mask ? mask + (ok0 ? row0 : 0) * ld_mask : nullptr;
-  const uint8_t* m1p = mask ? mask + (ok1 ? row1 : 0) * ld_mask : nullptr;
+  const int64_t m0 = static_cast<int64_t>(blockIdx.x) * kDownRows;
+  const int64_t c_begin = static_cast<int64_t>(blockIdx.y) * c_per_cta;
+  const int64_t c_end = (c_begin + c_per_cta < C) ? c_begin + c_per_cta : C;
+  const __half* ap[4];
+  const uint8_t* mp[4];
+  bool ok[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t row = m0 + g + 8 * i;
+    ok[i] = row < M;
+    ap[i] = act + (ok[i] ? row : 0) * ldact;
+    mp[i] = mask ? mask + (ok[i] ? row : 0) * ld_mask : nullptr;
+  }
   const __half* r0p = R + static_cast<int64_t>(g) * C;
   const __half* r1p = R + static_cast<int64_t>(g + 8) * C;
-  float c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+  float c[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) c[i][j] = 0.f;
   const uint4 zero = make_uint4(0, 0, 0, 0);
-  for (int64_t k = static_cast<int64_t>(warp) * 32 + t * 8; k < C; k += kDownWarps * 32) {
-    uint4 x0 = ok0 ? __ldg(reinterpret_cast<const uint4*>(a0p + k)) : zero;
-    uint4 x1 = ok1 ? __ldg(reinterpret_cast<const uint4*>(a1p + k)) : zero;
+#pragma unroll 2
+  for (int64_t k = c_begin + static_cast<int64_t>(warp) * 32 + t * 8; k < c_end; k += kDownWarps * 32) {
+    uint4 x[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) x[i] = ok[i] ? __ldg(reinterpret_cast<const uint4*>(ap[i] + k)) : zero;
     const uint4 ra = __ldg(reinterpret_cast<const uint4*>(r0p + k));
     const uint4 rb = __ldg(reinterpret_cast<const uint4*>(r1p + k));
     if (mask) {
-      x0 = drop8(x0, __ldg(reinterpret_cast<const uint2*>(m0p + k)), keep_scale);
-      x1 = drop8(x1, __ldg(reinterpret_cast<const uint2*>(m1p + k)), keep_scale);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) x[i] = drop8(x[i], __ldg(reinterpret_cast<const uint2*>(mp[i] + k)), keep_scale);
     }
     // columns k..k+3 -> MMA slots (2t, 2t+1, 2t+8, 2t+9) of the first MMA, k+4..k+7 of the second
-    mma16816(c0, ra.x, rb.x, ra.y, rb.y, x0.x, x0.y);
-    mma16816(c0, ra.z, rb.z, ra.w, rb.w, x0.z, x0.w);
-    mma16816(c1, ra.x, rb.x, ra.y, rb.y, x1.x, x1.y);
-    mma16816(c1, ra.z, rb.z, ra.w, rb.w, x1.z, x1.w);
-  }
-  // accumulator layout: c[0], c[1] = (rank g, rows 2t, 2t+1); c[2], c[3] = (rank g+8, same rows)
-  part[warp][2 * t][g] = c0[0];      part[warp][2 * t + 1][g] = c0[1];
-  part[warp][2 * t][g + 8] = c0[2];  part[warp][2 * t + 1][g + 8] = c0[3];
-  part[warp][8 + 2 * t][g] = c1[0];      part[warp][8 + 2 * t + 1][g] = c1[1];
-  part[warp][8 + 2 * t][g + 8] = c1[2];  part[warp][8 + 2 * t + 1][g + 8] = c1[3];
-  __syncthreads();
-  const int row = threadIdx.x >> 4, j = threadIdx.x & 15;
-  if (m0 + row < M) {
-    float v = 0.f;
 #pragma unroll
-    for (int w = 0; w < kDownWarps; ++w) v += part[w][row][j];
-    if (t32) t32[(m0 + row) * 16 + j] = v * t32_scale;
-    if (t16) t16[(m0 + row) * 16 + j] = __float2half_rn(v * t16_scale);
+    for (int i = 0; i < 4; ++i) {
+      mma16816(c[i], ra.x, rb.x, ra.y, rb.y, x[i].x, x[i].y);
+      mma16816(c[i], ra.z, rb.z, ra.w, rb.w, x[i].z, x[i].w);
+    }
   }
+  // accumulator layout: c[.][0], c[.][1] = (rank g, rows 2t, 2t+1); c[.][2], c[.][3] = (rank g+8, same rows)
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    part[warp][8 * i + 2 * t][g] = c[i][0];      part[warp][8 * i + 2 * t + 1][g] = c[i][1];
+    part[warp][8 * i + 2 * t][g + 8] = c[i][2];  part[warp][8 * i + 2 * t + 1][g + 8] = c[i][3];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < kDownRows * 16; idx += kDownWarps * 32) {
+    const int row = idx >> 4, j = idx & 15;
+    if (m0 + row < M) {
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < kDownWarps; ++w) v += part[w][row][j];
+      atomicAdd(t32 + (m0 + row) * 16 + j, v * scale);
+    }
+  }
+}
+
+// t16 = fp16(scale * t32), for callers of the stand-alone projection that want the fp16 copy
+__global__ void scale_to_half_kernel(const float* __restrict__ t32, __half* __restrict__ t16, float scale, int64_t n) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) t16[i] = __float2half_rn(t32[i] * scale);
 }
 
 // B[N,16] -> Bt[16,N] (fp16), for callers that do not keep a transposed shadow of lora_B.
@@ -114,14 +138,25 @@ int transpose_n16_launch(const void* B, void* Bt, int64_t N, cudaStream_t stream
   return NF4LL_OK;
 }
 
-// R is [16,C] row-major. t32 = t32_scale * (drop(act) . R^T), t16 = fp16(t16_scale * (...)).
+// R is [16,C] row-major. t32 (fp32 [M,16], required) = scale * (drop(act) . R^T).
 int lora_down_launch(const void* act, int64_t ldact, const uint8_t* mask, int64_t ld_mask, float keep_scale,
-                     const void* R, float t32_scale, float t16_scale, int64_t M, int64_t C, void* t32, void* t16,
-                     cudaStream_t stream) {
+                     const void* R, float scale, int64_t M, int64_t C, void* t32, cudaStream_t stream) {
   if (M == 0) return NF4LL_OK;
-  lora_down_kernel<<<static_cast<unsigned>((M + 15) / 16), kDownWarps * 32, 0, stream>>>(
-      static_cast<const __half*>(act), ldact, mask, ld_mask, keep_scale, static_cast<const __half*>(R), t32_scale,
-      t16_scale, M, C, static_cast<float*>(t32), static_cast<__half*>(t16));
+  int dev = 0, sms = 148;
+  NF4LL_CUDA(cudaGetDevice(&dev));
+  NF4LL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int64_t row_groups = (M + kDownRows - 1) / kDownRows;
+  const int64_t units = (C + kDownWarps * 32 - 1) / (kDownWarps * 32);     // 256-column units
+  int64_t ks = (2 * static_cast<int64_t>(sms)) / row_groups;   // at most two CTAs per SM: one wave, no tail
+  if (ks > units) ks = units;
+  if (ks < 1) ks = 1;
+  const int64_t c_per_cta = (units + ks - 1) / ks * (kDownWarps * 32);
+  ks = (C + c_per_cta - 1) / c_per_cta;
+  NF4LL_CUDA(cudaMemsetAsync(t32, 0, sizeof(float) * 16 * M, stream));
+  dim3 grid(static_cast<unsigned>(row_groups), static_cast<unsigned>(ks));
+  lora_down_kernel<<<grid, kDownWarps * 32, 0, stream>>>(static_cast<const __half*>(act), ldact, mask, ld_mask,
+                                                        keep_scale, static_cast<const __half*>(R), scale, M, C,
+                                                        c_per_cta, static_cast<float*>(t32));
   NF4LL_CUDA(cudaGetLastError());
   return NF4LL_OK;
 }
@@ -166,31 +201,51 @@ lora_grad_kernel(const __half* __restrict__ act, int64_t ldact, const uint8_t* _
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
 
-  for (int64_t r0 = r_begin; r0 < r_end; r0 += kGradStage) {
-    // stage the act tile: 64 rows x 8 chunks of 8 columns = 512 chunks over 128 threads
+  // software pipeline: the global loads of the next 64-row stage are in flight while this one is
+  // turned into MMAs, so a CTA always has its 12-16 KB of loads outstanding
+  uint4 pa[4];
+  uint2 pm[4];
+  float ps[8];
+  auto fetch = [&](int64_t r0) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int idx = threadIdx.x + i * kGradThreads;
       const int r = idx >> 3, ch = idx & 7;
       const int64_t row = r0 + r, col = c0 + ch * 8;
-      uint4 v = make_uint4(0, 0, 0, 0);
+      pa[i] = make_uint4(0, 0, 0, 0);
+      pm[i] = make_uint2(0x01010101u, 0x01010101u);
       if (row < r_end && col < C) {
-        v = __ldg(reinterpret_cast<const uint4*>(act + row * ldact + col));
-        if (mask) v = drop8(v, __ldg(reinterpret_cast<const uint2*>(mask + row * ld_mask + col)), keep_scale);
+        pa[i] = __ldg(reinterpret_cast<const uint4*>(act + row * ldact + col));
+        if (mask) pm[i] = __ldg(reinterpret_cast<const uint2*>(mask + row * ld_mask + col));
       }
-      *reinterpret_cast<uint4*>(&s_act[r][ch * 8]) = v;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = threadIdx.x + i * kGradThreads;
+      const int r = idx >> 4, j = idx & 15;
+      ps[i] = (r0 + r < r_end) ? __ldg(side + (r0 + r) * 16 + j) : 0.f;
+    }
+  };
+  if (r_begin < r_end) fetch(r_begin);
+  for (int64_t r0 = r_begin; r0 < r_end; r0 += kGradStage) {
+    // stage the act tile (dropout applied on the way): 64 rows x 8 chunks of 8 columns over 128 threads
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = threadIdx.x + i * kGradThreads;
+      const int r = idx >> 3, ch = idx & 7;
+      *reinterpret_cast<uint4*>(&s_act[r][ch * 8]) = mask ? drop8(pa[i], pm[i], keep_scale) : pa[i];
     }
     // stage side transposed, split into hi + lo: 64 rows x 16 = 1024 values over 128 threads
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int idx = threadIdx.x + i * kGradThreads;
       const int r = idx >> 4, j = idx & 15;
-      const float v = (r0 + r < r_end) ? __ldg(side + (r0 + r) * 16 + j) : 0.f;
-      const __half hi = __float2half_rn(v);
+      const __half hi = __float2half_rn(ps[i]);
       s_hi[j][r] = hi;
-      s_lo[j][r] = __float2half_rn(v - __half2float(hi));
+      s_lo[j][r] = __float2half_rn(ps[i] - __half2float(hi));
     }
     __syncthreads();
+    if (r0 + kGradStage < r_end) fetch(r0 + kGradStage);
     const int kb = warp * 16;      // this warp's 16 rows of the stage
     const uint32_t ah0 = *reinterpret_cast<const uint32_t*>(&s_hi[g][kb + 2 * t]);
     const uint32_t ah1 = *reinterpret_cast<const uint32_t*>(&s_hi[g + 8][kb + 2 * t]);
@@ -242,7 +297,7 @@ static int lora_grad_launch(const void* act, int64_t ldact, const uint8_t* mask,
   NF4LL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int64_t col_tiles = (C + kGradCols - 1) / kGradCols;
   const int64_t stages = (M + kGradStage - 1) / kGradStage;
-  int64_t msplit = (4 * static_cast<int64_t>(sms) + col_tiles - 1) / col_tiles;    // about four CTAs per SM
+  int64_t msplit = (3 * static_cast<int64_t>(sms)) / col_tiles;    // at most three CTAs per SM: one wave, no tail
   if (msplit > stages) msplit = stages;
   if (msplit < 1) msplit = 1;
   const int64_t rows_per = (stages + msplit - 1) / msplit * kGradStage;
@@ -270,7 +325,16 @@ extern "C" int nf4ll_lora_down(const void* x, int64_t ldx, const uint8_t* mask, 
     return NF4LL_ERR_ALIGN;
   }
   if (int rc = require_sm100()) return rc;
-  return lora_down_launch(x, ldx, mask, ld_mask, keep_scale, A, 1.0f, scale, M, K, t32, t16, static_cast<cudaStream_t>(stream));
+  if (!t32) { set_detail("nf4ll_lora_down: t32 is required (t16 is optional)"); return NF4LL_ERR_NULL; }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (int rc = lora_down_launch(x, ldx, mask, ld_mask, keep_scale, A, 1.0f, M, K, t32, st)) return rc;
+  if (t16 && M > 0) {
+    const int64_t n = M * 16;
+    scale_to_half_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(static_cast<const float*>(t32),
+                                                                              static_cast<__half*>(t16), scale, n);
+    NF4LL_CUDA(cudaGetLastError());
+  }
+  return NF4LL_OK;
 }
 
 extern "C" int nf4ll_lora_grads(const void* dy, int64_t lddy, const void* x, int64_t ldx, const uint8_t* mask,

@@ -85,7 +85,7 @@ int nf4ll_dequant(const uint8_t* nib, const uint8_t* qabs, const float* scale2, 
                   const float* code2, int64_t n_qblocks, void* out_f16, void* stream);
 
 /* Bytes of scratch that nf4ll_forward / nf4ll_backward_dx need for M rows against W[N,K] with LoRA
- * rank r (0 = no LoRA). The scratch holds the fp16 rank-r operand of the fused LoRA step, split-K
+ * rank r (0 = no LoRA). The scratch holds the fp32 rank-r projection feeding the fused LoRA step, split-K
  * partial sums and tile counters. Always a multiple of 256; the workspace must be 256-byte aligned. */
 int64_t nf4ll_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t r);
 
@@ -134,7 +134,7 @@ int nf4ll_backward_dx(const nf4ll_mat* W, const void* dy, int64_t lddy, const nf
 
 /* Rank-r projection on its own:  t32[M,r] = drop(x)[M,K] . A^T  and  t16 = fp16(scale * t32), with A
  * [r,K] row-major fp16 (lora_A; or lora_B transposed, to get dy . B). A small tensor-core GEMM that
- * streams x once. Replaces solution/fast_qwen.py:943-944 and 1370/1373. Either output may be NULL.
+ * streams x once. Replaces solution/fast_qwen.py:943-944 and 1370/1373. t32 is required, t16 optional.
  * K a multiple of 8; mask, when given, 16-byte aligned with ld_mask a multiple of 16. */
 int nf4ll_lora_down(const void* x, int64_t ldx, const uint8_t* mask, int64_t ld_mask,
                     float keep_scale, const void* A, float scale, int32_t r,

@@ -195,17 +195,26 @@ def test_split_contraction_is_stable_under_back_to_back_launches():
     """The split-contraction path (partial sums through scratch, last CTA of a tile adds them up) must
     give the same bits on every launch: 100 forwards queued back to back without host syncs, each
     compared with the single-pass result. Guards the ordering between the elected lane that issues
-    the TMA stores of the partial sums and the barrier that lets its warp-mates reuse the staging."""
-    pr = make_problem(1536, 1536, 2048, seed=61, lora=True, dropout=0.05, bias=True)
+    the TMA stores of the partial sums and the barrier that lets its warp-mates reuse the staging.
+    (Without LoRA: the rank-16 projection is summed with fp32 atomics, whose order is not fixed.)"""
+    pr = make_problem(1536, 1536, 2048, seed=61, lora=False, bias=True)
     d = to_device(pr)
     h = _lib.lib()
     h.nf4ll_tune_override(0, 0, 1)
     try:
-        y0, _ = linear.forward(d.w, d.x, bias=d.bias, lora=d.lora, mask=d.mask, keep_scale=d.keep_scale)
+        y0, _ = linear.forward(d.w, d.x, bias=d.bias)
     finally:
         h.nf4ll_tune_override(0, 0, 0)
-    outs = [linear.forward(d.w, d.x, bias=d.bias, lora=d.lora, mask=d.mask, keep_scale=d.keep_scale)[0] for _ in range(100)]
+    outs = [linear.forward(d.w, d.x, bias=d.bias)[0] for _ in range(100)]
     linear.check_status()
     assert all(torch.equal(o, outs[0]) for o in outs), "split-K results differ between launches"
     err, rel = nf4_oracle.errors(outs[0], y0.float())
     assert err <= 2e-3 and rel <= 1e-4, (err, rel)      # same sums, only the fp32 addition order differs
+    # with LoRA the launches may differ in the last bits, never by more than rounding
+    pl = make_problem(1536, 1536, 2048, seed=62, lora=True, dropout=0.05)
+    dl = to_device(pl)
+    outs = [linear.forward(dl.w, dl.x, lora=dl.lora, mask=dl.mask, keep_scale=dl.keep_scale)[0] for _ in range(50)]
+    linear.check_status()
+    for o in outs[1:]:
+        err, rel = nf4_oracle.errors(o, outs[0].float())
+        assert err <= 2e-3 and rel <= 1e-4, (err, rel)
