@@ -52,6 +52,15 @@ __device__ __forceinline__ uint32_t pack_half2_rn(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Raw byte permute. Unlike __byte_perm, which first clears bit 3 of every selector nibble (one more
+// logic instruction per call), this hands the selector to the hardware as it is: bit 3 of a nibble
+// would ask for sign replication, so callers keep it clear themselves.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+
 __device__ __forceinline__ BlockTable make_block_table(float absmax) {
   constexpr float lv[16] = {NF4LL_LEVELS};
   BlockTable t;
@@ -69,24 +78,26 @@ __device__ __forceinline__ BlockTable make_block_table(float absmax) {
 // Decode one 32-bit word of packed codes (bytes b0..b3 = elements 0..7, the even element of each
 // byte in its high nibble) into 8 fp16 values, returned as four half2 registers in element order.
 __device__ __forceinline__ uint4 decode_word(const BlockTable& t, uint32_t w) {
+  // every selector nibble below stays within 0..7 (bit 3 clear), as the raw permute requires; only the
+  // low 16 bits of a selector are read, so the shifted copies may carry anything above them
   const uint32_t sel = w & 0x77777777u;                                // low 3 bits of every code
   const uint32_t pick = ((w >> 1) & 0x44444444u) | 0x32103210u;        // byte i from the upper table if bit 3
   uint4 out;
   {
-    const uint32_t la = __byte_perm(t.lo[0], t.lo[1], sel), lb = __byte_perm(t.lo[2], t.lo[3], sel);
-    const uint32_t ha = __byte_perm(t.hi[0], t.hi[1], sel), hb = __byte_perm(t.hi[2], t.hi[3], sel);
-    const uint32_t lo = __byte_perm(la, lb, pick), hi = __byte_perm(ha, hb, pick);
+    const uint32_t la = prmt(t.lo[0], t.lo[1], sel), lb = prmt(t.lo[2], t.lo[3], sel);
+    const uint32_t ha = prmt(t.hi[0], t.hi[1], sel), hb = prmt(t.hi[2], t.hi[3], sel);
+    const uint32_t lo = prmt(la, lb, pick), hi = prmt(ha, hb, pick);
     // nibble order in the low 16 bits: e1, e0, e3, e2 -> (e0, e1) and (e2, e3)
-    out.x = __byte_perm(lo, hi, 0x4051);
-    out.y = __byte_perm(lo, hi, 0x6273);
+    out.x = prmt(lo, hi, 0x4051u);
+    out.y = prmt(lo, hi, 0x6273u);
   }
   {
     const uint32_t sel2 = sel >> 16, pick2 = pick >> 16;
-    const uint32_t la = __byte_perm(t.lo[0], t.lo[1], sel2), lb = __byte_perm(t.lo[2], t.lo[3], sel2);
-    const uint32_t ha = __byte_perm(t.hi[0], t.hi[1], sel2), hb = __byte_perm(t.hi[2], t.hi[3], sel2);
-    const uint32_t lo = __byte_perm(la, lb, pick2), hi = __byte_perm(ha, hb, pick2);
-    out.z = __byte_perm(lo, hi, 0x4051);
-    out.w = __byte_perm(lo, hi, 0x6273);
+    const uint32_t la = prmt(t.lo[0], t.lo[1], sel2), lb = prmt(t.lo[2], t.lo[3], sel2);
+    const uint32_t ha = prmt(t.hi[0], t.hi[1], sel2), hb = prmt(t.hi[2], t.hi[3], sel2);
+    const uint32_t lo = prmt(la, lb, pick2), hi = prmt(ha, hb, pick2);
+    out.z = prmt(lo, hi, 0x4051u);
+    out.w = prmt(lo, hi, 0x6273u);
   }
   return out;
 }

@@ -854,6 +854,9 @@ static int check_lora(const nf4ll_lora* l, const char* who, bool need_mask_ld, i
 int lora_down_launch(const void* act, int64_t ldact, const uint8_t* mask, int64_t ld_mask, float keep_scale,
                      const void* R, float scale, int64_t M, int64_t C, void* t32, cudaStream_t stream);
 int transpose_n16_launch(const void* B, void* Bt, int64_t N, cudaStream_t stream);
+int stream_forward_launch(const nf4ll_mat* W, const void* x, int64_t ldx, const void* bias, const float* t32,
+                          const void* lora_b, float lora_scale, int64_t M, void* y, int64_t ldy, cudaStream_t stream);
+constexpr int64_t kStreamMaxRows = 16;     // at or below this many token rows the forward is a weight-streaming pass
 
 static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact, const void* bias,
                     const nf4ll_lora* lora, void* side_out, int64_t M, void* out, int64_t ldo, int accumulate,
@@ -911,6 +914,10 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
       p.mask = lora->mask; p.ld_mask = lora->ld_mask; p.keep_scale = lora->keep_scale;
     }
     p.lora_left = left;
+    if (mode == kFwd && M <= kStreamMaxRows && !g_force_bm && !g_force_bn && !g_force_splits)
+      return stream_forward_launch(W, act, ldact, bias, left, lora->B, lora->scale, M, out, ldo, stream);
+  } else if (mode == kFwd && M <= kStreamMaxRows && !g_force_bm && !g_force_bn && !g_force_splits) {
+    return stream_forward_launch(W, act, ldact, bias, nullptr, nullptr, 0.f, M, out, ldo, stream);
   }
   if (pl.splits > 1) {
     p.counters = reinterpret_cast<int*>(ws + pl.left_bytes + pl.bt_bytes);
