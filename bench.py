@@ -338,6 +338,9 @@ def run_ours(args):
                 "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "ms_per_step": e2e_ms / args.steps},
                 "gpu_launches": 18 * args.steps, "clocks": clocks}
+        if world == 1 and not args.no_stream:
+            line["weight_stream"] = {"unit": "GB/s of NF4 bytes", "peak_gbs": pk["hbm_gbs"], "peak_source": pk["source"],
+                                     "cases": weight_stream_numbers(dev, pk["hbm_gbs"])}
         if world == 1 and not args.no_cpu:
             tf, dt, cores = time_cpu(128, 2, 1)
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
@@ -346,6 +349,46 @@ def run_ours(args):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def weight_stream_numbers(dev, peak_gbs):
+    """Secondary metric of the path: NF4 bytes streamed per second by the forward at decode-sized
+    batches (BASELINE config 4: Qwen2.5-32B shapes, LoRA r=16 fused, M in {1, 8, 64}). Distinct weight
+    copies larger than L2 (126 MB) rotate inside one CUDA graph so that every launch reads its NF4
+    bytes from HBM; the figure is algorithmic bytes (0.516 B per weight) over the median replay time."""
+    import statistics
+    import torch
+    from decentrik_prime_b200 import blocks, linear
+    out = []
+    for name, n, k, copies in (("q/o 5120x5120", 5120, 5120, 20), ("gate/up 27648x5120", 27648, 5120, 4),
+                               ("down 5120x27648", 5120, 27648, 4)):
+        ps = [blocks.make_projection(n, k, seed=900 + i, device=dev, lora=True) for i in range(copies)]
+        nbytes = ps[0].w.nbytes
+        for M in (1, 8, 64):
+            x = torch.randn(M, k, device=dev).half()
+            ys = [torch.empty(M, n, device=dev, dtype=torch.float16) for _ in ps]
+            side = torch.cuda.Stream(dev)
+            with torch.cuda.stream(side):
+                for p_, y_ in zip(ps, ys):
+                    linear.forward(p_.w, x, lora=p_.lora, out=y_)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for p_, y_ in zip(ps, ys):
+                        linear.forward(p_.w, x, lora=p_.lora, out=y_)
+                times = []
+                for _ in range(20):
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(side); graph.replay(); b.record(side)
+                    torch.cuda.synchronize()
+                    times.append(a.elapsed_time(b) * 1e-3 / copies)
+            t = statistics.median(times)
+            out.append({"shape": name, "M": M, "us": t * 1e6, "gbs": nbytes / t / 1e9,
+                        "frac_of_measured_hbm": nbytes / t / 1e9 / peak_gbs})
+            del graph
+        del ps
+        torch.cuda.empty_cache()
+    return out
 
 
 def _hook_block(blk, ev_pairs, M):
@@ -389,6 +432,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-stream", action="store_true", help="skip the small-batch weight-stream numbers")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
