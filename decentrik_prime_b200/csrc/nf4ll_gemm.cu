@@ -21,42 +21,9 @@
 // one W row (= one quantisation block, 128 bytes), 8 rows per 1024-byte swizzle atom. Forward reads
 // it as a K-major B operand (contraction along the row), backward as an MN-major one (contraction
 // across rows), so the same NF4 bytes serve W and W^T.
-#include <cuda.h>
-
-#include "nf4ll_common.cuh"
+#include "nf4ll_gemm_shared.cuh"
 
 namespace nf4ll {
-
-enum : int { kFwd = 0, kBwd = 1 };
-
-struct GemmParams {
-  const uint8_t* nib;
-  const uint8_t* qabs;
-  const float* scale2;
-  const float* offset2;
-  const float* code2;
-  int64_t N, K;            // W[N,K]
-  int64_t M;               // rows of the activation / output
-  int64_t NO;              // output columns: N (forward) or K (backward)
-  int64_t KC;              // contraction length: K (forward) or N (backward)
-  __half* out;
-  int64_t ldo;
-  const __half* bias;      // forward only, may be null
-  int accumulate;          // backward: out += result
-  int has_lora;
-  const float* lora_left;    // [M,16] fp32: T (forward) or s.U (backward)
-  float left_scale;          // applied when the left operand is rounded to fp16: s (forward) or 1 (backward)
-  const __half* lora_right;  // forward: B[N,16]; backward: A[16,K]
-  const uint8_t* mask;       // backward only: keep-mask of the LoRA input [M, ld_mask], may be null
-  int64_t ld_mask;
-  float keep_scale;
-  int splits;              // split of the contraction across blockIdx.z
-  float* partial;          // [splits][M_pad][NO] fp32 when splits > 1
-  int* counters;           // one per output tile when splits > 1 (zero on entry, zero on exit)
-  int64_t m_pad;
-  int32_t* status;
-  int debug;               // timing experiments only: bit 0 skips the decode, bit 1 skips the MMAs
-};
 
 template <int BM_TILES, int BN>
 struct TileCfg {
@@ -75,46 +42,6 @@ struct TileCfg {
   // the LoRA operands are only read by the very first MMAs: they borrow the last activation stage
   static_assert(kLoraLeftBytes + kLoraRightBytes <= kABytes, "LoRA operands must fit one activation stage");
 };
-
-constexpr int kFixSlots = 8;     // 16 KB slots of the split-K fix-up ring (fits every tile shape's operand rings)
-
-struct Abort {
-  volatile int* flag;
-  int32_t* status;
-  __device__ __forceinline__ void raise(int code) const {
-    *flag = 1;
-    if (status) atomicCAS(status, 0, code);
-  }
-};
-
-__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, const Abort& ab, int code) {
-  if (mbar_wait(bar, parity, ab.flag)) return true;
-  ab.raise(code);
-  return false;
-}
-
-__device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
-  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
-  return v;
-}
-__device__ __forceinline__ float lds_f32(uint32_t addr) {
-  float v;
-  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
-  return v;
-}
-
-// Decode one quantisation block (32 bytes of codes) into one 128-byte row of a 128B-swizzled tile
-// (row_addr: shared-memory address of the row; key: row index modulo 8).
-__device__ __forceinline__ void dequant_block_to_smem(uint32_t row_addr, int key, const uint4& c0, const uint4& c1, float absmax) {
-  const BlockTable t = make_block_table(absmax);
-  const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-#pragma unroll
-  for (int j = 0; j < 8; ++j) sts128(row_addr + ((j ^ key) << 4), decode_word(t, w[j]));
-}
 
 template <int MODE, int BM_TILES, int BN>
 __global__ void __launch_bounds__(TileCfg<BM_TILES, BN>::kThreads, 1)
@@ -736,6 +663,7 @@ static int make_nib_map(CUtensorMap* map, const void* nib, int64_t N, int64_t K,
 }
 
 struct Plan {
+  int pair;                // 1: CTA-pair kernel (tcgen05 cta_group::2), tile (bm_tiles x 256) x 256 per pair
   int bm_tiles, bn, splits;
   int64_t tiles_m, tiles_o, m_pad;
   int64_t left_bytes, bt_bytes, counter_bytes, partial_bytes;
@@ -748,22 +676,29 @@ static thread_local cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;
 
 static int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
 
-static Plan make_plan(int64_t M, int64_t NO, int64_t KC, int r, int sms) {
+static Plan make_plan(int mode, int64_t M, int64_t NO, int64_t KC, int r, int sms) {
   Plan pl;
+  // CTA pairs whenever the output is wide enough for a 256-column tile and tall enough to fill the
+  // pair's 256 accumulator rows; the single-CTA kernel serves narrow or short problems.
+  // Measured on B200 (M = 2048, Qwen2.5-1.5B shapes): the pair is 8-10 % faster for backward-dX and a few
+  // per cent slower for forward, whose single-CTA pipeline has less cross-CTA latency to hide.
+  pl.pair = (mode == kBwd && NO > 128 && M > 128) ? 1 : 0;
   pl.bn = (NO % 256 == 0 || NO > 256) ? 256 : 128;
   if (NO <= 128) pl.bn = 128;
   pl.bm_tiles = (M > 128) ? 2 : 1;
-  if (g_force_bn) pl.bn = g_force_bn;
+  if (pl.pair) { pl.bn = 256; pl.bm_tiles = (M > 256) ? 2 : 1; }
+  if (g_force_bn == 512) { pl.pair = 1; pl.bn = 256; }          // testing hook: 512 asks for the pair kernel
+  else if (g_force_bn) { pl.pair = 0; pl.bn = g_force_bn; if (!g_force_bm) pl.bm_tiles = (M > 128) ? 2 : 1; }
   if (g_force_bm) pl.bm_tiles = g_force_bm;
-  const int64_t bm = pl.bm_tiles * 128;
+  const int64_t bm = pl.bm_tiles * (pl.pair ? 256 : 128);       // rows per tile (per pair or per CTA)
   pl.tiles_m = (M + bm - 1) / bm;
   pl.tiles_o = (NO + pl.bn - 1) / pl.bn;
   pl.m_pad = pl.tiles_m * bm;
-  const int64_t tiles = pl.tiles_m * pl.tiles_o;
+  const int64_t ctas = pl.tiles_m * pl.tiles_o * (pl.pair ? 2 : 1);
   const int64_t nkb = KC / 64;
   int splits = 1;
-  if (tiles * 2 <= sms) {                       // less than half a wave: split the contraction
-    splits = static_cast<int>(sms / tiles);
+  if (ctas * 2 <= sms) {                        // less than half a wave: split the contraction
+    splits = static_cast<int>(sms / ctas);
     const int64_t max_by_k = nkb / 4 > 0 ? nkb / 4 : 1;     // at least 4 stages per split
     if (splits > max_by_k) splits = static_cast<int>(max_by_k);
     if (splits > 16) splits = 16;
@@ -774,7 +709,7 @@ static Plan make_plan(int64_t M, int64_t NO, int64_t KC, int r, int sms) {
   pl.splits = splits;
   pl.left_bytes = r > 0 ? align256(M * r * 4) : 0;      // fp32 rank-16 projection when the caller does not keep it
   pl.bt_bytes = r > 0 ? align256(KC * r * 2) : 0;      // room for lora_B transposed (backward only uses it)
-  pl.counter_bytes = splits > 1 ? align256(tiles * 4) : 0;
+  pl.counter_bytes = splits > 1 ? align256(ctas * 4) : 0;      // one per CTA-owned block of output rows
   pl.partial_bytes = splits > 1 ? align256(static_cast<int64_t>(splits) * pl.m_pad * NO * 4) : 0;
   return pl;
 }
@@ -854,6 +789,8 @@ static int check_lora(const nf4ll_lora* l, const char* who, bool need_mask_ld, i
 int lora_down_launch(const void* act, int64_t ldact, const uint8_t* mask, int64_t ld_mask, float keep_scale,
                      const void* R, float scale, int64_t M, int64_t C, void* t32, cudaStream_t stream);
 int transpose_n16_launch(const void* B, void* Bt, int64_t N, cudaStream_t stream);
+int launch_pair(int mode, int bm_tiles, const CUtensorMap& map, const CUtensorMap& nib_map, const CUtensorMap& out_map,
+                const GemmParams& p, int64_t tiles_o, int64_t tiles_mp, int splits, cudaStream_t stream);
 int stream_forward_launch(const nf4ll_mat* W, const void* x, int64_t ldx, const void* bias, const float* t32,
                           const void* lora_b, float lora_scale, int64_t M, void* y, int64_t ldy, cudaStream_t stream);
 constexpr int64_t kStreamMaxRows = 16;     // at or below this many token rows the forward is a weight-streaming pass
@@ -875,7 +812,7 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
   if (int rc = require_sm100()) return rc;
   int sms = 148;
   if (int rc = device_sms(&sms)) return rc;
-  const Plan pl = make_plan(M, NO, KC, lora ? lora->r : 0, sms);
+  const Plan pl = make_plan(mode, M, NO, KC, lora ? lora->r : 0, sms);
   if (pl.total() > 0) {
     if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || workspace_bytes < pl.total()) {
       set_detail("%s: needs a 256-byte aligned workspace of %lld bytes (got %lld)", who,
@@ -933,11 +870,13 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
     if (int rc = make_tile_map(&out_map, p.partial, static_cast<int64_t>(pl.splits) * pl.m_pad, NO, NO, true)) return rc;
   }
   CUtensorMap nib_map;
-  if (int rc = make_nib_map(&nib_map, W->nib, W->N, W->K, mode, pl.bn)) return rc;
+  if (int rc = make_nib_map(&nib_map, W->nib, W->N, W->K, mode, pl.pair ? 128 : pl.bn)) return rc;
   cudaEvent_t ev0 = g_ev_start, ev1 = g_ev_stop;
   g_ev_start = g_ev_stop = nullptr;
   if (ev0) NF4LL_CUDA(cudaEventRecord(ev0, stream));
-  const int rc = mode == kFwd ? launch<kFwd>(map, nib_map, out_map, p, pl, stream) : launch<kBwd>(map, nib_map, out_map, p, pl, stream);
+  const int rc = pl.pair ? launch_pair(mode, pl.bm_tiles, map, nib_map, out_map, p, pl.tiles_o, pl.tiles_m, pl.splits, stream)
+                 : (mode == kFwd ? launch<kFwd>(map, nib_map, out_map, p, pl, stream)
+                                 : launch<kBwd>(map, nib_map, out_map, p, pl, stream));
   if (rc == NF4LL_OK && ev1) NF4LL_CUDA(cudaEventRecord(ev1, stream));
   return rc;
 }
@@ -953,7 +892,7 @@ extern "C" int64_t nf4ll_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_
     int v = 0;
     if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) sms = v;
   }
-  const int64_t f = make_plan(M, N, K, r, sms).total(), b = make_plan(M, K, N, r, sms).total();
+  const int64_t f = make_plan(kFwd, M, N, K, r, sms).total(), b = make_plan(kBwd, M, K, N, r, sms).total();
   return f > b ? f : b;
 }
 
@@ -974,7 +913,7 @@ extern "C" int nf4ll_backward_dx(const nf4ll_mat* W, const void* dy, int64_t ldd
 // chosen by the calling thread's next calls; zeros restore the built-in heuristic.
 extern "C" void nf4ll_tune_override(int32_t bm_tiles, int32_t bn, int32_t splits) {
   nf4ll::g_force_bm = (bm_tiles == 1 || bm_tiles == 2) ? bm_tiles : 0;
-  nf4ll::g_force_bn = (bn == 128 || bn == 256) ? bn : 0;
+  nf4ll::g_force_bn = (bn == 128 || bn == 256 || bn == 512) ? bn : 0;
   nf4ll::g_force_splits = splits > 0 ? splits : 0;
 }
 

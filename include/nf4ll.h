@@ -166,7 +166,7 @@ int nf4ll_swiglu_backward(const void* g, int64_t ldg, const void* u, int64_t ldu
 int nf4ll_read_status(const int32_t* status, void* stream);
 
 /* Testing and tuning hook; no counterpart in the reference. Forces the tile shape (bm_tiles 1|2 =
- * 128|256 rows, bn 128|256 columns) and the split count of the contraction for the calling
+ * 128|256 rows, bn 128|256 columns, bn 512 = the CTA-pair kernel) and the split count of the contraction for the calling
  * thread's next nf4ll_forward / nf4ll_backward_dx calls; zeros restore the built-in heuristic. */
 void nf4ll_tune_override(int32_t bm_tiles, int32_t bn, int32_t splits);
 

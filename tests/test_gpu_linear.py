@@ -69,8 +69,10 @@ def test_leading_dimensions():
     run_case(256, 256, 130, padded=True, bias=True)
 
 
-@pytest.mark.parametrize("force", [(1, 128, 1), (2, 128, 1), (1, 256, 1), (2, 256, 1), (1, 128, 3), (2, 256, 2), (2, 256, 4)])
+@pytest.mark.parametrize("force", [(1, 128, 1), (2, 128, 1), (1, 256, 1), (2, 256, 1), (1, 128, 3), (2, 256, 2), (2, 256, 4),
+                                   (1, 512, 1), (2, 512, 1), (1, 512, 2), (2, 512, 3)])
 def test_every_tile_shape_and_split(force):
+    """force = (M tiles per CTA, tile columns, splits of the contraction); 512 columns = the CTA-pair kernel."""
     run_case(512, 768, 300, bias=True, force=force, seed=sum(force))
 
 
