@@ -238,6 +238,8 @@ def run_ours(args):
         step(i, dev_x[i % N_INPUT_SETS], dev_dy[i % N_INPUT_SETS], mask_sets[i % N_INPUT_SETS])
     barrier()
     linear.check_status(dev)
+    _fill_event_pool(6 * args.steps + 6)
+    torch.cuda.synchronize()
     sampler = ClockSampler(local) if rank == 0 else None
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -351,6 +353,90 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_stack(args):
+    """Secondary workloads (not the driver's default line): the full projection stack of BASELINE
+    config 2 (`--workload stack1.5b`: 28 layers, 4 packed sequences of 64..512 tokens, one GPU) and
+    config 3 (`--workload stack7b`: Qwen2.5-7B shapes, M = 16384 packed rows split by rows over the
+    ranks = strong scaling, LoRA gradients all-reduced once per step). Only projections and the
+    minimal glue of decentrik_prime_b200/stack.py run; FLOPs are the projections' algorithmic FLOPs."""
+    import torch
+    import torch.distributed as dist
+    from decentrik_prime_b200 import dp, linear, stack
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if args.workload == "stack1.5b":
+        hidden, inter, kv, layers, distinct = 1536, 8960, 256, 28, 28
+        lens, M_total = stack.pack_lengths(4, 64, 512, seed=2)
+        note = f"4 sequences of lengths {lens}"
+    else:
+        hidden, inter, kv, layers, distinct = 3584, 18944, 512, 28, 2
+        lens, M_total = stack.pack_lengths(32, 256, 512, seed=3)
+        M_total = 16384          # the configuration's fixed packed row count
+        note = "32 sequences packed to 16384 rows; 2 distinct weight sets reused over 28 layers"
+    lo, hi = dp.shard_rows(M_total, world, rank)
+    M = hi - lo
+    st = stack.ProjectionStack(hidden, inter, kv, layers, dev, seed=7, distinct_layers=distinct)
+    gen = torch.Generator().manual_seed(100 + rank)
+    x = torch.randn(M, hidden, generator=gen).half().to(dev)
+    dy = (torch.randn(M, hidden, generator=gen) * 0.1).half().to(dev)
+    gdev = torch.Generator(device=dev).manual_seed(5 + rank)
+    n_mask_sets = min(distinct, 4)
+    masks = [{n: (torch.rand(M, hidden, device=dev, generator=gdev) >= P_DROP).to(torch.uint8) for n in ("q_proj", "v_proj")}
+             for _ in range(n_mask_sets)]
+    masks = [masks[i % n_mask_sets] for i in range(layers)]
+    keep_scale = 1.0 / float(torch.tensor(1.0 - P_DROP, dtype=torch.float32))
+
+    def step():
+        st.step(x, dy, masks, keep_scale)
+        if world > 1:
+            dist.all_reduce(st.bucket.flat)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    steps, warmup = min(args.steps, 20), min(max(args.warmup, 3), 5)
+    for _ in range(warmup):
+        step()
+    barrier()
+    linear.check_status(dev)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        step()
+    t1.record()
+    barrier()
+    ms = t0.elapsed_time(t1)
+    linear.check_status(dev)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+        fl = torch.tensor([float(st.flops(M))], dtype=torch.float64, device=dev)
+        dist.all_reduce(fl)
+        flops = fl.item()
+    else:
+        flops = float(st.flops(M))
+    if rank == 0:
+        line = {"metric": "nf4_lora_projection_stack_tokens_per_s", "value": M_total * steps / (ms * 1e-3), "unit": "tokens/s",
+                "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True,
+                "scaling": "strong" if args.workload == "stack7b" else "weak", "vs_baseline": None, "dtype": "f16",
+                "data": "synthetic",
+                "config": {"workload": args.workload, "rows": M_total, "rows_per_gpu": M, "layers": layers, "hidden": hidden,
+                           "intermediate": inter, "kv": kv, "lora": "r=16 on q_proj, v_proj", "note": note,
+                           "tflops": flops * steps / (ms * 1e-3) / 1e12, "parallelism": f"dp{world}"}}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def weight_stream_numbers(dev, peak_gbs):
     """Secondary metric of the path: NF4 bytes streamed per second by the forward at decode-sized
     batches (BASELINE config 4: Qwen2.5-32B shapes, LoRA r=16 fused, M in {1, 8, 64}). Distinct weight
@@ -391,6 +477,19 @@ def weight_stream_numbers(dev, peak_gbs):
     return out
 
 
+_event_pool = []
+
+
+def _fill_event_pool(n):
+    """Timing events are created (and their handles materialised by a first record) before the timed
+    region, so that arming the kernel hook costs one ctypes call per launch."""
+    import torch
+    while len(_event_pool) < n:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); b.record()
+        _event_pool.append((a, b))
+
+
 def _hook_block(blk, ev_pairs, M):
     """Arrange for the six tensor-core launches of this block step to be bracketed by CUDA events.
     The library records a one-shot event pair around its next GEMM kernel, so each projection call
@@ -406,8 +505,7 @@ def _hook_block(blk, ev_pairs, M):
     def arm(proj, n_out):
         if blk._ev_sink is None:
             return
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record(); b.record()                      # materialise the handles
+        a, b = _event_pool.pop()
         h.nf4ll_kernel_events(a.cuda_event, b.cuda_event)
         blk._ev_sink.append((a, b, 2 * M * proj.w.N * proj.w.K + 2 * M * 16 * n_out))
 
@@ -433,9 +531,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-stream", action="store_true", help="skip the small-batch weight-stream numbers")
+    ap.add_argument("--workload", default="mlp", choices=("mlp", "stack1.5b", "stack7b"),
+                    help="mlp = the default bench line (BASELINE config 1); stack* = configs 2 / 3")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "mlp":
+        run_stack(args)
     else:
         run_ours(args)
 

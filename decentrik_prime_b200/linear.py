@@ -59,6 +59,10 @@ class _DeviceState(threading.local):
 _state = _DeviceState()
 
 
+def _workspace_need(M, N, K, r):
+    return _lib.lib().nf4ll_workspace_bytes(M, N, K, r)
+
+
 def _workspace(device, nbytes):
     """Per-thread, per-device scratch that grows on demand (the library never allocates). Calls on
     different streams of the same thread must not overlap while sharing it; pass `workspace=` to
@@ -126,8 +130,7 @@ def forward(w: Nf4Weight, x, bias=None, lora=None, mask=None, keep_scale=1.0, ou
     keep, ref = _lora_struct(lora, mask, keep_scale)
     t = torch.empty(M, RANK, dtype=torch.float32, device=x.device) if (want_t and lora is not None) else None
     h = _lib.lib()
-    need = h.nf4ll_workspace_bytes(M, w.N, w.K, RANK if lora is not None else 0)
-    ws = _workspace(x.device, need) if workspace is None else workspace
+    ws = _workspace(x.device, _workspace_need(M, w.N, w.K, RANK if lora is not None else 0)) if workspace is None else workspace
     _lib.check(h.nf4ll_forward(ctypes.byref(w._c), x.data_ptr(), x.stride(0),
                                None if bias is None else bias.data_ptr(), ref,
                                None if t is None else t.data_ptr(), M, y.data_ptr(), y.stride(0),
@@ -151,8 +154,7 @@ def backward_dx(w: Nf4Weight, dy, lora=None, mask=None, keep_scale=1.0, out=None
     keep, ref = _lora_struct(lora, mask, keep_scale)
     u = torch.empty(M, RANK, dtype=torch.float32, device=dy.device) if (want_u and lora is not None) else None
     h = _lib.lib()
-    need = h.nf4ll_workspace_bytes(M, w.N, w.K, RANK if lora is not None else 0)
-    ws = _workspace(dy.device, need) if workspace is None else workspace
+    ws = _workspace(dy.device, _workspace_need(M, w.N, w.K, RANK if lora is not None else 0)) if workspace is None else workspace
     _lib.check(h.nf4ll_backward_dx(ctypes.byref(w._c), dy.data_ptr(), dy.stride(0), ref,
                                    None if u is None else u.data_ptr(), M, out.data_ptr(), out.stride(0),
                                    1 if accumulate else 0, ws.data_ptr(), ws.numel(),

@@ -1,0 +1,144 @@
+"""All seven projections of every decoder layer, packed the way the reference packs them, driven
+through the fused NF4 + LoRA linear: the projection stack of BASELINE configs 2 and 3.
+
+Per layer the 4-bit weights q, k, v, o, gate, up, down live in one flat PackedLayer buffer
+(k_nf4.repack_layer, same order and segment table as reference solution/k_nf4.py:126-173), so Q|K|V
+and gate|up are contiguous and the three attention projections write into column slices of one
+[M, hidden + 2*kv] buffer through the kernels' leading-dimension argument, as the reference's fused
+W_qkv GEMM does (solution/fast_qwen.py:405-413, 947). LoRA (r=16) sits on the projections named in
+`lora_on` (the task: q_proj and v_proj, solution/fast_qwen.py:93-99).
+
+Only the projections are this library's business. What sits between them in a transformer
+(normalisation, rotary embedding, attention, residuals) is stood in for by the cheapest
+differentiable PyTorch glue that keeps every projection's input and gradient non-trivial:
+
+    a   = q;  a[:, :kv] += k;  a[:, kv:2kv] += v        (stand-in for attention)
+    h1  = x + o_proj(a)
+    x'  = h1 + down_proj(silu(gate_proj(h1)) * up_proj(h1))
+
+The backward is written by hand like the reference's (solution/fast_qwen.py:1232-1384): dX of
+projections that share an input are accumulated in-kernel, LoRA gradients land in one flat bucket.
+Token rows are a packed varlen batch: M = sum of the sequence lengths (fast_qwen.py:803-876); the
+projections never need the sequence boundaries.
+"""
+
+import torch
+
+from . import blocks, k_nf4, linear, quantize
+
+
+def pack_lengths(batch, lo, hi, seed):
+    """Seeded sequence lengths, uniform in [lo, hi], and their packed row count."""
+    gen = torch.Generator().manual_seed(seed)
+    lens = torch.randint(lo, hi + 1, (batch,), generator=gen)
+    return lens.tolist(), int(lens.sum())
+
+
+class DecoderLayerProjections:
+    def __init__(self, hidden, inter, kv, seed, device, lora_on=("q_proj", "v_proj"), bucket=None, bias_qkv=True):
+        self.hidden, self.inter, self.kv = hidden, inter, kv
+        shapes = {"q_proj": (hidden, hidden), "k_proj": (kv, hidden), "v_proj": (kv, hidden), "o_proj": (hidden, hidden),
+                  "gate_proj": (inter, hidden), "up_proj": (inter, hidden), "down_proj": (hidden, inter)}
+        linears = {name: quantize.random_nf4_weight(*shapes[name], seed=seed * 16 + i, device=device)
+                   for i, name in enumerate(k_nf4.LAYER_WEIGHTS)}
+        self.layer, self.code2 = k_nf4.repack_layer(linears, torch.device(device))
+        self.proj = {}
+        gen = torch.Generator().manual_seed(seed * 16 + 9)
+        for i, name in enumerate(k_nf4.LAYER_WEIGHTS):
+            w = linear.Nf4Weight.from_layer(self.layer, name, self.code2)
+            bias = None
+            if bias_qkv and name in ("q_proj", "k_proj", "v_proj"):      # Qwen2 has biases on q, k, v only
+                bias = (torch.randn(shapes[name][0], generator=gen) * 0.1).half().to(device)
+            self.proj[name] = blocks.Projection(w, bias=bias, lora=name in lora_on, bucket=bucket, seed=seed * 16 + 10 + i)
+        self._saved = None
+
+    def grad_numel(self, lora_on):
+        return sum(blocks.lora_grad_numel(self.proj[n].w.N, self.proj[n].w.K) for n in lora_on)
+
+    def flops(self, M):
+        return sum(p.flops(M) for p in self.proj.values())
+
+    def forward(self, x, masks, keep_scale):
+        """x [M, hidden] fp16; masks: dict projection name -> uint8 keep-mask [M, K] for the LoRA ones."""
+        P, H, KV, M = self.proj, self.hidden, self.kv, x.shape[0]
+        qkv = torch.empty(M, H + 2 * KV, dtype=torch.float16, device=x.device)
+        P["q_proj"].forward(x, masks.get("q_proj"), keep_scale, out=qkv[:, :H])
+        P["k_proj"].forward(x, masks.get("k_proj"), keep_scale, out=qkv[:, H:H + KV])
+        P["v_proj"].forward(x, masks.get("v_proj"), keep_scale, out=qkv[:, H + KV:])
+        a = qkv[:, :H].clone()
+        a[:, :KV] += qkv[:, H:H + KV]
+        a[:, KV:2 * KV] += qkv[:, H + KV:]
+        h1 = x + P["o_proj"].forward(a, masks.get("o_proj"), keep_scale)
+        g = P["gate_proj"].forward(h1, masks.get("gate_proj"), keep_scale)
+        u = P["up_proj"].forward(h1, masks.get("up_proj"), keep_scale)
+        h = linear.swiglu_forward(g, u)
+        out = h1 + P["down_proj"].forward(h, masks.get("down_proj"), keep_scale)
+        self._saved = (g, u)
+        return out
+
+    def backward(self, dout, need_dx=True):
+        P, H, KV = self.proj, self.hidden, self.kv
+        g, u = self._saved
+        dh = P["down_proj"].backward(dout)
+        dg, du = linear.swiglu_backward(g, u, dh, inplace=True)
+        dh1 = P["gate_proj"].backward(dg)
+        dh1 = P["up_proj"].backward(du, out=dh1, accumulate=True)
+        dh1 += dout                                            # residual around the MLP
+        da = P["o_proj"].backward(dh1)
+        dqkv = torch.empty(da.shape[0], H + 2 * KV, dtype=torch.float16, device=da.device)
+        dqkv[:, :H] = da
+        dqkv[:, H:H + KV] = da[:, :KV]
+        dqkv[:, H + KV:] = da[:, KV:2 * KV]
+        dx = None
+        if need_dx:
+            dx = P["q_proj"].backward(dqkv[:, :H])
+            dx = P["k_proj"].backward(dqkv[:, H:H + KV], out=dx, accumulate=True)
+            dx = P["v_proj"].backward(dqkv[:, H + KV:], out=dx, accumulate=True)
+            dx += dh1                                          # residual around the attention stand-in
+        else:
+            # the first layer needs no d(input), only its LoRA gradients (solution/fast_qwen.py:1363-1364)
+            for name, sl in (("q_proj", slice(0, H)), ("k_proj", slice(H, H + KV)), ("v_proj", slice(H + KV, H + 2 * KV))):
+                P[name].backward(dqkv[:, sl], need_dx=False)
+        self._saved = None
+        return dx
+
+
+class ProjectionStack:
+    """n_layers DecoderLayerProjections with one LoRA gradient bucket (all-reduced once per step under DP)."""
+
+    def __init__(self, hidden, inter, kv, n_layers, device, seed=0, lora_on=("q_proj", "v_proj"), distinct_layers=None):
+        self.hidden, self.inter, self.kv, self.n_layers, self.lora_on = hidden, inter, kv, n_layers, tuple(lora_on)
+        per_layer = sum(blocks.lora_grad_numel(*{"q_proj": (hidden, hidden), "k_proj": (kv, hidden), "v_proj": (kv, hidden),
+                                                 "o_proj": (hidden, hidden), "gate_proj": (inter, hidden),
+                                                 "up_proj": (inter, hidden), "down_proj": (hidden, inter)}[n])
+                        for n in self.lora_on)
+        # `distinct_layers` < n_layers reuses weight sets round-robin (benchmarks of very deep stacks on a
+        # budget of set-up time); gradients then accumulate per distinct layer
+        n_distinct = n_layers if distinct_layers is None else min(distinct_layers, n_layers)
+        self.bucket = blocks.GradBucket(per_layer * n_distinct, device)
+        self._distinct = [DecoderLayerProjections(hidden, inter, kv, seed * 1000 + i, device, self.lora_on, self.bucket)
+                          for i in range(n_distinct)]
+        self.layers = [self._distinct[i % n_distinct] for i in range(n_layers)]
+        # saved activations live in the layer objects: a reused object cannot appear twice in one forward pass
+        self._shared = n_distinct < n_layers
+
+    def flops(self, M):
+        return sum(layer.flops(M) for layer in self.layers)
+
+    def step(self, x, dy, masks_per_layer, keep_scale, need_input_grad=False):
+        """Forward through all layers, then backward-dX through all layers. With shared weight sets
+        each layer runs forward+backward in turn instead (activation memory of one layer). The first
+        layer's d(input) is only computed on request (the reference skips it: nothing below needs it)."""
+        if self._shared:
+            dx = None
+            for i, layer in enumerate(self.layers):
+                out = layer.forward(x, masks_per_layer[i % len(masks_per_layer)], keep_scale)
+                dx = layer.backward(dy, need_dx=True)
+            return out, dx
+        acts = [x]
+        for i, layer in enumerate(self.layers):
+            acts.append(layer.forward(acts[-1], masks_per_layer[i], keep_scale))
+        d = dy
+        for i in reversed(range(self.n_layers)):
+            d = self.layers[i].backward(d, need_dx=i > 0 or need_input_grad)
+        return acts[-1], d
