@@ -133,13 +133,32 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Every wait on an mbarrier is bounded: after kSpinLimit failed polls (each poll itself suspends
 // for a hardware-chosen interval) the waiter gives up, and the kernel reports it through the
 // status word instead of hanging the GPU. `abort_flag` (shared memory) makes all other waiters of
 // the CTA give up quickly too.
+// The first polls use the non-blocking test_wait: try_wait costs a few hundred cycles even when the
+// phase is already complete, which is the common case on the MMA issuer's and the decoders'
+// critical paths; try_wait (which lets the hardware park the thread) only takes over for long waits.
 constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint32_t kFastPolls = 32;
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kFastPolls; ++i) {
+    if (mbar_test_wait(bar, parity)) return true;
+  }
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 63u) == 63u && *abort_flag) return false;

@@ -39,8 +39,8 @@ struct TileCfg {
   static constexpr int kTmemCols = BM_TILES * BN;        // 128, 256 or 512: a power of two >= 32
   static constexpr int kSmemBytes = 1024 /* alignment slack */ + kStages * (kABytes + kBBytes + kNibBytes + kAbsBytes) +
                                     1024 /* code2 */ + 512 /* barriers */;
-  // the LoRA operands are only read by the very first MMAs: they borrow the last activation stage
-  static_assert(kLoraLeftBytes + kLoraRightBytes <= kABytes, "LoRA operands must fit one activation stage");
+  // the LoRA operands are only read by the very first MMAs: they borrow the last weight-tile stage
+  static_assert(kLoraLeftBytes + kLoraRightBytes <= kBBytes, "LoRA operands must fit one weight stage");
 };
 
 template <int MODE, int BM_TILES, int BN>
@@ -59,11 +59,13 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
   uint8_t* sAbs = sNib + S * Cfg::kNibBytes;            // [S][BN] fp32 absmax
   float* sCode2 = reinterpret_cast<float*>(sAbs + S * Cfg::kAbsBytes);
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sCode2) + 1024);
-  uint8_t* sLL = sA + (S - 1) * Cfg::kABytes;           // LoRA left operand  [BM_TILES][128 x 16] (borrowed stage)
+  uint8_t* sLL = sB + (S - 1) * Cfg::kBBytes;           // LoRA left operand  [BM_TILES][128 x 16] (borrows the last weight stage)
   uint8_t* sLR = sLL + Cfg::kLoraLeftBytes;             // LoRA right operand [BN x 16] or [16 x BN]
   // barrier slots
-  uint64_t* full_a = bars;            // [S] activation boxes landed
-  uint64_t* full_b = bars + S;        // [S] dequantised tile written (one arrive per dequant warp)
+  // [S] stage ready for the tensor core: activation boxes landed (producer arrive + bytes) and the
+  // weight tile dequantised (one arrive per warp of the stage's team); one barrier, one wait per stage
+  uint64_t* full_a = bars;
+  uint64_t* full_b = full_a;
   uint64_t* empty = bars + 2 * S;     // [S] MMAs that read the stage have completed
   uint64_t* nib_full = bars + 3 * S;  // [S] packed codes landed and absmax written
   uint64_t* nib_empty = bars + 4 * S; // [S] dequant warps have read codes and absmax
@@ -97,11 +99,10 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(smem_u32(full_a + s), 1);
-      mbar_init(smem_u32(full_b + s), NDW);
+      mbar_init(smem_u32(full_a + s), 1 + NDW / 2);    // producer + one of the two dequant teams per stage
       mbar_init(smem_u32(empty + s), 1);
       mbar_init(smem_u32(nib_full + s), 3);        // TMA expect_tx arrive + the two absmax warps
-      mbar_init(smem_u32(nib_empty + s), NDW);
+      mbar_init(smem_u32(nib_empty + s), NDW / 2);
     }
     mbar_init(smem_u32(lora_done), 1);
     mbar_init(smem_u32(fix_go), 1);
@@ -109,7 +110,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
       mbar_init(smem_u32(fx_full + i), 1);
       mbar_init(smem_u32(fx_empty + i), NDW);
     }
-    mbar_init(smem_u32(lora_full), 2);
+    mbar_init(smem_u32(lora_full), NDW);
     mbar_init(smem_u32(acc_full), 1);
     mbar_init(smem_u32(pre_full), 1);
     mbar_init(smem_u32(pre_done), NDW);
@@ -147,10 +148,6 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
           tma_load_2d(smem_u32(sNib + s * Cfg::kNibBytes), &tmap_nib, static_cast<int>(o0 / 2), kb * 64, smem_u32(nib_full + s));
         }
         if (!wait_or_abort(smem_u32(empty + s), free_parity, ab, 0x0101)) break;
-        if (lora_here && i == S - 1) {
-          // the last activation stage is lent to the LoRA operands until the rank-16 MMAs have read them
-          if (!wait_or_abort(smem_u32(lora_done), 0, ab, 0x0103)) break;
-        }
         mbar_arrive_expect_tx(smem_u32(full_a + s), Cfg::kABytes);
 #pragma unroll
         for (int mt = 0; mt < BM_TILES; ++mt) {
@@ -205,7 +202,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
             const uint64_t ldesc = make_smem_desc(smem_u32(sLL + mt * 4096), 128, 256, kSwizzleNone);
             tc_mma_f16(tmem_base + mt * BN, ldesc, rdesc, idesc_main, 0u);
           }
-          tc_commit(smem_u32(lora_done));     // the borrowed activation stage may be overwritten after this
+          tc_commit(smem_u32(lora_done));     // the borrowed weight stage may be overwritten after this
           if (premask) {
             tc_commit(smem_u32(pre_full));
             ok = wait_or_abort(smem_u32(pre_done), 0, ab, 0x0202);
@@ -216,12 +213,13 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
       for (int i = 0; ok && i < nkb; ++i) {
         const int s = i % S;
         const uint32_t ph = (i / S) & 1;
-        if (!wait_or_abort(smem_u32(full_a + s), ph, ab, 0x0203) ||
-            !wait_or_abort(smem_u32(full_b + s), ph, ab, 0x0204)) {
+        if (!wait_or_abort(smem_u32(full_a + s), ph, ab, 0x0203)) {
           ok = false;
           break;
         }
         tc_fence_after();
+        const bool tr = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && i < 32;
+        if (tr) p.trace[i * 8 + 5] = clock64();
         const uint32_t a_base = smem_u32(sA + s * Cfg::kABytes);
         const uint32_t b_base = smem_u32(sB + s * Cfg::kBBytes);
 #pragma unroll
@@ -236,6 +234,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
           }
         }
         tc_commit(smem_u32(empty + s));     // frees the stage once these MMAs have read it
+        if (tr) p.trace[i * 8 + 6] = clock64();
       }
       tc_commit(smem_u32(acc_full));
       if (!ok) {
@@ -244,46 +243,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
       }
     }
   } else if (warp < 4) {
-    // ----------------------------------------------------------------------------- LoRA operand staging
-    if (lora_here) {
-      const int t = threadIdx.x - 64;   // 0..63
-      // left: rows m0.. of lora_left[M,16] (fp32), scaled and rounded to fp16 here;
-      // chunk (row, h) -> (row/8)*256 + h*128 + (row%8)*16
-      for (int c = t; c < BM_TILES * 128 * 2; c += 64) {
-        const int row = c >> 1, h = c & 1;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (m0 + row < p.M) {
-          const float4* src = reinterpret_cast<const float4*>(p.lora_left + (m0 + row) * 16 + h * 8);
-          const float4 a = __ldg(src), b = __ldg(src + 1);
-          v.x = pack_half2_rn(a.x * p.left_scale, a.y * p.left_scale);
-          v.y = pack_half2_rn(a.z * p.left_scale, a.w * p.left_scale);
-          v.z = pack_half2_rn(b.x * p.left_scale, b.y * p.left_scale);
-          v.w = pack_half2_rn(b.z * p.left_scale, b.w * p.left_scale);
-        }
-        const int mt = row >> 7, r = row & 127;
-        *reinterpret_cast<uint4*>(sLL + mt * 4096 + (r >> 3) * 256 + h * 128 + (r & 7) * 16) = v;
-      }
-      if (MODE == kFwd) {
-        // right: rows o0.. of B[N,16], same chunk layout
-        for (int c = t; c < BN * 2; c += 64) {
-          const int row = c >> 1, h = c & 1;
-          uint4 v = make_uint4(0, 0, 0, 0);
-          if (o0 + row < p.NO) v = __ldg(reinterpret_cast<const uint4*>(p.lora_right + (o0 + row) * 16 + h * 8));
-          *reinterpret_cast<uint4*>(sLR + (row >> 3) * 256 + h * 128 + (row & 7) * 16) = v;
-        }
-      } else {
-        // right: columns o0.. of A[16,K]; chunk (8 columns c8, rank row j) -> c8*256 + (j/8)*128 + (j%8)*16
-        for (int c = t; c < 16 * (BN / 8); c += 64) {
-          const int j = c / (BN / 8), c8 = c % (BN / 8);
-          uint4 v = make_uint4(0, 0, 0, 0);
-          if (o0 + c8 * 8 < p.NO) v = __ldg(reinterpret_cast<const uint4*>(p.lora_right + j * p.K + o0 + c8 * 8));
-          *reinterpret_cast<uint4*>(sLR + c8 * 256 + (j >> 3) * 128 + (j & 7) * 16) = v;
-        }
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(lora_full));
-    }
+    // ----------------------------------------------------------------------------- absmax helper
     // absmax of the stage's BN quantisation blocks: code2[q] * scale2 + offset2, rounded separately
     {
       constexpr int PER = BN / 64;                 // blocks per helper thread
@@ -341,73 +301,181 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
     const int q = warp & 3;               // tensor-memory lane quarter this warp may read
     bool ok = true;
 
-    if (premask) {
-      // The LoRA product is already in the accumulator: scale it by keep_scale * mask in place, so
-      // that the base GEMM then accumulates on top (dropout acts on the LoRA input only).
-      ok = wait_or_abort(smem_u32(pre_full), 0, ab, 0x0301);
-      if (ok) {
-        tc_fence_after();
-        constexpr int kChunks = BM_TILES * (BN / 32);
-        for (int u = ew >> 2; u < kChunks; u += NDW / 4) {
-          const int mt = u / (BN / 32), c = u % (BN / 32);
-          const int64_t row = m0 + mt * 128 + q * 32 + lane;
-          const int64_t col0 = o0 + c * 32;
-          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + mt * BN + c * 32;
-          uint32_t v[32];
-          __syncwarp();
-          tmem_ld32(taddr, v);
-          tmem_ld_wait();
-          uint32_t mk[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-          if (row < p.M && col0 < p.NO) {
-            const uint4* mp = reinterpret_cast<const uint4*>(p.mask + row * p.ld_mask + col0);
-            const uint4 a = __ldg(mp), b = __ldg(mp + 1);
-            mk[0] = a.x; mk[1] = a.y; mk[2] = a.z; mk[3] = a.w;
-            mk[4] = b.x; mk[5] = b.y; mk[6] = b.z; mk[7] = b.w;
-          }
+    // --- LoRA operands: staged by these warps while the first weight codes are still on their way.
+    // All loads are issued before the first store, so the cost is one trip to memory.
+    if (lora_here) {
+      constexpr int NT = NDW * 32;
+      constexpr int LEFT = BM_TILES * 128 * 2;         // 16-byte chunks (8 fp16) of the left operand
+      constexpr int RIGHT = BN * 2;
+      constexpr int LPT = (LEFT + NT - 1) / NT, RPT = (RIGHT + NT - 1) / NT;
+      float4 la[LPT], lb[LPT];
+      uint4 rv[RPT];
+      // left: rows m0.. of lora_left[M,16] (fp32), scaled and rounded to fp16 here
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const bool keep = ((mk[j >> 2] >> ((j & 3) * 8)) & 0xffu) != 0;
-            v[j] = keep ? __float_as_uint(__uint_as_float(v[j]) * p.keep_scale) : 0u;
-          }
-          tmem_st32(taddr, v);
-          tmem_st_wait();
+      for (int e = 0; e < LPT; ++e) {
+        const int c = d + e * NT, row = c >> 1, h = c & 1;
+        la[e] = make_float4(0.f, 0.f, 0.f, 0.f); lb[e] = la[e];
+        if (c < LEFT && m0 + row < p.M) {
+          const float4* src = reinterpret_cast<const float4*>(p.lora_left + (m0 + row) * 16 + h * 8);
+          la[e] = __ldg(src); lb[e] = __ldg(src + 1);
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(pre_done));
       }
+#pragma unroll
+      for (int e = 0; e < RPT; ++e) {
+        const int c = d + e * NT;
+        rv[e] = make_uint4(0, 0, 0, 0);
+        if (MODE == kFwd) {
+          const int row = c >> 1, h = c & 1;           // rows o0.. of B[N,16]
+          if (c < RIGHT && o0 + row < p.NO) rv[e] = __ldg(reinterpret_cast<const uint4*>(p.lora_right + (o0 + row) * 16 + h * 8));
+        } else {
+          const int j = c / (BN / 8), c8 = c % (BN / 8);   // columns o0.. of A[16,K]
+          if (c < RIGHT && o0 + c8 * 8 < p.NO) rv[e] = __ldg(reinterpret_cast<const uint4*>(p.lora_right + j * p.K + o0 + c8 * 8));
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < LPT; ++e) {
+        const int c = d + e * NT, row = c >> 1, h = c & 1;
+        if (c < LEFT) {
+          uint4 v;
+          v.x = pack_half2_rn(la[e].x * p.left_scale, la[e].y * p.left_scale);
+          v.y = pack_half2_rn(la[e].z * p.left_scale, la[e].w * p.left_scale);
+          v.z = pack_half2_rn(lb[e].x * p.left_scale, lb[e].y * p.left_scale);
+          v.w = pack_half2_rn(lb[e].z * p.left_scale, lb[e].w * p.left_scale);
+          // chunk (row, h) -> (row/8)*256 + h*128 + (row%8)*16 inside the 128-row tile
+          const int mt = row >> 7, r = row & 127;
+          *reinterpret_cast<uint4*>(sLL + mt * 4096 + (r >> 3) * 256 + h * 128 + (r & 7) * 16) = v;
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < RPT; ++e) {
+        const int c = d + e * NT;
+        if (c < RIGHT) {
+          if (MODE == kFwd) {
+            const int row = c >> 1, h = c & 1;
+            *reinterpret_cast<uint4*>(sLR + (row >> 3) * 256 + h * 128 + (row & 7) * 16) = rv[e];
+          } else {
+            // chunk (8 columns c8, rank row j) -> c8*256 + (j/8)*128 + (j%8)*16
+            const int j = c / (BN / 8), c8 = c % (BN / 8);
+            *reinterpret_cast<uint4*>(sLR + c8 * 256 + (j >> 3) * 128 + (j & 7) * 16) = rv[e];
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(lora_full));
     }
 
-    // --- dequantise one block per stage
-    uint32_t nib_off, row_off;     // this thread's 32 bytes of codes / 128-byte output row inside a stage
-    int key;
-    if (MODE == kFwd) {
-      nib_off = d * 32;
-      row_off = d * 128;
-      key = d & 7;
-    } else {
-      constexpr int SUB = BN / 64;
-      const int j = d % SUB, r = d / SUB;              // sub-tile (64 output columns) and row in the stage
-      nib_off = r * (BN / 2) + j * 32;
-      row_off = j * 8192 + r * 128;
-      key = r & 7;
+    // --- dequantise. The warps form two teams that take alternate stages, two blocks per thread, so
+    // that one team's barrier round trips (wait, proxy fence, arrive) overlap the other team's decode
+    // instead of leaving the integer pipe idle while all warps sit in the same wait.
+    constexpr int TEAM = BN / 2;                       // threads per team = blocks per thread pair
+    const int team = d / TEAM, tg = d % TEAM;
+    uint32_t nib_off[2], row_off[2];                   // 32 bytes of codes / 128-byte output row inside a stage
+    int key[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int blk = tg + h * TEAM;
+      if (MODE == kFwd) {
+        nib_off[h] = blk * 32;
+        row_off[h] = blk * 128;
+        key[h] = blk & 7;
+      } else {
+        constexpr int SUB = BN / 64;
+        const int j = blk % SUB, r = blk / SUB;        // sub-tile (64 output columns) and row in the stage
+        nib_off[h] = r * (BN / 2) + j * 32;
+        row_off[h] = j * 8192 + r * 128;
+        key[h] = r & 7;
+      }
     }
-    const uint32_t nib_base = smem_u32(sNib) + nib_off, abs_base = smem_u32(sAbs) + d * 4, b_base = smem_u32(sB) + row_off;
-    for (int i = 0; ok && i < nkb; ++i) {
+    const uint32_t nib_base = smem_u32(sNib), abs_base = smem_u32(sAbs) + tg * 4, b_base = smem_u32(sB);
+    auto dequant_stage = [&](int i) -> bool {
       const int s = i % S;
       const uint32_t ph = (i / S) & 1;
-      if (!wait_or_abort(smem_u32(nib_full + s), ph, ab, 0x0304)) { ok = false; break; }
-      const uint4 c0 = lds128(nib_base + s * Cfg::kNibBytes), c1 = lds128(nib_base + s * Cfg::kNibBytes + 16);
-      const float absmax = lds_f32(abs_base + s * Cfg::kAbsBytes);
-      if (!wait_or_abort(smem_u32(empty + s), ph ^ 1, ab, 0x0302)) { ok = false; break; }
-      if (!(p.debug & 1)) dequant_block_to_smem(b_base + s * Cfg::kBBytes, key, c0, c1, absmax);
+      const bool tr = p.trace && d == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && i < 32;
+      if (tr) p.trace[i * 8 + 0] = clock64();
+      if (!wait_or_abort(smem_u32(nib_full + s), ph, ab, 0x0304)) return false;
+      uint4 c[2][2];
+      float absmax[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        c[h][0] = lds128(nib_base + s * Cfg::kNibBytes + nib_off[h]);
+        c[h][1] = lds128(nib_base + s * Cfg::kNibBytes + nib_off[h] + 16);
+        absmax[h] = lds_f32(abs_base + s * Cfg::kAbsBytes + h * TEAM * 4);
+      }
+      if (tr) p.trace[i * 8 + 1] = clock64();
+      if (!wait_or_abort(smem_u32(empty + s), ph ^ 1, ab, 0x0302)) return false;
+      // the last stage holds the LoRA operands until the rank-16 MMAs have read them
+      if (lora_here && i == S - 1 && !wait_or_abort(smem_u32(lora_done), 0, ab, 0x0305)) return false;
+      if (tr) p.trace[i * 8 + 2] = clock64();
+      if (!(p.debug & 1)) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          dequant_block_to_smem(b_base + s * Cfg::kBBytes + row_off[h], key[h], c[h][0], c[h][1], absmax[h]);
+      }
+      if (tr) p.trace[i * 8 + 3] = clock64();
       fence_proxy_async_smem();      // generic-proxy stores -> visible to the tensor core's async proxy
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(smem_u32(full_b + s));
         mbar_arrive(smem_u32(nib_empty + s));      // codes and absmax of this stage are in registers / consumed
       }
+      if (tr) p.trace[i * 8 + 4] = clock64();
+      return true;
+    };
+
+    int i_next = team;
+    if (premask) {
+      // The LoRA product lands in the accumulator first and is scaled by keep_scale * mask in place, so
+      // that the base GEMM then accumulates on top (dropout acts on the LoRA input only). While the
+      // rank-16 MMAs run, each team already dequantises its first stage and the first mask bytes travel.
+      constexpr int kChunks = BM_TILES * (BN / 32);
+      constexpr int kStep = NDW / 4;
+      auto load_mask = [&](int u, uint4& a, uint4& b) {
+        a = make_uint4(0, 0, 0, 0); b = a;
+        if (u < kChunks) {
+          const int mt = u / (BN / 32), c = u % (BN / 32);
+          const int64_t row = m0 + mt * 128 + q * 32 + lane;
+          const int64_t col0 = o0 + c * 32;
+          if (row < p.M && col0 < p.NO) {
+            const uint4* mp = reinterpret_cast<const uint4*>(p.mask + row * p.ld_mask + col0);
+            a = __ldg(mp); b = __ldg(mp + 1);
+          }
+        }
+      };
+      uint4 ma, mb;
+      load_mask(ew >> 2, ma, mb);
+      if (i_next < nkb && i_next < S - 1) {
+        ok = dequant_stage(i_next);
+        i_next += 2;
+      }
+      if (ok) ok = wait_or_abort(smem_u32(pre_full), 0, ab, 0x0301);
+      if (ok) {
+        tc_fence_after();
+        for (int u = ew >> 2; u < kChunks; u += kStep) {
+          const int mt = u / (BN / 32), c = u % (BN / 32);
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + mt * BN + c * 32;
+          uint32_t v[32];
+          __syncwarp();
+          tmem_ld32(taddr, v);
+          uint4 na, nb;
+          load_mask(u + kStep, na, nb);                // next chunk's mask travels during this chunk
+          tmem_ld_wait();
+          const uint32_t mk[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const bool keep = ((mk[j >> 2] >> ((j & 3) * 8)) & 0xffu) != 0;
+            v[j] = keep ? __float_as_uint(__uint_as_float(v[j]) * p.keep_scale) : 0u;
+          }
+          tmem_st32(taddr, v);
+          ma = na; mb = nb;
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(pre_done));
+      }
     }
+    for (int i = i_next; ok && i < nkb; i += 2) ok = dequant_stage(i);
 
     // --- epilogue: tensor memory -> registers -> swizzled shared staging -> TMA store.
     // The operand rings are idle once the accumulator is complete, so they serve as staging space:
@@ -672,6 +740,7 @@ struct Plan {
 
 static thread_local int g_force_bm = 0, g_force_bn = 0, g_force_splits = 0;
 static thread_local int g_debug = 0;
+static thread_local long long* g_trace = nullptr;
 static thread_local cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;
 
 static int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
@@ -828,7 +897,7 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
   p.bias = static_cast<const __half*>(bias);
   p.accumulate = accumulate;
   p.has_lora = lora != nullptr;
-  p.splits = pl.splits; p.m_pad = pl.m_pad; p.status = status; p.debug = g_debug;
+  p.splits = pl.splits; p.m_pad = pl.m_pad; p.status = status; p.debug = g_debug; p.trace = g_trace;
   if (lora) {
     // rank-16 projection of the activation, fp32: T = drop(x).A^T (forward) or U = s.dy.B (backward);
     // it lands in the caller's t_out / u_out when given, else in the workspace
@@ -988,3 +1057,5 @@ extern "C" int nf4ll_forward_static(const nf4ll_mat* W, const void* x, int64_t l
   // stream before every launch that uses them, and every other byte is written before it is read.
   return run_gemm(kFwd, W, x, ldx, bias, lora, t_out, M, y, ldy, 0, scratch, NF4LL_STATIC_SCRATCH_BYTES, status, stream);
 }
+
+extern "C" void nf4ll_debug_trace(void* device_buffer) { nf4ll::g_trace = static_cast<long long*>(device_buffer); }

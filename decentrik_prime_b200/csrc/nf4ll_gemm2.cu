@@ -29,7 +29,7 @@ struct PairCfg {
   static constexpr int kTmemCols = BM_TILES * 256;
   static constexpr int kRingBytes = kStages * (kABytes + kBBytes);
   static constexpr int kSmemBytes = 1024 + kStages * (kABytes + kBBytes + kNibBytes + kAbsBytes) + 1024 + 512;
-  static_assert(kLoraLeftBytes + kLoraRightBytes <= kABytes, "LoRA operands must fit one activation stage");
+  static_assert(kLoraLeftBytes + kLoraRightBytes <= kBBytes, "LoRA operands must fit one weight stage");
   static_assert(kRingBytes >= kFixSlots * 16384, "fix-up ring must fit the operand rings");
 };
 
@@ -117,10 +117,12 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
   uint8_t* sAbs = sNib + S * Cfg::kNibBytes;            // [S][128] fp32
   float* sCode2 = reinterpret_cast<float*>(sAbs + S * Cfg::kAbsBytes);
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sCode2) + 1024);
-  uint8_t* sLL = sA + (S - 1) * Cfg::kABytes;           // LoRA operands borrow the last activation stage
+  uint8_t* sLL = sB + (S - 1) * Cfg::kBBytes;           // LoRA operands borrow the last weight-tile stage
   uint8_t* sLR = sLL + Cfg::kLoraLeftBytes;
-  uint64_t* full_a = bars;              // [S] this CTA's activation boxes landed
-  uint64_t* full_b = bars + S;          // [S] this CTA's blocks dequantised
+  // [S] this CTA's stage is ready: activation boxes landed (producer arrive + bytes), blocks dequantised
+  // (one arrive per warp of the stage's team) and, in rank 0, the relayed arrive of rank 1's own barrier
+  uint64_t* full_a = bars;
+  uint64_t* full_b = full_a;
   uint64_t* empty = bars + 2 * S;       // [S] the pair's MMAs on the stage are done (multicast commit)
   uint64_t* nib_full = bars + 3 * S;    // [S]
   uint64_t* nib_empty = bars + 4 * S;   // [S]
@@ -160,14 +162,13 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(smem_u32(full_a + s), 1);
-      mbar_init(smem_u32(full_b + s), NDW);
+      mbar_init(smem_u32(full_a + s), 1 + NDW / 2 + (rank == 0 ? 1 : 0));
       mbar_init(smem_u32(empty + s), 1);
       mbar_init(smem_u32(nib_full + s), 3);
-      mbar_init(smem_u32(nib_empty + s), NDW);
+      mbar_init(smem_u32(nib_empty + s), NDW / 2);
       mbar_init(smem_u32(peer_ready + s), 1);
     }
-    mbar_init(smem_u32(lora_full), 2);
+    mbar_init(smem_u32(lora_full), NDW);
     mbar_init(smem_u32(acc_full), 1);
     mbar_init(smem_u32(pre_full), 1);
     mbar_init(smem_u32(pre_done), NDW);
@@ -213,9 +214,7 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
           tma_load_2d(smem_u32(sNib + s * Cfg::kNibBytes), &tmap_nib, static_cast<int>(oh / 2), kb * 64, smem_u32(nib_full + s));
         }
         if (!wait_cluster_or_abort(smem_u32(empty + s), free_parity, ab, 0x0101)) break;
-        if (lora_here && i == S - 1) {
-          if (!wait_or_abort(smem_u32(lora_done), 0, ab, 0x0103)) break;
-        }
+        if (p.trace && blockIdx.x < 2 && blockIdx.y == 0 && blockIdx.z == 0 && i < 32) p.trace[i * 16 + 5 + blockIdx.x] = clock64();
         mbar_arrive_expect_tx(smem_u32(full_a + s), Cfg::kABytes);
 #pragma unroll
         for (int mt = 0; mt < BM_TILES; ++mt) {
@@ -266,11 +265,12 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
       for (int i = 0; ok && i < nkb; ++i) {
         const int s = i % S;
         const uint32_t ph = (i / S) & 1;
-        if (!wait_or_abort(smem_u32(full_a + s), ph, ab, 0x0213) || !wait_or_abort(smem_u32(full_b + s), ph, ab, 0x0214)) {
+        if (!wait_or_abort(smem_u32(full_a + s), ph, ab, 0x0213)) {
           ok = false;
           break;
         }
-        mbar_arrive_remote(map_to_cta(smem_u32(peer_ready + s), 0));
+        if (p.trace && blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0 && i < 32) p.trace[i * 16 + 7] = clock64();
+        mbar_arrive_remote(map_to_cta(smem_u32(full_a + s), 0));
       }
     } else if (lane == 0) {
       // ----------------------------------------------------------------------------- rank 0: the pair's MMA issuer
@@ -297,11 +297,10 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
       for (int i = 0; ok && i < nkb; ++i) {
         const int s = i % S;
         const uint32_t ph = (i / S) & 1;
-        if (!wait_or_abort(smem_u32(full_a + s), ph, ab, 0x0203) || !wait_or_abort(smem_u32(full_b + s), ph, ab, 0x0204) ||
-            !wait_cluster_or_abort(smem_u32(peer_ready + s), ph, ab, 0x0207)) {
-          ok = false;
-          break;
-        }
+        const bool tr = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && i < 32;
+        if (tr) p.trace[i * 16 + 0] = clock64();
+        if (!wait_cluster_or_abort(smem_u32(full_a + s), ph, ab, 0x0203)) { ok = false; break; }
+        if (tr) p.trace[i * 16 + 3] = clock64();
         tc_fence_after();
         const uint32_t a_base = smem_u32(sA + s * Cfg::kABytes);
         const uint32_t b_base = smem_u32(sB + s * Cfg::kBBytes);
@@ -318,6 +317,7 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
           }
         }
         tc_commit2(smem_u32(empty + s));
+        if (tr) p.trace[i * 16 + 4] = clock64();
       }
       tc_commit2(smem_u32(acc_full));
       if (!ok) {
@@ -325,45 +325,7 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
       }
     }
   } else if (warp < 4) {
-    // ----------------------------------------------------------------------------- LoRA operand staging, then absmax
-    if (lora_here) {
-      const int t = threadIdx.x - 64;
-      for (int c = t; c < BM_TILES * 128 * 2; c += 64) {
-        const int row = c >> 1, h = c & 1;
-        const int mt = row >> 7, r = row & 127;
-        const int64_t grow = m0 + mt * 256 + r;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (grow < p.M) {
-          const float4* src = reinterpret_cast<const float4*>(p.lora_left + grow * 16 + h * 8);
-          const float4 a = __ldg(src), b = __ldg(src + 1);
-          v.x = pack_half2_rn(a.x * p.left_scale, a.y * p.left_scale);
-          v.y = pack_half2_rn(a.z * p.left_scale, a.w * p.left_scale);
-          v.z = pack_half2_rn(b.x * p.left_scale, b.y * p.left_scale);
-          v.w = pack_half2_rn(b.z * p.left_scale, b.w * p.left_scale);
-        }
-        *reinterpret_cast<uint4*>(sLL + mt * 4096 + (r >> 3) * 256 + h * 128 + (r & 7) * 16) = v;
-      }
-      if (MODE == kFwd) {
-        // right: this CTA's 128 rows of B[N,16]
-        for (int c = t; c < 128 * 2; c += 64) {
-          const int row = c >> 1, h = c & 1;
-          uint4 v = make_uint4(0, 0, 0, 0);
-          if (oh + row < p.NO) v = __ldg(reinterpret_cast<const uint4*>(p.lora_right + (oh + row) * 16 + h * 8));
-          *reinterpret_cast<uint4*>(sLR + (row >> 3) * 256 + h * 128 + (row & 7) * 16) = v;
-        }
-      } else {
-        // right: this CTA's 128 columns of A[16,K]
-        for (int c = t; c < 16 * 16; c += 64) {
-          const int j = c / 16, c8 = c % 16;
-          uint4 v = make_uint4(0, 0, 0, 0);
-          if (oh + c8 * 8 < p.NO) v = __ldg(reinterpret_cast<const uint4*>(p.lora_right + j * p.K + oh + c8 * 8));
-          *reinterpret_cast<uint4*>(sLR + c8 * 256 + (j >> 3) * 128 + (j & 7) * 16) = v;
-        }
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(lora_full));
-    }
+    // ----------------------------------------------------------------------------- absmax helper
     {
       constexpr int PER = 2;                       // 128 blocks over 64 helper threads
       const int t = threadIdx.x - 64;
@@ -419,77 +381,156 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
     const int q = warp & 3;
     bool ok = true;
 
-    if (premask) {
-      ok = wait_or_abort(smem_u32(pre_full), 0, ab, 0x0301);
-      if (ok) {
-        tc_fence_after();
-        constexpr int kChunks = BM_TILES * (BN / 32);
-        for (int u = ew >> 2; u < kChunks; u += NDW / 4) {
-          const int mt = u / (BN / 32), c = u % (BN / 32);
-          const int64_t row = m0 + mt * 256 + q * 32 + lane;
-          const int64_t col0 = o0 + c * 32;
-          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + mt * BN + c * 32;
-          uint32_t v[32];
-          __syncwarp();
-          tmem_ld32(taddr, v);
-          tmem_ld_wait();
-          uint32_t mk[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-          if (row < p.M && col0 < p.NO) {
-            const uint4* mp = reinterpret_cast<const uint4*>(p.mask + row * p.ld_mask + col0);
-            const uint4 a = __ldg(mp), b = __ldg(mp + 1);
-            mk[0] = a.x; mk[1] = a.y; mk[2] = a.z; mk[3] = a.w;
-            mk[4] = b.x; mk[5] = b.y; mk[6] = b.z; mk[7] = b.w;
-          }
+    // --- LoRA operands: staged by these warps while the first weight codes are still on their way
+    // (all loads issued before the first store: one trip to memory)
+    if (lora_here) {
+      constexpr int NT = NDW * 32;
+      constexpr int LEFT = BM_TILES * 128 * 2;         // 16-byte chunks (8 fp16) of this CTA's left operand rows
+      constexpr int RIGHT = 128 * 2;                   // this CTA's 128 rows of B[N,16] / 128 columns of A[16,K]
+      constexpr int LPT = (LEFT + NT - 1) / NT, RPT = (RIGHT + NT - 1) / NT;
+      float4 la[LPT], lb[LPT];
+      uint4 rv[RPT];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const bool keep = ((mk[j >> 2] >> ((j & 3) * 8)) & 0xffu) != 0;
-            v[j] = keep ? __float_as_uint(__uint_as_float(v[j]) * p.keep_scale) : 0u;
-          }
-          tmem_st32(taddr, v);
-          tmem_st_wait();
+      for (int e = 0; e < LPT; ++e) {
+        const int c = d + e * NT, row = c >> 1, h = c & 1;
+        const int mt = row >> 7, r = row & 127;
+        const int64_t grow = m0 + mt * 256 + r;
+        la[e] = make_float4(0.f, 0.f, 0.f, 0.f); lb[e] = la[e];
+        if (c < LEFT && grow < p.M) {
+          const float4* src = reinterpret_cast<const float4*>(p.lora_left + grow * 16 + h * 8);
+          la[e] = __ldg(src); lb[e] = __ldg(src + 1);
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(pre_done));
       }
+#pragma unroll
+      for (int e = 0; e < RPT; ++e) {
+        const int c = d + e * NT;
+        rv[e] = make_uint4(0, 0, 0, 0);
+        if (MODE == kFwd) {
+          const int row = c >> 1, h = c & 1;
+          if (c < RIGHT && oh + row < p.NO) rv[e] = __ldg(reinterpret_cast<const uint4*>(p.lora_right + (oh + row) * 16 + h * 8));
+        } else {
+          const int j = c / 16, c8 = c % 16;
+          if (c < RIGHT && oh + c8 * 8 < p.NO) rv[e] = __ldg(reinterpret_cast<const uint4*>(p.lora_right + j * p.K + oh + c8 * 8));
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < LPT; ++e) {
+        const int c = d + e * NT, row = c >> 1, h = c & 1;
+        if (c < LEFT) {
+          uint4 v;
+          v.x = pack_half2_rn(la[e].x * p.left_scale, la[e].y * p.left_scale);
+          v.y = pack_half2_rn(la[e].z * p.left_scale, la[e].w * p.left_scale);
+          v.z = pack_half2_rn(lb[e].x * p.left_scale, lb[e].y * p.left_scale);
+          v.w = pack_half2_rn(lb[e].z * p.left_scale, lb[e].w * p.left_scale);
+          const int mt = row >> 7, r = row & 127;
+          *reinterpret_cast<uint4*>(sLL + mt * 4096 + (r >> 3) * 256 + h * 128 + (r & 7) * 16) = v;
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < RPT; ++e) {
+        const int c = d + e * NT;
+        if (c < RIGHT) {
+          if (MODE == kFwd) {
+            const int row = c >> 1, h = c & 1;
+            *reinterpret_cast<uint4*>(sLR + (row >> 3) * 256 + h * 128 + (row & 7) * 16) = rv[e];
+          } else {
+            const int j = c / 16, c8 = c % 16;
+            *reinterpret_cast<uint4*>(sLR + c8 * 256 + (j >> 3) * 128 + (j & 7) * 16) = rv[e];
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(lora_full));
     }
 
-    const int blk = d >> 1, half = d & 1;
+    // --- dequantise: two teams of four warps take alternate stages, one block per thread (see the
+    // single-CTA kernel for why the teams alternate)
+    const int team = d >> 7, blk = d & 127;
     uint32_t nib_off, row_off;
     int key;
     if (MODE == kFwd) {
-      nib_off = blk * 32 + half * 16;
+      nib_off = blk * 32;
       row_off = blk * 128;
       key = blk & 7;
     } else {
       const int j = blk % 2, r = blk / 2;
-      nib_off = r * 64 + j * 32 + half * 16;
+      nib_off = r * 64 + j * 32;
       row_off = j * 8192 + r * 128;
       key = r & 7;
     }
     const uint32_t nib_base = smem_u32(sNib) + nib_off, abs_base = smem_u32(sAbs) + blk * 4, b_base = smem_u32(sB) + row_off;
-    for (int i = 0; ok && i < nkb; ++i) {
+    auto dequant_stage = [&](int i) -> bool {
       const int s = i % S;
       const uint32_t ph = (i / S) & 1;
-      if (!wait_or_abort(smem_u32(nib_full + s), ph, ab, 0x0304)) { ok = false; break; }
-      const uint4 c = lds128(nib_base + s * Cfg::kNibBytes);
+      if (!wait_or_abort(smem_u32(nib_full + s), ph, ab, 0x0304)) return false;
+      const uint4 c0 = lds128(nib_base + s * Cfg::kNibBytes), c1 = lds128(nib_base + s * Cfg::kNibBytes + 16);
       const float absmax = lds_f32(abs_base + s * Cfg::kAbsBytes);
-      if (!wait_or_abort(smem_u32(empty + s), ph ^ 1, ab, 0x0302)) { ok = false; break; }
-      if (!(p.debug & 1)) {
-        const BlockTable tb = make_block_table(absmax);
-        const uint32_t row_addr = b_base + s * Cfg::kBBytes;
-        sts128(row_addr + (((half * 4 + 0) ^ key) << 4), decode_word(tb, c.x));
-        sts128(row_addr + (((half * 4 + 1) ^ key) << 4), decode_word(tb, c.y));
-        sts128(row_addr + (((half * 4 + 2) ^ key) << 4), decode_word(tb, c.z));
-        sts128(row_addr + (((half * 4 + 3) ^ key) << 4), decode_word(tb, c.w));
-      }
+      if (!wait_or_abort(smem_u32(empty + s), ph ^ 1, ab, 0x0302)) return false;
+      // the last stage holds the LoRA operands until the rank-16 MMAs have read them
+      if (lora_here && i == S - 1 && !wait_or_abort(smem_u32(lora_done), 0, ab, 0x0305)) return false;
+      if (!(p.debug & 1)) dequant_block_to_smem(b_base + s * Cfg::kBBytes, key, c0, c1, absmax);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(smem_u32(full_b + s));
         mbar_arrive(smem_u32(nib_empty + s));
       }
+      return true;
+    };
+
+    int i_next = team;
+    if (premask) {
+      // scale the LoRA product in the accumulator by keep_scale * mask before the base GEMM lands on it;
+      // each team dequantises its first stage and the first mask bytes travel while the rank-16 MMAs run
+      constexpr int kChunks = BM_TILES * (BN / 32);
+      constexpr int kStep = NDW / 4;
+      auto load_mask = [&](int u, uint4& a, uint4& b) {
+        a = make_uint4(0, 0, 0, 0); b = a;
+        if (u < kChunks) {
+          const int mt = u / (BN / 32), c = u % (BN / 32);
+          const int64_t row = m0 + mt * 256 + q * 32 + lane;
+          const int64_t col0 = o0 + c * 32;
+          if (row < p.M && col0 < p.NO) {
+            const uint4* mp = reinterpret_cast<const uint4*>(p.mask + row * p.ld_mask + col0);
+            a = __ldg(mp); b = __ldg(mp + 1);
+          }
+        }
+      };
+      uint4 ma, mb;
+      load_mask(ew >> 2, ma, mb);
+      if (i_next < nkb && i_next < S - 1) {
+        ok = dequant_stage(i_next);
+        i_next += 2;
+      }
+      if (ok) ok = wait_or_abort(smem_u32(pre_full), 0, ab, 0x0301);
+      if (ok) {
+        tc_fence_after();
+        for (int u = ew >> 2; u < kChunks; u += kStep) {
+          const int mt = u / (BN / 32), c = u % (BN / 32);
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + mt * BN + c * 32;
+          uint32_t v[32];
+          __syncwarp();
+          tmem_ld32(taddr, v);
+          uint4 na, nb;
+          load_mask(u + kStep, na, nb);
+          tmem_ld_wait();
+          const uint32_t mk[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const bool keep = ((mk[j >> 2] >> ((j & 3) * 8)) & 0xffu) != 0;
+            v[j] = keep ? __float_as_uint(__uint_as_float(v[j]) * p.keep_scale) : 0u;
+          }
+          tmem_st32(taddr, v);
+          ma = na; mb = nb;
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(pre_done));
+      }
     }
+    for (int i = i_next; ok && i < nkb; i += 2) ok = dequant_stage(i);
 
     // --- epilogue: tensor memory -> registers -> swizzled shared staging -> TMA store (see the single-CTA kernel)
     if (ok) ok = wait_or_abort(smem_u32(acc_full), 0, ab, 0x0303);

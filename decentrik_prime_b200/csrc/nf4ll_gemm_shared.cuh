@@ -36,6 +36,7 @@ struct GemmParams {
   int64_t m_pad;
   int32_t* status;
   int debug;               // timing experiments only: bit 0 skips the decode, bit 1 skips the MMAs
+  long long* trace;        // timing experiments only: per-iteration clock samples of CTA (0,0,0) / its peer
 };
 
 constexpr int kFixSlots = 8;     // 16 KB slots of the split-K fix-up ring (fits every tile shape's operand rings)
