@@ -135,10 +135,13 @@ class MlpBlock:
     def __init__(self, hidden, inter, seed, device, lora=True, bucket=None, fused_glue=True):
         self.hidden, self.inter = hidden, inter
         self.fused_glue = fused_glue      # library SwiGLU kernels (reference k_mlp.py) or plain PyTorch
+        grad_lo = bucket._at if bucket is not None else 0
         self.gate = make_projection(inter, hidden, seed * 10 + 1, device, lora=lora, bucket=bucket)
         self.up = make_projection(inter, hidden, seed * 10 + 2, device, lora=lora, bucket=bucket)
         self.down = make_projection(hidden, inter, seed * 10 + 3, device, lora=lora, bucket=bucket)
         self.projections = (self.gate, self.up, self.down)
+        # with a bucket the block's gradients are one contiguous slice: cleared by one fill per backward
+        self._grad_slice = bucket.flat[grad_lo:bucket._at] if (bucket is not None and lora) else None
         self._saved = None
 
     @staticmethod
@@ -156,9 +159,12 @@ class MlpBlock:
         self._saved = (g, u)
         return y
 
-    def backward(self, dy, need_dx=True):
+    def backward(self, dy, need_dx=True, accumulate_grads=False):
         g, u = self._saved
-        dh = self.down.backward(dy)
+        if self._grad_slice is not None and not accumulate_grads:
+            self._grad_slice.zero_()
+            accumulate_grads = True
+        dh = self.down.backward(dy, accumulate_grads=accumulate_grads)
         if self.fused_glue:
             dg, du = linear.swiglu_backward(g, u, dh, inplace=True)
         else:
@@ -167,9 +173,9 @@ class MlpBlock:
             dhf = dh.float()
             du = (dhf * gf * sig).half()
             dg = (dhf * u.float() * sig * (1.0 + gf * (1.0 - sig))).half()
-        dx = self.gate.backward(dg, need_dx=need_dx)
+        dx = self.gate.backward(dg, need_dx=need_dx, accumulate_grads=accumulate_grads)
         # d(input) of gate and up are summed into one buffer (the reference adds them in fp16,
         # solution/fast_qwen.py:1320-1323; here the add happens on the fp32 accumulator)
-        dx = self.up.backward(du, out=dx, accumulate=need_dx, need_dx=need_dx)
+        dx = self.up.backward(du, out=dx, accumulate=need_dx, need_dx=need_dx, accumulate_grads=accumulate_grads)
         self._saved = None
         return dx

@@ -856,7 +856,8 @@ static int check_lora(const nf4ll_lora* l, const char* who, bool need_mask_ld, i
 }
 
 int lora_down_launch(const void* act, int64_t ldact, const uint8_t* mask, int64_t ld_mask, float keep_scale,
-                     const void* R, float scale, int64_t M, int64_t C, void* t32, cudaStream_t stream);
+                     const void* R, float scale, int64_t M, int64_t C, void* t32, int* zero_ptr, int zero_words,
+                     cudaStream_t stream);
 int transpose_n16_launch(const void* B, void* Bt, int64_t N, cudaStream_t stream);
 int launch_pair(int mode, int bm_tiles, const CUtensorMap& map, const CUtensorMap& nib_map, const CUtensorMap& out_map,
                 const GemmParams& p, int64_t tiles_o, int64_t tiles_mp, int splits, cudaStream_t stream);
@@ -898,13 +899,20 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
   p.accumulate = accumulate;
   p.has_lora = lora != nullptr;
   p.splits = pl.splits; p.m_pad = pl.m_pad; p.status = status; p.debug = g_debug; p.trace = g_trace;
+  int* counters = nullptr;
+  int counter_words = 0;
+  if (pl.splits > 1) {
+    counters = reinterpret_cast<int*>(ws + pl.left_bytes + pl.bt_bytes);
+    counter_words = static_cast<int>(pl.counter_bytes / sizeof(int));
+  }
   if (lora) {
     // rank-16 projection of the activation, fp32: T = drop(x).A^T (forward) or U = s.dy.B (backward);
-    // it lands in the caller's t_out / u_out when given, else in the workspace
+    // it lands in the caller's t_out / u_out when given, else in the workspace. The same kernel
+    // resets the split-K tile counters of the GEMM that follows it on the stream.
     float* left = side_out ? static_cast<float*>(side_out) : reinterpret_cast<float*>(ws);
     if (mode == kFwd) {
       if (int rc = lora_down_launch(act, ldact, lora->mask, lora->ld_mask, lora->keep_scale, lora->A, 1.0f, M, W->K, left,
-                                    stream)) return rc;
+                                    counters, counter_words, stream)) return rc;
       p.lora_right = static_cast<const __half*>(lora->B);
       p.left_scale = lora->scale;
     } else {
@@ -914,7 +922,8 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
         if (int rc = transpose_n16_launch(lora->B, tmp, W->N, stream)) return rc;
         bt = tmp;
       }
-      if (int rc = lora_down_launch(act, ldact, nullptr, 0, 1.0f, bt, lora->scale, M, W->N, left, stream)) return rc;
+      if (int rc = lora_down_launch(act, ldact, nullptr, 0, 1.0f, bt, lora->scale, M, W->N, left, counters, counter_words,
+                                    stream)) return rc;
       p.lora_right = static_cast<const __half*>(lora->A);
       p.left_scale = 1.0f;
       p.mask = lora->mask; p.ld_mask = lora->ld_mask; p.keep_scale = lora->keep_scale;
@@ -926,9 +935,9 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
     return stream_forward_launch(W, act, ldact, bias, nullptr, nullptr, 0.f, M, out, ldo, stream);
   }
   if (pl.splits > 1) {
-    p.counters = reinterpret_cast<int*>(ws + pl.left_bytes + pl.bt_bytes);
+    p.counters = counters;
     p.partial = reinterpret_cast<float*>(ws + pl.left_bytes + pl.bt_bytes + pl.counter_bytes);
-    NF4LL_CUDA(cudaMemsetAsync(p.counters, 0, pl.counter_bytes, stream));
+    if (!lora) NF4LL_CUDA(cudaMemsetAsync(p.counters, 0, pl.counter_bytes, stream));
   }
   CUtensorMap map;
   if (int rc = make_tile_map(&map, act, M, KC, ldact, false)) return rc;

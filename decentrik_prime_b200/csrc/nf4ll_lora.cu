@@ -38,33 +38,62 @@ __device__ __forceinline__ uint4 drop8(uint4 raw, uint2 m, float keep_scale) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Row reduction: t[M,16] += scale * drop(act)[M,C] . R^T with R [16,C] row-major fp16.
-// One CTA = 32 rows x a range of the contraction, 8 warps; warp w takes the 32-column chunks
-// w, w+8, ... of the range. Per chunk a lane issues four 128-bit loads of act (rows g, g+8, g+16,
-// g+24) and two of R (rank rows g and g+8); a lane's 8 consecutive columns feed two MMAs with the
-// SAME column-to-slot assignment on both operands, so no shuffle or shared-memory transpose is
-// needed: out^T[16 ranks, 8 rows] = R[16, k] . act^T[k, 8 rows]. The warps' partial 16x32 results
-// are summed through shared memory and added to t with fp32 atomics (t is zeroed by the launcher),
-// which lets the contraction be split over enough CTAs to keep every SM's loads in flight.
+// Row reduction: t[M,16] = scale * drop(act)[M,C] . R^T with R [16,C] row-major fp16.
+// One CTA = 8*RG rows x a range of the contraction, 8 warps; warp w takes the 32-column chunks
+// w, w+8, ... of the range. Per chunk a lane issues RG 128-bit loads of act (rows g, g+8, ...) and
+// two of R (rank rows g and g+8); a lane's 8 consecutive columns feed two MMAs with the SAME
+// column-to-slot assignment on both operands, so no shuffle or shared-memory transpose is needed:
+// out^T[16 ranks, 8 rows] = R[16, k] . act^T[k, 8 rows]. The warps' partial results are summed
+// through shared memory. The contraction is split over grid.y so that every SM has loads in
+// flight; how the parts of one row block meet depends on COMBINE:
+//   kDownDirect   grid.y == 1, plain stores;
+//   kDownCluster  the grid.y CTAs of a row block form one thread-block cluster (at most 8); after a
+//                 cluster barrier rank 0 adds the others' partial sums out of their shared memory in
+//                 rank order and stores: no zero-fill, no atomics, bit-reproducible;
+//   kDownAtomic   more than 8 parts (few rows, long contraction): fp32 atomics into t, which the
+//                 launcher zeroes first.
+// `zero_words` 32-bit words at `zero_ptr` are cleared by CTA (0,0): the caller's next kernel (the
+// split-K GEMM this product feeds) finds its tile counters reset without a separate memset.
 // ---------------------------------------------------------------------------------------------
 constexpr int kDownWarps = 8;
-constexpr int kDownRows = 32;
+constexpr int kDownDirect = 0, kDownCluster = 1, kDownAtomic = 2;
 
-__global__ void __launch_bounds__(kDownWarps * 32)
+__device__ __forceinline__ uint32_t down_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void down_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float down_peer_load(const float* local, uint32_t rank) {
+  uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(local)), r;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(r) : "memory");
+  return v;
+}
+
+template <int RG, int COMBINE, int NW>
+__global__ void __launch_bounds__(NW * 32)
 lora_down_kernel(const __half* __restrict__ act, int64_t ldact, const uint8_t* __restrict__ mask, int64_t ld_mask,
                  float keep_scale, const __half* __restrict__ R, float scale, int64_t M, int64_t C, int64_t c_per_cta,
-                 float* __restrict__ t32) {
-  __shared__ float part[kDownWarps][kDownRows][17];
+                 float* __restrict__ t32, int* __restrict__ zero_ptr, int zero_words) {
+  constexpr int ROWS = 8 * RG;
+  __shared__ float part[NW][ROWS][17];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int64_t m0 = static_cast<int64_t>(blockIdx.x) * kDownRows;
+  if (blockIdx.x == 0 && blockIdx.y == 0) {
+    for (int i = threadIdx.x; i < zero_words; i += NW * 32) zero_ptr[i] = 0;
+  }
+  const int64_t m0 = static_cast<int64_t>(blockIdx.x) * ROWS;
   const int64_t c_begin = static_cast<int64_t>(blockIdx.y) * c_per_cta;
   const int64_t c_end = (c_begin + c_per_cta < C) ? c_begin + c_per_cta : C;
-  const __half* ap[4];
-  const uint8_t* mp[4];
-  bool ok[4];
+  const __half* ap[RG];
+  const uint8_t* mp[RG];
+  bool ok[RG];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < RG; ++i) {
     const int64_t row = m0 + g + 8 * i;
     ok[i] = row < M;
     ap[i] = act + (ok[i] ? row : 0) * ldact;
@@ -72,44 +101,82 @@ lora_down_kernel(const __half* __restrict__ act, int64_t ldact, const uint8_t* _
   }
   const __half* r0p = R + static_cast<int64_t>(g) * C;
   const __half* r1p = R + static_cast<int64_t>(g + 8) * C;
-  float c[4][4];
+  float c[RG][4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < RG; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) c[i][j] = 0.f;
   const uint4 zero = make_uint4(0, 0, 0, 0);
-#pragma unroll 2
-  for (int64_t k = c_begin + static_cast<int64_t>(warp) * 32 + t * 8; k < c_end; k += kDownWarps * 32) {
-    uint4 x[4];
+  // U chunks per trip, every load of the trip issued before the first use: the loop is bound by the
+  // number of bytes a warp keeps in flight, not by arithmetic
+  constexpr int U = (RG == 2) ? 4 : 2;
+  for (int64_t k0 = c_begin + static_cast<int64_t>(warp) * 32 + t * 8; k0 < c_end; k0 += U * NW * 32) {
+    uint4 x[U][RG], ra[U], rb[U];
+    uint2 mk[U][RG];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) x[i] = ok[i] ? __ldg(reinterpret_cast<const uint4*>(ap[i] + k)) : zero;
-    const uint4 ra = __ldg(reinterpret_cast<const uint4*>(r0p + k));
-    const uint4 rb = __ldg(reinterpret_cast<const uint4*>(r1p + k));
-    if (mask) {
+    for (int u = 0; u < U; ++u) {
+      const int64_t k = k0 + u * NW * 32;
+      const bool in = k < c_end;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) x[i] = drop8(x[i], __ldg(reinterpret_cast<const uint2*>(mp[i] + k)), keep_scale);
+      for (int i = 0; i < RG; ++i) {
+        x[u][i] = (in && ok[i]) ? __ldg(reinterpret_cast<const uint4*>(ap[i] + k)) : zero;
+        mk[u][i] = (in && mask) ? __ldg(reinterpret_cast<const uint2*>(mp[i] + k)) : make_uint2(0, 0);
+      }
+      ra[u] = in ? __ldg(reinterpret_cast<const uint4*>(r0p + k)) : zero;
+      rb[u] = in ? __ldg(reinterpret_cast<const uint4*>(r1p + k)) : zero;
     }
-    // columns k..k+3 -> MMA slots (2t, 2t+1, 2t+8, 2t+9) of the first MMA, k+4..k+7 of the second
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      mma16816(c[i], ra.x, rb.x, ra.y, rb.y, x[i].x, x[i].y);
-      mma16816(c[i], ra.z, rb.z, ra.w, rb.w, x[i].z, x[i].w);
+    for (int u = 0; u < U; ++u) {
+      if (mask) {
+#pragma unroll
+        for (int i = 0; i < RG; ++i) x[u][i] = drop8(x[u][i], mk[u][i], keep_scale);
+      }
+      // columns k..k+3 -> MMA slots (2t, 2t+1, 2t+8, 2t+9) of the first MMA, k+4..k+7 of the second
+#pragma unroll
+      for (int i = 0; i < RG; ++i) {
+        mma16816(c[i], ra[u].x, rb[u].x, ra[u].y, rb[u].y, x[u][i].x, x[u][i].y);
+        mma16816(c[i], ra[u].z, rb[u].z, ra[u].w, rb[u].w, x[u][i].z, x[u][i].w);
+      }
     }
   }
   // accumulator layout: c[.][0], c[.][1] = (rank g, rows 2t, 2t+1); c[.][2], c[.][3] = (rank g+8, same rows)
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < RG; ++i) {
     part[warp][8 * i + 2 * t][g] = c[i][0];      part[warp][8 * i + 2 * t + 1][g] = c[i][1];
     part[warp][8 * i + 2 * t][g + 8] = c[i][2];  part[warp][8 * i + 2 * t + 1][g + 8] = c[i][3];
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < kDownRows * 16; idx += kDownWarps * 32) {
-    const int row = idx >> 4, j = idx & 15;
-    if (m0 + row < M) {
+  if (COMBINE == kDownCluster) {
+    // every CTA folds its warps' parts into part[0]; rank 0 then gathers the cluster's
+    for (int idx = threadIdx.x; idx < ROWS * 16; idx += NW * 32) {
+      const int row = idx >> 4, j = idx & 15;
       float v = 0.f;
 #pragma unroll
-      for (int w = 0; w < kDownWarps; ++w) v += part[w][row][j];
-      atomicAdd(t32 + (m0 + row) * 16 + j, v * scale);
+      for (int w = 0; w < NW; ++w) v += part[w][row][j];
+      part[0][row][j] = v;                       // read and written by this thread only
+    }
+    down_cluster_sync();
+    if (down_cluster_rank() == 0) {
+      for (int idx = threadIdx.x; idx < ROWS * 16; idx += NW * 32) {
+        const int row = idx >> 4, j = idx & 15;
+        if (m0 + row < M) {
+          float v = part[0][row][j];
+          for (uint32_t r = 1; r < gridDim.y; ++r) v += down_peer_load(&part[0][row][j], r);
+          t32[(m0 + row) * 16 + j] = v * scale;
+        }
+      }
+    }
+    down_cluster_sync();                         // peers keep their shared memory until rank 0 has read it
+  } else {
+    for (int idx = threadIdx.x; idx < ROWS * 16; idx += NW * 32) {
+      const int row = idx >> 4, j = idx & 15;
+      if (m0 + row < M) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) v += part[w][row][j];
+        if (COMBINE == kDownAtomic) atomicAdd(t32 + (m0 + row) * 16 + j, v * scale);
+        else t32[(m0 + row) * 16 + j] = v * scale;
+      }
     }
   }
 }
@@ -138,25 +205,55 @@ int transpose_n16_launch(const void* B, void* Bt, int64_t N, cudaStream_t stream
   return NF4LL_OK;
 }
 
-// R is [16,C] row-major. t32 (fp32 [M,16], required) = scale * (drop(act) . R^T).
+// R is [16,C] row-major. t32 (fp32 [M,16], required) = scale * (drop(act) . R^T). `zero_ptr` / `zero_words`:
+// optional 32-bit words the kernel clears on the way (see the kernel).
 int lora_down_launch(const void* act, int64_t ldact, const uint8_t* mask, int64_t ld_mask, float keep_scale,
-                     const void* R, float scale, int64_t M, int64_t C, void* t32, cudaStream_t stream) {
-  if (M == 0) return NF4LL_OK;
+                     const void* R, float scale, int64_t M, int64_t C, void* t32, int* zero_ptr, int zero_words,
+                     cudaStream_t stream) {
+  if (M == 0) {
+    if (zero_words > 0) NF4LL_CUDA(cudaMemsetAsync(zero_ptr, 0, sizeof(int) * zero_words, stream));
+    return NF4LL_OK;
+  }
   int dev = 0, sms = 148;
   NF4LL_CUDA(cudaGetDevice(&dev));
   NF4LL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const int64_t row_groups = (M + kDownRows - 1) / kDownRows;
+  const __half* a = static_cast<const __half*>(act);
+  const __half* r = static_cast<const __half*>(R);
+  float* t = static_cast<float*>(t32);
+  const int64_t groups16 = (M + 15) / 16;
+  if (groups16 * 4 >= 3 * static_cast<int64_t>(sms)) {
+    // enough rows for (nearly) one CTA per SM at 16 rows each: a CTA takes the whole contraction,
+    // sixteen warps deep, and stores its rows directly
+    lora_down_kernel<2, kDownDirect, 16><<<dim3(static_cast<unsigned>(groups16), 1), 16 * 32, 0, stream>>>(
+        a, ldact, mask, ld_mask, keep_scale, r, scale, M, C, C, t, zero_ptr, zero_words);
+    NF4LL_CUDA(cudaGetLastError());
+    return NF4LL_OK;
+  }
+  const int64_t row_groups = (M + 31) / 32;
   const int64_t units = (C + kDownWarps * 32 - 1) / (kDownWarps * 32);     // 256-column units
-  int64_t ks = (2 * static_cast<int64_t>(sms)) / row_groups;   // at most two CTAs per SM: one wave, no tail
+  int64_t ks = (2 * static_cast<int64_t>(sms)) / row_groups;     // at most two CTAs per SM: one wave, no tail
   if (ks > units) ks = units;
   if (ks < 1) ks = 1;
   const int64_t c_per_cta = (units + ks - 1) / ks * (kDownWarps * 32);
   ks = (C + c_per_cta - 1) / c_per_cta;
-  NF4LL_CUDA(cudaMemsetAsync(t32, 0, sizeof(float) * 16 * M, stream));
   dim3 grid(static_cast<unsigned>(row_groups), static_cast<unsigned>(ks));
-  lora_down_kernel<<<grid, kDownWarps * 32, 0, stream>>>(static_cast<const __half*>(act), ldact, mask, ld_mask,
-                                                        keep_scale, static_cast<const __half*>(R), scale, M, C,
-                                                        c_per_cta, static_cast<float*>(t32));
+  if (ks == 1) {
+    lora_down_kernel<4, kDownDirect, kDownWarps><<<grid, kDownWarps * 32, 0, stream>>>(
+        a, ldact, mask, ld_mask, keep_scale, r, scale, M, C, c_per_cta, t, zero_ptr, zero_words);
+  } else if (ks <= 8) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = dim3(kDownWarps * 32); cfg.dynamicSmemBytes = 0; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = static_cast<unsigned>(ks); attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    NF4LL_CUDA(cudaLaunchKernelEx(&cfg, lora_down_kernel<4, kDownCluster, kDownWarps>, a, ldact, mask, ld_mask, keep_scale, r,
+                                  scale, M, C, c_per_cta, t, zero_ptr, zero_words));
+  } else {
+    NF4LL_CUDA(cudaMemsetAsync(t32, 0, sizeof(float) * 16 * M, stream));
+    lora_down_kernel<4, kDownAtomic, kDownWarps><<<grid, kDownWarps * 32, 0, stream>>>(
+        a, ldact, mask, ld_mask, keep_scale, r, scale, M, C, c_per_cta, t, zero_ptr, zero_words);
+  }
   NF4LL_CUDA(cudaGetLastError());
   return NF4LL_OK;
 }
@@ -327,7 +424,7 @@ extern "C" int nf4ll_lora_down(const void* x, int64_t ldx, const uint8_t* mask, 
   if (int rc = require_sm100()) return rc;
   if (!t32) { set_detail("nf4ll_lora_down: t32 is required (t16 is optional)"); return NF4LL_ERR_NULL; }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (int rc = lora_down_launch(x, ldx, mask, ld_mask, keep_scale, A, 1.0f, M, K, t32, st)) return rc;
+  if (int rc = lora_down_launch(x, ldx, mask, ld_mask, keep_scale, A, 1.0f, M, K, t32, nullptr, 0, st)) return rc;
   if (t16 && M > 0) {
     const int64_t n = M * 16;
     scale_to_half_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(static_cast<const float*>(t32),

@@ -43,6 +43,7 @@ class DecoderLayerProjections:
                    for i, name in enumerate(k_nf4.LAYER_WEIGHTS)}
         self.layer, self.code2 = k_nf4.repack_layer(linears, torch.device(device))
         self.proj = {}
+        grad_lo = bucket._at if bucket is not None else 0
         gen = torch.Generator().manual_seed(seed * 16 + 9)
         for i, name in enumerate(k_nf4.LAYER_WEIGHTS):
             w = linear.Nf4Weight.from_layer(self.layer, name, self.code2)
@@ -50,6 +51,8 @@ class DecoderLayerProjections:
             if bias_qkv and name in ("q_proj", "k_proj", "v_proj"):      # Qwen2 has biases on q, k, v only
                 bias = (torch.randn(shapes[name][0], generator=gen) * 0.1).half().to(device)
             self.proj[name] = blocks.Projection(w, bias=bias, lora=name in lora_on, bucket=bucket, seed=seed * 16 + 10 + i)
+        # with a bucket the layer's gradients are one contiguous slice: cleared by one fill per backward
+        self._grad_slice = bucket.flat[grad_lo:bucket._at] if bucket is not None and bucket._at > grad_lo else None
         self._saved = None
 
     def grad_numel(self, lora_on):
@@ -76,29 +79,33 @@ class DecoderLayerProjections:
         self._saved = (g, u)
         return out
 
-    def backward(self, dout, need_dx=True):
+    def backward(self, dout, need_dx=True, accumulate_grads=False):
         P, H, KV = self.proj, self.hidden, self.kv
         g, u = self._saved
-        dh = P["down_proj"].backward(dout)
+        if self._grad_slice is not None and not accumulate_grads:
+            self._grad_slice.zero_()
+            accumulate_grads = True
+        ag = accumulate_grads
+        dh = P["down_proj"].backward(dout, accumulate_grads=ag)
         dg, du = linear.swiglu_backward(g, u, dh, inplace=True)
-        dh1 = P["gate_proj"].backward(dg)
-        dh1 = P["up_proj"].backward(du, out=dh1, accumulate=True)
+        dh1 = P["gate_proj"].backward(dg, accumulate_grads=ag)
+        dh1 = P["up_proj"].backward(du, out=dh1, accumulate=True, accumulate_grads=ag)
         dh1 += dout                                            # residual around the MLP
-        da = P["o_proj"].backward(dh1)
+        da = P["o_proj"].backward(dh1, accumulate_grads=ag)
         dqkv = torch.empty(da.shape[0], H + 2 * KV, dtype=torch.float16, device=da.device)
         dqkv[:, :H] = da
         dqkv[:, H:H + KV] = da[:, :KV]
         dqkv[:, H + KV:] = da[:, KV:2 * KV]
         dx = None
         if need_dx:
-            dx = P["q_proj"].backward(dqkv[:, :H])
-            dx = P["k_proj"].backward(dqkv[:, H:H + KV], out=dx, accumulate=True)
-            dx = P["v_proj"].backward(dqkv[:, H + KV:], out=dx, accumulate=True)
+            dx = P["q_proj"].backward(dqkv[:, :H], accumulate_grads=ag)
+            dx = P["k_proj"].backward(dqkv[:, H:H + KV], out=dx, accumulate=True, accumulate_grads=ag)
+            dx = P["v_proj"].backward(dqkv[:, H + KV:], out=dx, accumulate=True, accumulate_grads=ag)
             dx += dh1                                          # residual around the attention stand-in
         else:
             # the first layer needs no d(input), only its LoRA gradients (solution/fast_qwen.py:1363-1364)
             for name, sl in (("q_proj", slice(0, H)), ("k_proj", slice(H, H + KV)), ("v_proj", slice(H + KV, H + 2 * KV))):
-                P[name].backward(dqkv[:, sl], need_dx=False)
+                P[name].backward(dqkv[:, sl], need_dx=False, accumulate_grads=ag)
         self._saved = None
         return dx
 
