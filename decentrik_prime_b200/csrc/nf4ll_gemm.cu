@@ -108,7 +108,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
     mbar_init(smem_u32(fix_go), 1);
     for (int i = 0; i < kFixSlots; ++i) {
       mbar_init(smem_u32(fx_full + i), 1);
-      mbar_init(smem_u32(fx_empty + i), NDW);
+      mbar_init(smem_u32(fx_empty + i), p.coop ? 4 : NDW);   // a slot is read by one warp group (shared reduction) or by all
     }
     mbar_init(smem_u32(lora_full), NDW);
     mbar_init(smem_u32(acc_full), 1);
@@ -157,7 +157,28 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
       }
       if (p.splits > 1 && !*abort_flag && !(p.debug & 4)) {
         // split-K: if this CTA turns out to be the last of its tile, stream all slabs back in
-        if (wait_or_abort(smem_u32(fix_go), 0, ab, 0x0104) && *last_flag) {
+        if (wait_or_abort(smem_u32(fix_go), 0, ab, 0x0104) && p.coop && !*abort_flag) {
+          // shared reduction: this CTA owns every splits-th box of the tile and streams the other
+          // splits' partial sums of exactly those boxes back in
+          fence_proxy_async_all();
+          constexpr int NB = BM_TILES * (BN / 32);
+          int n = 0;
+          bool fine = true;
+          for (int b = split; fine && b < NB; b += p.splits) {
+            const int mt = b / (BN / 32), cb = b % (BN / 32);
+            const int64_t col0 = o0 + cb * 32;
+            if (col0 >= p.NO) continue;
+            for (int sp = 0; sp < p.splits; ++sp) {
+              if (sp == split) continue;
+              const int slot = n % kFixSlots;
+              if (!wait_or_abort(smem_u32(fx_empty + slot), ((n / kFixSlots) & 1) ^ 1, ab, 0x0105)) { fine = false; break; }
+              mbar_arrive_expect_tx(smem_u32(fx_full + slot), 16384);
+              tma_load_2d(smem_u32(smem) + slot * 16384, &tmap_out, static_cast<int>(col0),
+                          static_cast<int>(static_cast<int64_t>(sp) * p.m_pad + m0 + mt * 128), smem_u32(fx_full + slot));
+              ++n;
+            }
+          }
+        } else if (!p.coop && *last_flag) {
           fence_proxy_async_all();     // the other splits' slab writes were observed through ordinary loads / atomics
           int n = 0;
           bool fine = true;
@@ -493,7 +514,51 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
       const uint32_t row_addr = stage + r_in * 128;
       const int key = r_in & 7;
       const bool leader = (q == 0 && lane == 0);
-      for (int mt = grp; mt < BM_TILES; mt += G) {
+      if (!direct && p.coop) {
+        // shared reduction, first half: every box of the tile that another split owns goes to this
+        // split's slab as fp32, four boxes per staging round, rounds dealt to the warp groups in turn
+        constexpr int NB = BM_TILES * (BN / 32);
+        constexpr int SB = 4;
+        int f = 0, pending = 0;
+        uint32_t staged = 0;                         // box indices of the round, 8 bits each
+        auto flush = [&]() {
+          fence_proxy_async_smem();
+          named_barrier(bar_id, 128);
+          if (leader) {
+            for (int k = 0; k < pending; ++k) {
+              const int b = (staged >> (8 * k)) & 0xff;
+              const int mt = b / (BN / 32), cb = b % (BN / 32);
+              const int64_t col0 = o0 + cb * 32;
+              if (col0 < p.NO)
+                tma_store_2d(&tmap_out, stage + k * 16384, static_cast<int>(col0),
+                             static_cast<int>(static_cast<int64_t>(split) * p.m_pad + m0 + mt * 128));
+            }
+            bulk_commit();
+            bulk_wait_read_all();
+          }
+          named_barrier(bar_id, 128);
+          pending = 0; staged = 0;
+        };
+#pragma unroll 1
+        for (int b = 0; b < NB; ++b) {
+          if (b % p.splits == split) continue;
+          const int round = f / SB;
+          ++f;
+          if (round % G != grp) continue;
+          const int mt = b / (BN / 32), cb = b % (BN / 32);
+          uint32_t v[32];
+          __syncwarp();
+          tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + mt * BN + cb * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            sts128(row_addr + pending * 16384 + ((j ^ key) << 4), make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+          staged |= static_cast<uint32_t>(b) << (8 * pending);
+          if (++pending == SB) flush();
+        }
+        if (pending) flush();
+      }
+      for (int mt = grp; mt < BM_TILES && !(!direct && p.coop); mt += G) {
         const uint32_t tacc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + mt * BN;
         const int row_g = static_cast<int>(m0 + mt * 128);
         if (direct) {
@@ -578,7 +643,93 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
         __threadfence();
       }
     }
-    if (!direct && !(p.debug & 4)) {
+    if (!direct && p.coop && !(p.debug & 4)) {
+      // shared reduction, second half: once every split of this tile has published its slab, each
+      // split finishes the boxes it owns: its own partial sums straight from tensor memory plus the
+      // other splits' in ascending order (a fixed order: results do not depend on timing).
+      __threadfence();
+      named_barrier(1, NDW * 32);
+      if (d == 0) {
+        int* counter = p.counters + (static_cast<int64_t>(tile_m) * gridDim.x + tile_o);
+        __threadfence();
+        atomicAdd(counter, 1);
+        bool seen = false;
+        for (uint32_t i = 0; i < kCoopSpinLimit; ++i) {
+          if (ld_acquire_gpu(counter) >= p.splits) { seen = true; break; }
+          if ((i & 255u) == 255u && *abort_flag) break;
+          __nanosleep(32);
+        }
+        if (!seen) ab.raise(0x0306);
+        __threadfence();
+        mbar_arrive(smem_u32(fix_go));       // warp 0 starts streaming the other splits' boxes
+      }
+      named_barrier(1, NDW * 32);
+      if (!*abort_flag) {
+        constexpr int NB = BM_TILES * (BN / 32);
+        constexpr int G = NDW / 4;
+        const int grp = ew >> 2;
+        const int r_in = q * 32 + lane;
+        const uint32_t ring = smem_u32(smem);
+        int n = 0, mine = 0;
+        bool fine = true;
+#pragma unroll 1
+        for (int b = split; fine && b < NB; b += p.splits) {
+          const int mt = b / (BN / 32), cb = b % (BN / 32);
+          const int64_t col0 = o0 + cb * 32;
+          if (col0 >= p.NO) continue;
+          const int n0 = n;
+          n += p.splits - 1;
+          if ((mine++) % G != grp) continue;
+          uint32_t v[32];
+          __syncwarp();
+          tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + mt * BN + cb * 32, v);
+          tmem_ld_wait();
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          if (MODE == kFwd && p.bias) {
+#pragma unroll
+            for (int j8 = 0; j8 < 4; ++j8) {
+              const uint4 bb = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + j8 * 8));
+              const __half2* bh = reinterpret_cast<const __half2*>(&bb);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) { const float2 t2 = __half22float2(bh[j]); f[j8 * 8 + 2 * j] += t2.x; f[j8 * 8 + 2 * j + 1] += t2.y; }
+            }
+          }
+          for (int k = 0; k < p.splits - 1; ++k) {
+            const int nn = n0 + k, slot = nn % kFixSlots;
+            if (!wait_or_abort(smem_u32(fx_full + slot), (nn / kFixSlots) & 1, ab, 0x0305)) { fine = false; break; }
+            const uint32_t src = ring + slot * 16384 + r_in * 128;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint4 w = lds128(src + ((j ^ (r_in & 7)) << 4));
+              f[4 * j] += __uint_as_float(w.x); f[4 * j + 1] += __uint_as_float(w.y);
+              f[4 * j + 2] += __uint_as_float(w.z); f[4 * j + 3] += __uint_as_float(w.w);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(fx_empty + slot));
+          }
+          const int64_t row = m0 + mt * 128 + r_in;
+          if (fine && row < p.M) {
+            __half* dst = p.out + row * p.ldo + col0;
+#pragma unroll
+            for (int j8 = 0; j8 < 4; ++j8) {
+              float* g8 = f + j8 * 8;
+              if (MODE == kBwd && p.accumulate) {
+                const uint4 o = *reinterpret_cast<const uint4*>(dst + j8 * 8);
+                const __half2* oh = reinterpret_cast<const __half2*>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { const float2 of = __half22float2(oh[j]); g8[2 * j] += of.x; g8[2 * j + 1] += of.y; }
+              }
+              uint4 o;
+              o.x = pack_half2_rn(g8[0], g8[1]); o.y = pack_half2_rn(g8[2], g8[3]);
+              o.z = pack_half2_rn(g8[4], g8[5]); o.w = pack_half2_rn(g8[6], g8[7]);
+              *reinterpret_cast<uint4*>(dst + j8 * 8) = o;
+            }
+          }
+        }
+      }
+    } else if (!direct && !(p.debug & 4)) {
       // split-K fix-up: the last CTA of this output tile to finish sums all slabs in split order
       // (deterministic) and writes the fp16 result. Every dequant thread takes both barriers, also
       // after a failed wait, so that nobody is left behind at a barrier.
@@ -798,6 +949,17 @@ static int launch_cfg(const CUtensorMap& map, const CUtensorMap& nib_map, const 
   auto kernel = nf4_gemm_kernel<MODE, BM_TILES, BN>;
   NF4LL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
   dim3 grid(static_cast<unsigned>(pl.tiles_o), static_cast<unsigned>(pl.tiles_m), static_cast<unsigned>(pl.splits));
+  if (p.coop) {
+    // the splits of a tile wait for one another: only legal when the whole grid is resident at once
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = dim3(Cfg::kThreads); cfg.dynamicSmemBytes = Cfg::kSmemBytes; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    NF4LL_CUDA(cudaLaunchKernelEx(&cfg, kernel, map, nib_map, out_map, p));
+    return NF4LL_OK;
+  }
   kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map, nib_map, out_map, p);
   NF4LL_CUDA(cudaGetLastError());
   return NF4LL_OK;
@@ -899,6 +1061,11 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
   p.accumulate = accumulate;
   p.has_lora = lora != nullptr;
   p.splits = pl.splits; p.m_pad = pl.m_pad; p.status = status; p.debug = g_debug; p.trace = g_trace;
+  // one CTA per SM (shared memory): a split-K grid of at most `sms` CTAs is resident as a whole
+  {
+    const int64_t ctas = pl.tiles_o * pl.tiles_m * pl.splits * (pl.pair ? 2 : 1);
+    p.coop = (pl.splits > 1 && ctas <= sms && !(g_debug & 8)) ? 1 : 0;
+  }
   int* counters = nullptr;
   int counter_words = 0;
   if (pl.splits > 1) {

@@ -178,7 +178,7 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
     mbar_init(smem_u32(peer_pre), 1);
     for (int i = 0; i < kFixSlots; ++i) {
       mbar_init(smem_u32(fx_full + i), 1);
-      mbar_init(smem_u32(fx_empty + i), NDW);
+      mbar_init(smem_u32(fx_empty + i), p.coop ? 4 : NDW);   // a slot is read by one warp group (shared reduction) or by all
     }
     *abort_flag = 0;
     *last_flag = 0;
@@ -223,7 +223,27 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
         }
       }
       if (p.splits > 1 && !*abort_flag && !(p.debug & 4)) {
-        if (wait_or_abort(smem_u32(fix_go), 0, ab, 0x0104) && *last_flag) {
+        if (wait_or_abort(smem_u32(fix_go), 0, ab, 0x0104) && p.coop && !*abort_flag) {
+          // shared reduction (see the single-CTA kernel): stream the other splits' partial sums of the boxes this CTA owns
+          fence_proxy_async_all();
+          constexpr int NB = BM_TILES * (BN / 32);
+          int n = 0;
+          bool fine = true;
+          for (int b = split; fine && b < NB; b += p.splits) {
+            const int mt = b / (BN / 32), cb = b % (BN / 32);
+            const int64_t col0 = o0 + cb * 32;
+            if (col0 >= p.NO) continue;
+            for (int sp = 0; sp < p.splits; ++sp) {
+              if (sp == split) continue;
+              const int slot = n % kFixSlots;
+              if (!wait_or_abort(smem_u32(fx_empty + slot), ((n / kFixSlots) & 1) ^ 1, ab, 0x0105)) { fine = false; break; }
+              mbar_arrive_expect_tx(smem_u32(fx_full + slot), 16384);
+              tma_load_2d(smem_u32(smem) + slot * 16384, &tmap_out, static_cast<int>(col0),
+                          static_cast<int>(static_cast<int64_t>(sp) * p.m_pad + m0 + mt * 256), smem_u32(fx_full + slot));
+              ++n;
+            }
+          }
+        } else if (!p.coop && *last_flag) {
           fence_proxy_async_all();
           int n = 0;
           bool fine = true;
@@ -546,7 +566,52 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
       const uint32_t row_addr = stage + r_in * 128;
       const int key2 = r_in & 7;
       const bool leader = (q == 0 && lane == 0);
-      for (int u = grp; u < BM_TILES * HALVES; u += G) {
+      if (!direct && p.coop) {
+        // shared reduction, first half (see the single-CTA kernel): boxes owned by other splits go to this split's slab
+        constexpr int NB = BM_TILES * (BN / 32);
+        constexpr int SB = 4;
+        const uint32_t stage4 = smem_u32(smem) + grp * 65536;
+        const uint32_t row_addr4 = stage4 + r_in * 128;
+        int f = 0, pending = 0;
+        uint32_t staged = 0;
+        auto flush = [&]() {
+          fence_proxy_async_smem();
+          named_barrier(bar_id, 128);
+          if (leader) {
+            for (int k = 0; k < pending; ++k) {
+              const int b = (staged >> (8 * k)) & 0xff;
+              const int mt = b / (BN / 32), cb = b % (BN / 32);
+              const int64_t col0 = o0 + cb * 32;
+              if (col0 < p.NO)
+                tma_store_2d(&tmap_out, stage4 + k * 16384, static_cast<int>(col0),
+                             static_cast<int>(static_cast<int64_t>(split) * p.m_pad + m0 + mt * 256));
+            }
+            bulk_commit();
+            bulk_wait_read_all();
+          }
+          named_barrier(bar_id, 128);
+          pending = 0; staged = 0;
+        };
+#pragma unroll 1
+        for (int b = 0; b < NB; ++b) {
+          if (b % p.splits == split) continue;
+          const int round = f / SB;
+          ++f;
+          if (round % G != grp) continue;
+          const int mt = b / (BN / 32), cb = b % (BN / 32);
+          uint32_t v[32];
+          __syncwarp();
+          tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + mt * BN + cb * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            sts128(row_addr4 + pending * 16384 + ((j ^ key2) << 4), make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+          staged |= static_cast<uint32_t>(b) << (8 * pending);
+          if (++pending == SB) flush();
+        }
+        if (pending) flush();
+      }
+      for (int u = grp; u < BM_TILES * HALVES && !(!direct && p.coop); u += G) {
         const int mt = u / HALVES, ch = u % HALVES;
         const uint32_t tacc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + mt * BN + ch * 128;
         const int row_g = static_cast<int>(m0 + mt * 256);
@@ -629,7 +694,91 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
         __threadfence();
       }
     }
-    if (!direct && !(p.debug & 4)) {
+    if (!direct && p.coop && !(p.debug & 4)) {
+      // shared reduction, second half (see the single-CTA kernel)
+      __threadfence();
+      named_barrier(1, NDW * 32);
+      if (d == 0) {
+        int* counter = p.counters + ((static_cast<int64_t>(tile_m) * tiles_o + tile_o) * 2 + rank);
+        __threadfence();
+        atomicAdd(counter, 1);
+        bool seen = false;
+        for (uint32_t i = 0; i < kCoopSpinLimit; ++i) {
+          if (ld_acquire_gpu(counter) >= p.splits) { seen = true; break; }
+          if ((i & 255u) == 255u && *abort_flag) break;
+          __nanosleep(32);
+        }
+        if (!seen) ab.raise(0x0306);
+        __threadfence();
+        mbar_arrive(smem_u32(fix_go));
+      }
+      named_barrier(1, NDW * 32);
+      if (!*abort_flag) {
+        constexpr int NB = BM_TILES * (BN / 32);
+        constexpr int G = NDW / 4;
+        const int grp = ew >> 2;
+        const int r_in = q * 32 + lane;
+        const uint32_t ring = smem_u32(smem);
+        int n = 0, mine = 0;
+        bool fine = true;
+#pragma unroll 1
+        for (int b = split; fine && b < NB; b += p.splits) {
+          const int mt = b / (BN / 32), cb = b % (BN / 32);
+          const int64_t col0 = o0 + cb * 32;
+          if (col0 >= p.NO) continue;
+          const int n0 = n;
+          n += p.splits - 1;
+          if ((mine++) % G != grp) continue;
+          uint32_t v[32];
+          __syncwarp();
+          tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + mt * BN + cb * 32, v);
+          tmem_ld_wait();
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          if (MODE == kFwd && p.bias) {
+#pragma unroll
+            for (int j8 = 0; j8 < 4; ++j8) {
+              const uint4 bb = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + j8 * 8));
+              const __half2* bh = reinterpret_cast<const __half2*>(&bb);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) { const float2 t2 = __half22float2(bh[j]); f[j8 * 8 + 2 * j] += t2.x; f[j8 * 8 + 2 * j + 1] += t2.y; }
+            }
+          }
+          for (int k = 0; k < p.splits - 1; ++k) {
+            const int nn = n0 + k, slot = nn % kFixSlots;
+            if (!wait_or_abort(smem_u32(fx_full + slot), (nn / kFixSlots) & 1, ab, 0x0305)) { fine = false; break; }
+            const uint32_t src = ring + slot * 16384 + r_in * 128;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint4 w = lds128(src + ((j ^ (r_in & 7)) << 4));
+              f[4 * j] += __uint_as_float(w.x); f[4 * j + 1] += __uint_as_float(w.y);
+              f[4 * j + 2] += __uint_as_float(w.z); f[4 * j + 3] += __uint_as_float(w.w);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(fx_empty + slot));
+          }
+          const int64_t row = m0 + mt * 256 + r_in;
+          if (fine && row < p.M) {
+            __half* dst = p.out + row * p.ldo + col0;
+#pragma unroll
+            for (int j8 = 0; j8 < 4; ++j8) {
+              float* g8 = f + j8 * 8;
+              if (MODE == kBwd && p.accumulate) {
+                const uint4 o = *reinterpret_cast<const uint4*>(dst + j8 * 8);
+                const __half2* oh2 = reinterpret_cast<const __half2*>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { const float2 of = __half22float2(oh2[j]); g8[2 * j] += of.x; g8[2 * j + 1] += of.y; }
+              }
+              uint4 o;
+              o.x = pack_half2_rn(g8[0], g8[1]); o.y = pack_half2_rn(g8[2], g8[3]);
+              o.z = pack_half2_rn(g8[4], g8[5]); o.w = pack_half2_rn(g8[6], g8[7]);
+              *reinterpret_cast<uint4*>(dst + j8 * 8) = o;
+            }
+          }
+        }
+      }
+    } else if (!direct && !(p.debug & 4)) {
       // split-K fix-up, per CTA: the last CTA (over the splits) that owns these rows of this tile adds the slabs up
       __threadfence();
       named_barrier(1, NDW * 32);
@@ -726,13 +875,16 @@ static int launch_pair_cfg(const CUtensorMap& map, const CUtensorMap& nib_map, c
   cfg.blockDim = dim3(Cfg::kThreads);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // shared split-K reduction: the splits of a tile wait for one another, so the grid must be resident as a whole
+  attr[1].id = cudaLaunchAttributeCooperative;
+  attr[1].val.cooperative = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = p.coop ? 2 : 1;
   NF4LL_CUDA(cudaLaunchKernelEx(&cfg, kernel, map, nib_map, out_map, p));
   return NF4LL_OK;
 }

@@ -34,11 +34,14 @@ struct GemmParams {
   float* partial;          // [splits][M_pad][NO] fp32 when splits > 1
   int* counters;           // one per output tile when splits > 1 (zero on entry, zero on exit)
   int64_t m_pad;
+  int coop;                // split-K: every CTA of the grid is resident at once (cooperative launch), so the splits
+                           // of a tile share its reduction instead of leaving it to the last one to finish
   int32_t* status;
   int debug;               // timing experiments only: bit 0 skips the decode, bit 1 skips the MMAs
   long long* trace;        // timing experiments only: per-iteration clock samples of CTA (0,0,0) / its peer
 };
 
+constexpr uint32_t kCoopSpinLimit = 1u << 22;   // polls (each followed by a short sleep) of a tile counter before giving up
 constexpr int kFixSlots = 8;     // 16 KB slots of the split-K fix-up ring (fits every tile shape's operand rings)
 
 struct Abort {
@@ -49,6 +52,12 @@ struct Abort {
     if (status) atomicCAS(status, 0, code);
   }
 };
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, const Abort& ab, int code) {
   if (mbar_wait(bar, parity, ab.flag)) return true;
