@@ -261,32 +261,50 @@ int lora_down_launch(const void* act, int64_t ldact, const uint8_t* mask, int64_
 // ---------------------------------------------------------------------------------------------
 // Column reduction: out[c][j] (+)= scale * sum_m drop(act)[m][c] * side[m][j]   (j < 16)
 // as out^T[16, C] = side^T[16, M] . drop(act)[M, C]. One CTA = 64 columns x a range of rows, 4
-// warps. Per 64-row stage the act tile goes to shared memory (dropout applied on the way), side
-// goes there transposed and split into fp16 hi + lo parts (two MMAs recover ~22 mantissa bits),
-// warp w contracts rows 16w..16w+15 of the stage against all 64 columns (ldmatrix.trans delivers the
-// row-major act tile as the MMA's k-by-n operand). Row ranges of different CTAs are combined with
-// fp32 atomics, so the summation order across ranges is not fixed.
+// warps. The rows arrive in 64-row stages through a ring of shared-memory buffers filled by
+// cp.async (act, mask and side as they lie in memory, two stages always in flight per CTA and
+// several CTAs per SM: the kernel is a pass over act at memory speed). A stage is then prepared in
+// place - dropout applied to the act tile, side transposed and split into fp16 hi + lo parts (two
+// MMAs recover ~22 mantissa bits) - and warp w contracts rows 16w..16w+15 of it against all 64
+// columns (ldmatrix.trans delivers the row-major act tile as the MMA's k-by-n operand). Row ranges
+// of different CTAs are combined with fp32 atomics, so the summation order across ranges is not fixed.
 // out index = j * ld_j + c * ld_c: dA[16,K] uses (K, 1), dB[N,16] uses (1, 16).
 // ---------------------------------------------------------------------------------------------
 constexpr int kGradThreads = 128;
 constexpr int kGradCols = 64;
 constexpr int kGradStage = 64;
+constexpr int kGradRing = 3;
 constexpr int kActStride = 72;     // halves per shared row: 144 B keeps ldmatrix rows on distinct banks
+constexpr int kGradActBytes = kGradStage * kActStride * 2;
+constexpr int kGradMaskBytes = kGradStage * kGradCols;
+constexpr int kGradSideBytes = kGradStage * 16 * 4;
+constexpr int kGradStageBytes = kGradActBytes + kGradMaskBytes + kGradSideBytes;
+constexpr int kGradHiLoBytes = 2 * 16 * kActStride * 2;
+constexpr int kGradSmemBytes = kGradRing * kGradStageBytes + kGradHiLoBytes;
+static_assert(4 * 16 * (kGradCols + 1) * 4 <= kGradRing * kGradStageBytes, "the final reduction reuses the ring");
 
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
                : "r"(addr));
 }
+// 16 bytes global -> shared, or 16 zero bytes when `valid` is false (src must still be an address)
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-__global__ void __launch_bounds__(kGradThreads)
+__global__ void __launch_bounds__(kGradThreads, 4)
 lora_grad_kernel(const __half* __restrict__ act, int64_t ldact, const uint8_t* __restrict__ mask, int64_t ld_mask,
                  float keep_scale, const float* __restrict__ side, float scale, int64_t M, int64_t C, int64_t rows_per_cta,
                  float* __restrict__ out, int64_t ld_j, int64_t ld_c) {
-  __shared__ __align__(16) __half s_act[kGradStage][kActStride];
-  __shared__ __align__(16) __half s_hi[16][kActStride];
-  __shared__ __align__(16) __half s_lo[16][kActStride];
-  __shared__ float s_red[4][16][kGradCols + 1];
+  extern __shared__ __align__(16) uint8_t g_smem[];
+  const uint32_t ring = smem_u32(g_smem);
+  __half (*s_hi)[kActStride] = reinterpret_cast<__half (*)[kActStride]>(g_smem + kGradRing * kGradStageBytes);
+  __half (*s_lo)[kActStride] = s_hi + 16;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int64_t c0 = static_cast<int64_t>(blockIdx.x) * kGradCols;
@@ -298,51 +316,67 @@ lora_grad_kernel(const __half* __restrict__ act, int64_t ldact, const uint8_t* _
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
 
-  // software pipeline: the global loads of the next 64-row stage are in flight while this one is
-  // turned into MMAs, so a CTA always has its 12-16 KB of loads outstanding
-  uint4 pa[4];
-  uint2 pm[4];
-  float ps[8];
-  auto fetch = [&](int64_t r0) {
+  // one stage of loads: 64 rows x (128 B of act, 64 B of mask, 64 B of side), one commit group
+  auto issue = [&](int64_t r0, int slot) {
+    const uint32_t base = ring + slot * kGradStageBytes;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int idx = threadIdx.x + i * kGradThreads;
       const int r = idx >> 3, ch = idx & 7;
       const int64_t row = r0 + r, col = c0 + ch * 8;
-      pa[i] = make_uint4(0, 0, 0, 0);
-      pm[i] = make_uint2(0x01010101u, 0x01010101u);
-      if (row < r_end && col < C) {
-        pa[i] = __ldg(reinterpret_cast<const uint4*>(act + row * ldact + col));
-        if (mask) pm[i] = __ldg(reinterpret_cast<const uint2*>(mask + row * ld_mask + col));
+      const bool v = row < r_end && col < C;
+      cp_async16(base + r * (kActStride * 2) + ch * 16, v ? act + row * ldact + col : act, v);
+    }
+    if (mask) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int idx = threadIdx.x + i * kGradThreads;
+        const int r = idx >> 2, ch = idx & 3;
+        const int64_t row = r0 + r, col = c0 + ch * 16;
+        const bool v = row < r_end && col < C;
+        cp_async16(base + kGradActBytes + r * kGradCols + ch * 16, v ? mask + row * ld_mask + col : mask, v);
       }
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 2; ++i) {
       const int idx = threadIdx.x + i * kGradThreads;
-      const int r = idx >> 4, j = idx & 15;
-      ps[i] = (r0 + r < r_end) ? __ldg(side + (r0 + r) * 16 + j) : 0.f;
+      const int r = idx >> 2, ch = idx & 3;
+      const bool v = r0 + r < r_end;
+      cp_async16(base + kGradActBytes + kGradMaskBytes + r * 64 + ch * 16, v ? side + (r0 + r) * 16 + ch * 4 : side, v);
     }
+    cp_async_commit();
   };
-  if (r_begin < r_end) fetch(r_begin);
-  for (int64_t r0 = r_begin; r0 < r_end; r0 += kGradStage) {
-    // stage the act tile (dropout applied on the way): 64 rows x 8 chunks of 8 columns over 128 threads
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int idx = threadIdx.x + i * kGradThreads;
-      const int r = idx >> 3, ch = idx & 7;
-      *reinterpret_cast<uint4*>(&s_act[r][ch * 8]) = mask ? drop8(pa[i], pm[i], keep_scale) : pa[i];
+  for (int s0 = 0; s0 < kGradRing - 1; ++s0) issue(r_begin + s0 * kGradStage, s0);
+  int it = 0;
+  for (int64_t r0 = r_begin; r0 < r_end; r0 += kGradStage, ++it) {
+    issue(r0 + (kGradRing - 1) * kGradStage, (it + kGradRing - 1) % kGradRing);   // past the range: empty, zero-filled
+    cp_async_wait<kGradRing - 1>();
+    __syncthreads();
+    uint8_t* st = g_smem + (it % kGradRing) * kGradStageBytes;
+    if (mask) {
+      // dropout in place: 64 rows x 8 chunks of 8 columns over 128 threads
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int idx = threadIdx.x + i * kGradThreads;
+        const int r = idx >> 3, ch = idx & 7;
+        uint4* ap = reinterpret_cast<uint4*>(st + r * (kActStride * 2) + ch * 16);
+        const uint2 m = *reinterpret_cast<const uint2*>(st + kGradActBytes + r * kGradCols + ch * 8);
+        *ap = drop8(*ap, m, keep_scale);
+      }
     }
-    // stage side transposed, split into hi + lo: 64 rows x 16 = 1024 values over 128 threads
+    // side transposed, split into hi + lo: 64 rows x 16 = 1024 values over 128 threads
+    const float* sd = reinterpret_cast<const float*>(st + kGradActBytes + kGradMaskBytes);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int idx = threadIdx.x + i * kGradThreads;
       const int r = idx >> 4, j = idx & 15;
-      const __half hi = __float2half_rn(ps[i]);
+      const float v = sd[idx];
+      const __half hi = __float2half_rn(v);
       s_hi[j][r] = hi;
-      s_lo[j][r] = __float2half_rn(ps[i] - __half2float(hi));
+      s_lo[j][r] = __float2half_rn(v - __half2float(hi));
     }
     __syncthreads();
-    if (r0 + kGradStage < r_end) fetch(r0 + kGradStage);
     const int kb = warp * 16;      // this warp's 16 rows of the stage
     const uint32_t ah0 = *reinterpret_cast<const uint32_t*>(&s_hi[g][kb + 2 * t]);
     const uint32_t ah1 = *reinterpret_cast<const uint32_t*>(&s_hi[g + 8][kb + 2 * t]);
@@ -352,13 +386,14 @@ lora_grad_kernel(const __half* __restrict__ act, int64_t ldact, const uint8_t* _
     const uint32_t al1 = *reinterpret_cast<const uint32_t*>(&s_lo[g + 8][kb + 2 * t]);
     const uint32_t al2 = *reinterpret_cast<const uint32_t*>(&s_lo[g][kb + 2 * t + 8]);
     const uint32_t al3 = *reinterpret_cast<const uint32_t*>(&s_lo[g + 8][kb + 2 * t + 8]);
+    const uint32_t act_base = ring + (it % kGradRing) * kGradStageBytes;
 #pragma unroll
     for (int np = 0; np < 4; ++np) {     // pairs of 8-column tiles
       // matrices: (k 0-7, n 0-7), (k 8-15, n 0-7), (k 0-7, n 8-15), (k 8-15, n 8-15) of this pair
       const int mrow = kb + ((lane >> 3) & 1) * 8 + (lane & 7);
       const int mcol = np * 16 + (lane >> 4) * 8;
       uint32_t b0, b1, b2, b3;
-      ldmatrix_x4_trans(smem_u32(&s_act[mrow][mcol]), b0, b1, b2, b3);
+      ldmatrix_x4_trans(act_base + mrow * (kActStride * 2) + mcol * 2, b0, b1, b2, b3);
       mma16816(acc[2 * np], ah0, ah1, ah2, ah3, b0, b1);
       mma16816(acc[2 * np], al0, al1, al2, al3, b0, b1);
       mma16816(acc[2 * np + 1], ah0, ah1, ah2, ah3, b2, b3);
@@ -366,7 +401,10 @@ lora_grad_kernel(const __half* __restrict__ act, int64_t ldact, const uint8_t* _
     }
     __syncthreads();
   }
-  // combine the four warps' row slices, then add into the output
+  cp_async_wait<0>();
+  __syncthreads();
+  // combine the four warps' row slices (the ring is free now), then add into the output
+  float (*s_red)[16][kGradCols + 1] = reinterpret_cast<float (*)[16][kGradCols + 1]>(g_smem);
 #pragma unroll
   for (int n = 0; n < 8; ++n) {
     s_red[warp][g][n * 8 + 2 * t] = acc[n][0];
@@ -392,17 +430,18 @@ static int lora_grad_launch(const void* act, int64_t ldact, const uint8_t* mask,
   int dev = 0, sms = 148;
   NF4LL_CUDA(cudaGetDevice(&dev));
   NF4LL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  NF4LL_CUDA(cudaFuncSetAttribute(lora_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGradSmemBytes));
   const int64_t col_tiles = (C + kGradCols - 1) / kGradCols;
   const int64_t stages = (M + kGradStage - 1) / kGradStage;
-  int64_t msplit = (3 * static_cast<int64_t>(sms)) / col_tiles;    // at most three CTAs per SM: one wave, no tail
+  int64_t msplit = (3 * static_cast<int64_t>(sms)) / col_tiles;    // three CTAs per SM (shared memory): one wave, no tail
   if (msplit > stages) msplit = stages;
   if (msplit < 1) msplit = 1;
   const int64_t rows_per = (stages + msplit - 1) / msplit * kGradStage;
   msplit = (M + rows_per - 1) / rows_per;
   dim3 grid(static_cast<unsigned>(col_tiles), static_cast<unsigned>(msplit));
-  lora_grad_kernel<<<grid, kGradThreads, 0, stream>>>(static_cast<const __half*>(act), ldact, mask, ld_mask, keep_scale,
-                                                      static_cast<const float*>(side), scale, M, C, rows_per,
-                                                      static_cast<float*>(out), ld_j, ld_c);
+  lora_grad_kernel<<<grid, kGradThreads, kGradSmemBytes, stream>>>(static_cast<const __half*>(act), ldact, mask, ld_mask,
+                                                                   keep_scale, static_cast<const float*>(side), scale, M, C,
+                                                                   rows_per, static_cast<float*>(out), ld_j, ld_c);
   NF4LL_CUDA(cudaGetLastError());
   return NF4LL_OK;
 }
