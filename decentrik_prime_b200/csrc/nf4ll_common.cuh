@@ -10,6 +10,38 @@
 
 namespace nf4ll {
 
+// Launch configuration with the attributes this library uses: programmatic dependent launch (only
+// for kernels that call pdl_wait() first thing), an optional thread-block cluster, an optional
+// cooperative launch (whole grid resident at once; not combined with the programmatic attribute).
+struct PdlLaunch {
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attr[3];
+  PdlLaunch(dim3 grid, dim3 block, size_t smem, cudaStream_t stream, unsigned cluster_x = 0, unsigned cluster_y = 0,
+            bool cooperative = false) {
+    cfg = cudaLaunchConfig_t{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    int n = 0;
+    if (cluster_x || cluster_y) {
+      attr[n].id = cudaLaunchAttributeClusterDimension;
+      attr[n].val.clusterDim.x = cluster_x ? cluster_x : 1;
+      attr[n].val.clusterDim.y = cluster_y ? cluster_y : 1;
+      attr[n].val.clusterDim.z = 1;
+      ++n;
+    }
+    if (cooperative) {
+      attr[n].id = cudaLaunchAttributeCooperative;
+      attr[n].val.cooperative = 1;
+      ++n;
+    } else {
+      attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[n].val.programmaticStreamSerializationAllowed = 1;
+      ++n;
+    }
+    cfg.attrs = attr; cfg.numAttrs = n;
+  }
+};
+
+
 // ---------------------------------------------------------------------------------------------
 // Host-side error plumbing (definitions in nf4ll_api.cu)
 // ---------------------------------------------------------------------------------------------
@@ -105,6 +137,14 @@ __device__ __forceinline__ uint4 decode_word(const BlockTable& t, uint32_t w) {
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
 // ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch. A kernel launched through PdlLaunch may be set up on the SMs
+// while the kernel before it on the stream is still finishing; pdl_wait() blocks until that kernel
+// has completed and its writes are visible, and must come before the first access to global
+// memory. pdl_launch_dependents() lets the NEXT kernel's blocks start as soon as every block of this
+// one has called it (or exited). Both are no-ops for an ordinary launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -284,6 +324,32 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
 __host__ __device__ constexpr uint32_t make_idesc_f16(int m, int n, int a_mn, int b_mn) {
   return (1u << 4) | (static_cast<uint32_t>(a_mn) << 15) | (static_cast<uint32_t>(b_mn) << 16) |
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Warp-level pieces shared by the rank-16 LoRA kernels
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// drop(x) on 8 packed fp16 values: fp16(x * keep_scale) where the mask byte is non-zero, else 0
+// (reference solution/k_norm.py:49-53: scale in fp32, then one rounding to fp16).
+__device__ __forceinline__ uint4 drop8(uint4 raw, uint2 m, float keep_scale) {
+  uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  const uint32_t mw[2] = {m.x, m.y};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+    const bool k0 = ((mw[j >> 1] >> ((2 * j & 3) * 8)) & 0xffu) != 0;
+    const bool k1 = ((mw[j >> 1] >> (((2 * j + 1) & 3) * 8)) & 0xffu) != 0;
+    w[j] = pack_half2_rn(k0 ? v.x * keep_scale : 0.f, k1 ? v.y * keep_scale : 0.f);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 }  // namespace nf4ll

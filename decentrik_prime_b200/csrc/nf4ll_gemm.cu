@@ -51,6 +51,8 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
   constexpr int S = Cfg::kStages;
   constexpr int NDW = Cfg::kDequantWarps;
 
+  pdl_wait();                  // everything below may read what the previous kernel on the stream wrote
+  pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;                                   // [S][BM_TILES][128 rows][128 B]
@@ -949,18 +951,10 @@ static int launch_cfg(const CUtensorMap& map, const CUtensorMap& nib_map, const 
   auto kernel = nf4_gemm_kernel<MODE, BM_TILES, BN>;
   NF4LL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
   dim3 grid(static_cast<unsigned>(pl.tiles_o), static_cast<unsigned>(pl.tiles_m), static_cast<unsigned>(pl.splits));
-  if (p.coop) {
-    // the splits of a tile wait for one another: only legal when the whole grid is resident at once
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = grid; cfg.blockDim = dim3(Cfg::kThreads); cfg.dynamicSmemBytes = Cfg::kSmemBytes; cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeCooperative;
-    attr[0].val.cooperative = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
-    NF4LL_CUDA(cudaLaunchKernelEx(&cfg, kernel, map, nib_map, out_map, p));
-    return NF4LL_OK;
-  }
-  kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map, nib_map, out_map, p);
+  // split-K with a shared reduction: the splits of a tile wait for one another, which is only legal
+  // when the whole grid is resident at once (cooperative launch)
+  PdlLaunch lc(grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, 0, 0, p.coop != 0);
+  NF4LL_CUDA(cudaLaunchKernelEx(&lc.cfg, kernel, map, nib_map, out_map, p));
   NF4LL_CUDA(cudaGetLastError());
   return NF4LL_OK;
 }
@@ -1097,7 +1091,7 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
     }
     p.lora_left = left;
     if (mode == kFwd && M <= kStreamMaxRows && !g_force_bm && !g_force_bn && !g_force_splits)
-      return stream_forward_launch(W, act, ldact, bias, left, lora->B, lora->scale, M, out, ldo, stream);
+      return stream_forward_launch(W, act, ldact, bias, p.lora_left, lora->B, lora->scale, M, out, ldo, stream);
   } else if (mode == kFwd && M <= kStreamMaxRows && !g_force_bm && !g_force_bn && !g_force_splits) {
     return stream_forward_launch(W, act, ldact, bias, nullptr, nullptr, 0.f, M, out, ldo, stream);
   }

@@ -109,6 +109,8 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
   constexpr int NDW = Cfg::kDequantWarps;
   constexpr int BN = 256;                       // tile columns of the pair; this CTA dequantises 128 of them
 
+  pdl_wait();                  // everything below may read what the previous kernel on the stream wrote
+  pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;                                   // [S][BM_TILES][128 rows][128 B]
@@ -870,22 +872,9 @@ static int launch_pair_cfg(const CUtensorMap& map, const CUtensorMap& nib_map, c
   using Cfg = PairCfg<BM_TILES>;
   auto kernel = nf4_gemm_pair_kernel<MODE, BM_TILES>;
   NF4LL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(static_cast<unsigned>(2 * tiles_o), static_cast<unsigned>(tiles_mp), static_cast<unsigned>(splits));
-  cfg.blockDim = dim3(Cfg::kThreads);
-  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  // shared split-K reduction: the splits of a tile wait for one another, so the grid must be resident as a whole
-  attr[1].id = cudaLaunchAttributeCooperative;
-  attr[1].val.cooperative = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = p.coop ? 2 : 1;
-  NF4LL_CUDA(cudaLaunchKernelEx(&cfg, kernel, map, nib_map, out_map, p));
+  PdlLaunch lc(dim3(static_cast<unsigned>(2 * tiles_o), static_cast<unsigned>(tiles_mp), static_cast<unsigned>(splits)),
+               dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, 2, 1, p.coop != 0);
+  NF4LL_CUDA(cudaLaunchKernelEx(&lc.cfg, kernel, map, nib_map, out_map, p));
   return NF4LL_OK;
 }
 

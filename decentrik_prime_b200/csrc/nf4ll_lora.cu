@@ -14,29 +14,6 @@
 
 namespace nf4ll {
 
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// drop(x) on 8 packed fp16 values: fp16(x * keep_scale) where the mask byte is non-zero, else 0
-// (reference solution/k_norm.py:49-53: scale in fp32, then one rounding to fp16).
-__device__ __forceinline__ uint4 drop8(uint4 raw, uint2 m, float keep_scale) {
-  uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-  const uint32_t mw[2] = {m.x, m.y};
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
-    const bool k0 = ((mw[j >> 1] >> ((2 * j & 3) * 8)) & 0xffu) != 0;
-    const bool k1 = ((mw[j >> 1] >> (((2 * j + 1) & 3) * 8)) & 0xffu) != 0;
-    w[j] = pack_half2_rn(k0 ? v.x * keep_scale : 0.f, k1 ? v.y * keep_scale : 0.f);
-  }
-  return make_uint4(w[0], w[1], w[2], w[3]);
-}
-
 // ---------------------------------------------------------------------------------------------
 // Row reduction: t[M,16] = scale * drop(act)[M,C] . R^T with R [16,C] row-major fp16.
 // One CTA = 8*RG rows x a range of the contraction, 8 warps; warp w takes the 32-column chunks
@@ -79,6 +56,8 @@ __global__ void __launch_bounds__(NW * 32)
 lora_down_kernel(const __half* __restrict__ act, int64_t ldact, const uint8_t* __restrict__ mask, int64_t ld_mask,
                  float keep_scale, const __half* __restrict__ R, float scale, int64_t M, int64_t C, int64_t c_per_cta,
                  float* __restrict__ t32, int* __restrict__ zero_ptr, int zero_words) {
+  pdl_wait();
+  pdl_launch_dependents();
   constexpr int ROWS = 8 * RG;
   __shared__ float part[NW][ROWS][17];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -224,9 +203,9 @@ int lora_down_launch(const void* act, int64_t ldact, const uint8_t* mask, int64_
   if (groups16 * 4 >= 3 * static_cast<int64_t>(sms)) {
     // enough rows for (nearly) one CTA per SM at 16 rows each: a CTA takes the whole contraction,
     // sixteen warps deep, and stores its rows directly
-    lora_down_kernel<2, kDownDirect, 16><<<dim3(static_cast<unsigned>(groups16), 1), 16 * 32, 0, stream>>>(
-        a, ldact, mask, ld_mask, keep_scale, r, scale, M, C, C, t, zero_ptr, zero_words);
-    NF4LL_CUDA(cudaGetLastError());
+    PdlLaunch lc(dim3(static_cast<unsigned>(groups16), 1), dim3(16 * 32), 0, stream);
+    NF4LL_CUDA(cudaLaunchKernelEx(&lc.cfg, lora_down_kernel<2, kDownDirect, 16>, a, ldact, mask, ld_mask, keep_scale, r, scale, M, C,
+                                  C, t, zero_ptr, zero_words));
     return NF4LL_OK;
   }
   const int64_t row_groups = (M + 31) / 32;
@@ -301,6 +280,8 @@ __global__ void __launch_bounds__(kGradThreads, 4)
 lora_grad_kernel(const __half* __restrict__ act, int64_t ldact, const uint8_t* __restrict__ mask, int64_t ld_mask,
                  float keep_scale, const float* __restrict__ side, float scale, int64_t M, int64_t C, int64_t rows_per_cta,
                  float* __restrict__ out, int64_t ld_j, int64_t ld_c) {
+  pdl_wait();
+  pdl_launch_dependents();
   extern __shared__ __align__(16) uint8_t g_smem[];
   const uint32_t ring = smem_u32(g_smem);
   __half (*s_hi)[kActStride] = reinterpret_cast<__half (*)[kActStride]>(g_smem + kGradRing * kGradStageBytes);
@@ -439,10 +420,9 @@ static int lora_grad_launch(const void* act, int64_t ldact, const uint8_t* mask,
   const int64_t rows_per = (stages + msplit - 1) / msplit * kGradStage;
   msplit = (M + rows_per - 1) / rows_per;
   dim3 grid(static_cast<unsigned>(col_tiles), static_cast<unsigned>(msplit));
-  lora_grad_kernel<<<grid, kGradThreads, kGradSmemBytes, stream>>>(static_cast<const __half*>(act), ldact, mask, ld_mask,
-                                                                   keep_scale, static_cast<const float*>(side), scale, M, C,
-                                                                   rows_per, static_cast<float*>(out), ld_j, ld_c);
-  NF4LL_CUDA(cudaGetLastError());
+  PdlLaunch lc(grid, dim3(kGradThreads), kGradSmemBytes, stream);
+  NF4LL_CUDA(cudaLaunchKernelEx(&lc.cfg, lora_grad_kernel, static_cast<const __half*>(act), ldact, mask, ld_mask, keep_scale,
+                                static_cast<const float*>(side), scale, M, C, rows_per, static_cast<float*>(out), ld_j, ld_c));
   return NF4LL_OK;
 }
 

@@ -22,43 +22,82 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
                     pack_half2_rn(f[6], f[7]));
 }
 
+// sigmoid through the special-function unit: ex2.approx and rcp.approx, a few ulp of fp32 - far inside
+// the fp16 rounding of the results
+__device__ __forceinline__ float fast_sigmoid(float a) { return __fdividef(1.0f, 1.0f + __expf(-a)); }
+
+__device__ __forceinline__ uint4 swiglu_fwd8(const uint4& gv, const uint4& uv) {
+  float a[8], b[8], o[8];
+  unpack8(gv, a); unpack8(uv, b);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = a[j] * fast_sigmoid(a[j]) * b[j];
+  return pack8(o);
+}
+
+__device__ __forceinline__ void swiglu_bwd8(const uint4& gv, const uint4& uv, const uint4& dv, uint4& og4, uint4& ou4) {
+  float a[8], b[8], d[8], og[8], ou[8];
+  unpack8(gv, a); unpack8(uv, b); unpack8(dv, d);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float sig = fast_sigmoid(a[j]);
+    ou[j] = d[j] * (a[j] * sig);
+    og[j] = (d[j] * b[j]) * sig * (1.0f + a[j] * (1.0f - sig));
+  }
+  og4 = pack8(og); ou4 = pack8(ou);
+}
+
+// Both kernels are one pass at memory speed: a thread takes two 16-byte chunks per trip, all loads
+// of the trip issued before the arithmetic, so that every SM keeps enough bytes in flight.
 __global__ void __launch_bounds__(256)
 swiglu_fwd_kernel(const __half* __restrict__ g, int64_t ldg, const __half* __restrict__ u, int64_t ldu,
                   __half* __restrict__ h, int64_t ldh, int64_t M, int64_t chunks_per_row) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int64_t total = M * chunks_per_row;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += 2 * stride) {
+    const int64_t i2 = i + stride;
+    const bool two = i2 < total;
     const int64_t row = i / chunks_per_row, col = (i - row * chunks_per_row) * 8;
-    float a[8], b[8], o[8];
-    unpack8(*reinterpret_cast<const uint4*>(g + row * ldg + col), a);
-    unpack8(*reinterpret_cast<const uint4*>(u + row * ldu + col), b);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = a[j] / (1.0f + expf(-a[j])) * b[j];
-    *reinterpret_cast<uint4*>(h + row * ldh + col) = pack8(o);
+    const int64_t row2 = two ? i2 / chunks_per_row : row, col2 = two ? (i2 - row2 * chunks_per_row) * 8 : col;
+    const uint4 ga = __ldcs(reinterpret_cast<const uint4*>(g + row * ldg + col));
+    const uint4 ua = __ldcs(reinterpret_cast<const uint4*>(u + row * ldu + col));
+    const uint4 gb = __ldcs(reinterpret_cast<const uint4*>(g + row2 * ldg + col2));
+    const uint4 ub = __ldcs(reinterpret_cast<const uint4*>(u + row2 * ldu + col2));
+    *reinterpret_cast<uint4*>(h + row * ldh + col) = swiglu_fwd8(ga, ua);
+    if (two) *reinterpret_cast<uint4*>(h + row2 * ldh + col2) = swiglu_fwd8(gb, ub);
   }
 }
 
-// dg / du may alias g / u (in-place, as the reference overwrites [gate | up]).
+// dg / du may alias g / u (in-place, as the reference overwrites [gate | up]): a chunk is read in
+// full before it is written, by the same thread.
 __global__ void __launch_bounds__(256)
 swiglu_bwd_kernel(const __half* g, int64_t ldg, const __half* u, int64_t ldu, const __half* __restrict__ dh, int64_t lddh,
                   __half* dg, int64_t lddg, __half* du, int64_t lddu, int64_t M, int64_t chunks_per_row) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int64_t total = M * chunks_per_row;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += 2 * stride) {
+    const int64_t i2 = i + stride;
+    const bool two = i2 < total;
     const int64_t row = i / chunks_per_row, col = (i - row * chunks_per_row) * 8;
-    float a[8], b[8], d[8], og[8], ou[8];
-    unpack8(*reinterpret_cast<const uint4*>(g + row * ldg + col), a);
-    unpack8(*reinterpret_cast<const uint4*>(u + row * ldu + col), b);
-    unpack8(*reinterpret_cast<const uint4*>(dh + row * lddh + col), d);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float e = 1.0f + expf(-a[j]);
-      const float sig = 1.0f / e;
-      ou[j] = d[j] * (a[j] / e);
-      og[j] = (d[j] * b[j]) * sig * (1.0f + a[j] * (1.0f - sig));
+    const int64_t row2 = two ? i2 / chunks_per_row : row, col2 = two ? (i2 - row2 * chunks_per_row) * 8 : col;
+    const uint4 ga = *reinterpret_cast<const uint4*>(g + row * ldg + col);
+    const uint4 ua = *reinterpret_cast<const uint4*>(u + row * ldu + col);
+    const uint4 da = __ldcs(reinterpret_cast<const uint4*>(dh + row * lddh + col));
+    const uint4 gb = *reinterpret_cast<const uint4*>(g + row2 * ldg + col2);
+    const uint4 ub = *reinterpret_cast<const uint4*>(u + row2 * ldu + col2);
+    const uint4 db = __ldcs(reinterpret_cast<const uint4*>(dh + row2 * lddh + col2));
+    uint4 og, ou;
+    swiglu_bwd8(ga, ua, da, og, ou);
+    *reinterpret_cast<uint4*>(dg + row * lddg + col) = og;
+    *reinterpret_cast<uint4*>(du + row * lddu + col) = ou;
+    if (two) {
+      swiglu_bwd8(gb, ub, db, og, ou);
+      *reinterpret_cast<uint4*>(dg + row2 * lddg + col2) = og;
+      *reinterpret_cast<uint4*>(du + row2 * lddu + col2) = ou;
     }
-    *reinterpret_cast<uint4*>(dg + row * lddg + col) = pack8(og);
-    *reinterpret_cast<uint4*>(du + row * lddu + col) = pack8(ou);
   }
 }
 
@@ -75,7 +114,7 @@ static int grid_for(int64_t total, unsigned* blocks) {
   int dev = 0, sms = 148;
   NF4LL_CUDA(cudaGetDevice(&dev));
   NF4LL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  int64_t b = (total + 255) / 256;
+  int64_t b = (total + 511) / 512;              // two chunks per thread and trip
   const int64_t cap = static_cast<int64_t>(sms) * 8;
   *blocks = static_cast<unsigned>(b < cap ? b : cap);
   return NF4LL_OK;
@@ -94,9 +133,9 @@ extern "C" int nf4ll_swiglu_forward(const void* g, int64_t ldg, const void* u, i
   if (int rc = require_sm100()) return rc;
   unsigned blocks = 1;
   if (int rc = grid_for(M * (I / 8), &blocks)) return rc;
-  swiglu_fwd_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __half*>(g), ldg, static_cast<const __half*>(u), ldu, static_cast<__half*>(h), ldh, M, I / 8);
-  NF4LL_CUDA(cudaGetLastError());
+  PdlLaunch lc(dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream));
+  NF4LL_CUDA(cudaLaunchKernelEx(&lc.cfg, swiglu_fwd_kernel, static_cast<const __half*>(g), ldg, static_cast<const __half*>(u), ldu,
+                                static_cast<__half*>(h), ldh, M, I / 8));
   return NF4LL_OK;
 }
 
@@ -113,9 +152,9 @@ extern "C" int nf4ll_swiglu_backward(const void* g, int64_t ldg, const void* u, 
   if (int rc = require_sm100()) return rc;
   unsigned blocks = 1;
   if (int rc = grid_for(M * (I / 8), &blocks)) return rc;
-  swiglu_bwd_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __half*>(g), ldg, static_cast<const __half*>(u), ldu, static_cast<const __half*>(dh), lddh,
-      static_cast<__half*>(dg), lddg, static_cast<__half*>(du), lddu, M, I / 8);
-  NF4LL_CUDA(cudaGetLastError());
+  PdlLaunch lc(dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream));
+  NF4LL_CUDA(cudaLaunchKernelEx(&lc.cfg, swiglu_bwd_kernel, static_cast<const __half*>(g), ldg, static_cast<const __half*>(u), ldu,
+                                static_cast<const __half*>(dh), lddh, static_cast<__half*>(dg), lddg, static_cast<__half*>(du), lddu,
+                                M, I / 8));
   return NF4LL_OK;
 }
