@@ -342,7 +342,7 @@ def run_ours(args):
                              "launches_timed": n_kern, "avg_launch_us": kern_ms * 1e3 / max(n_kern, 1)},
                 "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "ms_per_step": e2e_ms / args.steps},
-                "gpu_launches": 20 * args.steps, "clocks": clocks}
+                "gpu_launches": 17 * args.steps, "clocks": clocks}
         if world == 1 and not args.no_stream:
             line["weight_stream"] = {"unit": "GB/s of NF4 bytes", "peak_gbs": pk["hbm_gbs"], "peak_source": pk["source"],
                                      "cases": weight_stream_numbers(dev, pk["hbm_gbs"])}

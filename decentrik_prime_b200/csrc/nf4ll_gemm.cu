@@ -241,8 +241,6 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
           break;
         }
         tc_fence_after();
-        const bool tr = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && i < 32;
-        if (tr) p.trace[i * 8 + 5] = clock64();
         const uint32_t a_base = smem_u32(sA + s * Cfg::kABytes);
         const uint32_t b_base = smem_u32(sB + s * Cfg::kBBytes);
 #pragma unroll
@@ -257,7 +255,6 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
           }
         }
         tc_commit(smem_u32(empty + s));     // frees the stage once these MMAs have read it
-        if (tr) p.trace[i * 8 + 6] = clock64();
       }
       tc_commit(smem_u32(acc_full));
       if (!ok) {
@@ -414,8 +411,6 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
     auto dequant_stage = [&](int i) -> bool {
       const int s = i % S;
       const uint32_t ph = (i / S) & 1;
-      const bool tr = p.trace && d == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && i < 32;
-      if (tr) p.trace[i * 8 + 0] = clock64();
       if (!wait_or_abort(smem_u32(nib_full + s), ph, ab, 0x0304)) return false;
       uint4 c[2][2];
       float absmax[2];
@@ -425,24 +420,20 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
         c[h][1] = lds128(nib_base + s * Cfg::kNibBytes + nib_off[h] + 16);
         absmax[h] = lds_f32(abs_base + s * Cfg::kAbsBytes + h * TEAM * 4);
       }
-      if (tr) p.trace[i * 8 + 1] = clock64();
       if (!wait_or_abort(smem_u32(empty + s), ph ^ 1, ab, 0x0302)) return false;
       // the last stage holds the LoRA operands until the rank-16 MMAs have read them
       if (lora_here && i == S - 1 && !wait_or_abort(smem_u32(lora_done), 0, ab, 0x0305)) return false;
-      if (tr) p.trace[i * 8 + 2] = clock64();
       if (!(p.debug & 1)) {
 #pragma unroll
         for (int h = 0; h < 2; ++h)
           dequant_block_to_smem(b_base + s * Cfg::kBBytes + row_off[h], key[h], c[h][0], c[h][1], absmax[h]);
       }
-      if (tr) p.trace[i * 8 + 3] = clock64();
       fence_proxy_async_smem();      // generic-proxy stores -> visible to the tensor core's async proxy
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(smem_u32(full_b + s));
         mbar_arrive(smem_u32(nib_empty + s));      // codes and absmax of this stage are in registers / consumed
       }
-      if (tr) p.trace[i * 8 + 4] = clock64();
       return true;
     };
 
@@ -893,7 +884,6 @@ struct Plan {
 
 static thread_local int g_force_bm = 0, g_force_bn = 0, g_force_splits = 0;
 static thread_local int g_debug = 0;
-static thread_local long long* g_trace = nullptr;
 static thread_local cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;
 
 static int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
@@ -1054,7 +1044,7 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
   p.bias = static_cast<const __half*>(bias);
   p.accumulate = accumulate;
   p.has_lora = lora != nullptr;
-  p.splits = pl.splits; p.m_pad = pl.m_pad; p.status = status; p.debug = g_debug; p.trace = g_trace;
+  p.splits = pl.splits; p.m_pad = pl.m_pad; p.status = status; p.debug = g_debug;
   // one CTA per SM (shared memory): a split-K grid of at most `sms` CTAs is resident as a whole
   {
     const int64_t ctas = pl.tiles_o * pl.tiles_m * pl.splits * (pl.pair ? 2 : 1);
@@ -1228,4 +1218,3 @@ extern "C" int nf4ll_forward_static(const nf4ll_mat* W, const void* x, int64_t l
   return run_gemm(kFwd, W, x, ldx, bias, lora, t_out, M, y, ldy, 0, scratch, NF4LL_STATIC_SCRATCH_BYTES, status, stream);
 }
 
-extern "C" void nf4ll_debug_trace(void* device_buffer) { nf4ll::g_trace = static_cast<long long*>(device_buffer); }

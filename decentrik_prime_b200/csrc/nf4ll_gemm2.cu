@@ -216,7 +216,6 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
           tma_load_2d(smem_u32(sNib + s * Cfg::kNibBytes), &tmap_nib, static_cast<int>(oh / 2), kb * 64, smem_u32(nib_full + s));
         }
         if (!wait_cluster_or_abort(smem_u32(empty + s), free_parity, ab, 0x0101)) break;
-        if (p.trace && blockIdx.x < 2 && blockIdx.y == 0 && blockIdx.z == 0 && i < 32) p.trace[i * 16 + 5 + blockIdx.x] = clock64();
         mbar_arrive_expect_tx(smem_u32(full_a + s), Cfg::kABytes);
 #pragma unroll
         for (int mt = 0; mt < BM_TILES; ++mt) {
@@ -291,7 +290,6 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
           ok = false;
           break;
         }
-        if (p.trace && blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0 && i < 32) p.trace[i * 16 + 7] = clock64();
         mbar_arrive_remote(map_to_cta(smem_u32(full_a + s), 0));
       }
     } else if (lane == 0) {
@@ -319,10 +317,7 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
       for (int i = 0; ok && i < nkb; ++i) {
         const int s = i % S;
         const uint32_t ph = (i / S) & 1;
-        const bool tr = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && i < 32;
-        if (tr) p.trace[i * 16 + 0] = clock64();
         if (!wait_cluster_or_abort(smem_u32(full_a + s), ph, ab, 0x0203)) { ok = false; break; }
-        if (tr) p.trace[i * 16 + 3] = clock64();
         tc_fence_after();
         const uint32_t a_base = smem_u32(sA + s * Cfg::kABytes);
         const uint32_t b_base = smem_u32(sB + s * Cfg::kBBytes);
@@ -339,7 +334,6 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
           }
         }
         tc_commit2(smem_u32(empty + s));
-        if (tr) p.trace[i * 16 + 4] = clock64();
       }
       tc_commit2(smem_u32(acc_full));
       if (!ok) {

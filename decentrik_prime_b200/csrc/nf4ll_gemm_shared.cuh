@@ -38,7 +38,6 @@ struct GemmParams {
                            // of a tile share its reduction instead of leaving it to the last one to finish
   int32_t* status;
   int debug;               // timing experiments only: bit 0 skips the decode, bit 1 skips the MMAs
-  long long* trace;        // timing experiments only: per-iteration clock samples of CTA (0,0,0) / its peer
 };
 
 constexpr uint32_t kCoopSpinLimit = 1u << 22;   // polls (each followed by a short sleep) of a tile counter before giving up

@@ -276,19 +276,46 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// One column reduction. A launch carries up to two of them (dA and dB of one projection): column
+// tiles [0, tiles_first) of the grid belong to the first, the rest to the second.
+struct GradProblem {
+  const __half* act;
+  int64_t ldact;
+  const uint8_t* mask;
+  int64_t ld_mask;
+  float keep_scale;
+  const float* side;
+  float scale;
+  int64_t C;
+  int64_t rows_per_cta;
+  float* out;
+  int64_t ld_j, ld_c;
+};
+
 __global__ void __launch_bounds__(kGradThreads, 4)
-lora_grad_kernel(const __half* __restrict__ act, int64_t ldact, const uint8_t* __restrict__ mask, int64_t ld_mask,
-                 float keep_scale, const float* __restrict__ side, float scale, int64_t M, int64_t C, int64_t rows_per_cta,
-                 float* __restrict__ out, int64_t ld_j, int64_t ld_c) {
+lora_grad_kernel(const GradProblem first, const GradProblem second, int tiles_first, int64_t M) {
   pdl_wait();
   pdl_launch_dependents();
+  const bool is_first = static_cast<int>(blockIdx.x) < tiles_first;
+  const GradProblem& pb = is_first ? first : second;
+  const __half* __restrict__ act = pb.act;
+  const int64_t ldact = pb.ldact;
+  const uint8_t* __restrict__ mask = pb.mask;
+  const int64_t ld_mask = pb.ld_mask;
+  const float keep_scale = pb.keep_scale;
+  const float* __restrict__ side = pb.side;
+  const float scale = pb.scale;
+  const int64_t C = pb.C, rows_per_cta = pb.rows_per_cta;
+  float* __restrict__ out = pb.out;
+  const int64_t ld_j = pb.ld_j, ld_c = pb.ld_c;
+  if (static_cast<int64_t>(blockIdx.y) * rows_per_cta >= M) return;      // this reduction has fewer row ranges than the other
   extern __shared__ __align__(16) uint8_t g_smem[];
   const uint32_t ring = smem_u32(g_smem);
   __half (*s_hi)[kActStride] = reinterpret_cast<__half (*)[kActStride]>(g_smem + kGradRing * kGradStageBytes);
   __half (*s_lo)[kActStride] = s_hi + 16;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int64_t c0 = static_cast<int64_t>(blockIdx.x) * kGradCols;
+  const int64_t c0 = static_cast<int64_t>(is_first ? blockIdx.x : blockIdx.x - tiles_first) * kGradCols;
   const int64_t r_begin = static_cast<int64_t>(blockIdx.y) * rows_per_cta;
   const int64_t r_end = (r_begin + rows_per_cta < M) ? r_begin + rows_per_cta : M;
   float acc[8][4];
@@ -405,24 +432,50 @@ lora_grad_kernel(const __half* __restrict__ act, int64_t ldact, const uint8_t* _
   }
 }
 
-static int lora_grad_launch(const void* act, int64_t ldact, const uint8_t* mask, int64_t ld_mask, float keep_scale,
-                            const void* side, float scale, int64_t M, int64_t C, void* out, int64_t ld_j, int64_t ld_c,
-                            cudaStream_t stream) {
+struct GradPlan {
+  int64_t col_tiles, msplit, rows_per;
+};
+static GradPlan grad_plan(int64_t M, int64_t C, int64_t sms, int64_t other_tiles) {
+  GradPlan g;
+  g.col_tiles = (C + kGradCols - 1) / kGradCols;
+  const int64_t stages = (M + kGradStage - 1) / kGradStage;
+  // three CTAs per SM (shared memory): one wave over both reductions of the launch, no tail
+  int64_t msplit = (3 * sms + (g.col_tiles + other_tiles) - 1) / (g.col_tiles + other_tiles);
+  if (msplit > stages) msplit = stages;
+  if (msplit < 1) msplit = 1;
+  g.rows_per = (stages + msplit - 1) / msplit * kGradStage;
+  g.msplit = (M + g.rows_per - 1) / g.rows_per;
+  return g;
+}
+
+// dA = u^T . drop(x) (u carries the LoRA scale, reference solution/fast_qwen.py:1370-1371) and / or
+// dB = scale * dy^T . t (fast_qwen.py:1369), in one launch.
+static int lora_grads_launch(const void* dy, int64_t lddy, const void* x, int64_t ldx, const uint8_t* mask, int64_t ld_mask,
+                             float keep_scale, const void* t32, const void* u32, float scale, int64_t M, int64_t N, int64_t K,
+                             void* dA, void* dB, cudaStream_t stream) {
   int dev = 0, sms = 148;
   NF4LL_CUDA(cudaGetDevice(&dev));
   NF4LL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   NF4LL_CUDA(cudaFuncSetAttribute(lora_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGradSmemBytes));
-  const int64_t col_tiles = (C + kGradCols - 1) / kGradCols;
-  const int64_t stages = (M + kGradStage - 1) / kGradStage;
-  int64_t msplit = (3 * static_cast<int64_t>(sms)) / col_tiles;    // three CTAs per SM (shared memory): one wave, no tail
-  if (msplit > stages) msplit = stages;
-  if (msplit < 1) msplit = 1;
-  const int64_t rows_per = (stages + msplit - 1) / msplit * kGradStage;
-  msplit = (M + rows_per - 1) / rows_per;
-  dim3 grid(static_cast<unsigned>(col_tiles), static_cast<unsigned>(msplit));
+  const int64_t tiles_a = dA ? (K + kGradCols - 1) / kGradCols : 0;
+  const int64_t tiles_b = dB ? (N + kGradCols - 1) / kGradCols : 0;
+  GradProblem pa{}, pbb{};
+  int64_t ms = 1;
+  if (dA) {
+    const GradPlan g = grad_plan(M, K, sms, tiles_b);
+    pa = GradProblem{static_cast<const __half*>(x), ldx, mask, ld_mask, keep_scale, static_cast<const float*>(u32), 1.0f, K,
+                     g.rows_per, static_cast<float*>(dA), K, 1};
+    ms = g.msplit;
+  }
+  if (dB) {
+    const GradPlan g = grad_plan(M, N, sms, tiles_a);
+    pbb = GradProblem{static_cast<const __half*>(dy), lddy, nullptr, 0, 1.0f, static_cast<const float*>(t32), scale, N,
+                      g.rows_per, static_cast<float*>(dB), 1, 16};
+    if (g.msplit > ms) ms = g.msplit;
+  }
+  dim3 grid(static_cast<unsigned>(tiles_a + tiles_b), static_cast<unsigned>(ms));
   PdlLaunch lc(grid, dim3(kGradThreads), kGradSmemBytes, stream);
-  NF4LL_CUDA(cudaLaunchKernelEx(&lc.cfg, lora_grad_kernel, static_cast<const __half*>(act), ldact, mask, ld_mask, keep_scale,
-                                static_cast<const float*>(side), scale, M, C, rows_per, static_cast<float*>(out), ld_j, ld_c));
+  NF4LL_CUDA(cudaLaunchKernelEx(&lc.cfg, lora_grad_kernel, pa, pbb, static_cast<int>(tiles_a), M));
   return NF4LL_OK;
 }
 
@@ -472,17 +525,9 @@ extern "C" int nf4ll_lora_grads(const void* dy, int64_t lddy, const void* x, int
     return NF4LL_ERR_ALIGN;
   }
   if (int rc = require_sm100()) return rc;
-  if (dA) {
-    if (!accumulate) NF4LL_CUDA(cudaMemsetAsync(dA, 0, sizeof(float) * 16 * K, stream));
-    // dA = u^T . drop(x); u already carries the LoRA scale (reference solution/fast_qwen.py:1370-1371)
-    if (M > 0)
-      if (int rc = lora_grad_launch(x, ldx, mask, ld_mask, keep_scale, u32, 1.0f, M, K, dA, K, 1, stream)) return rc;
-  }
-  if (dB) {
-    if (!accumulate) NF4LL_CUDA(cudaMemsetAsync(dB, 0, sizeof(float) * 16 * N, stream));
-    // dB = scale * dy^T . t (reference solution/fast_qwen.py:1369)
-    if (M > 0)
-      if (int rc = lora_grad_launch(dy, lddy, nullptr, 0, 1.0f, t32, scale, M, N, dB, 1, 16, stream)) return rc;
-  }
+  if (dA && !accumulate) NF4LL_CUDA(cudaMemsetAsync(dA, 0, sizeof(float) * 16 * K, stream));
+  if (dB && !accumulate) NF4LL_CUDA(cudaMemsetAsync(dB, 0, sizeof(float) * 16 * N, stream));
+  if (M > 0 && (dA || dB))
+    if (int rc = lora_grads_launch(dy, lddy, x, ldx, mask, ld_mask, keep_scale, t32, u32, scale, M, N, K, dA, dB, stream)) return rc;
   return NF4LL_OK;
 }
