@@ -74,8 +74,13 @@ class LoraArgs(ctypes.Structure):
                 ("keep_scale", ctypes.c_float), ("Bt", ctypes.c_void_p)]
 
 
+class Segment(ctypes.Structure):
+    """struct nf4ll_segment (include/nf4ll.h)."""
+    _fields_ = [("rows", ctypes.c_int64), ("lora", ctypes.POINTER(LoraArgs)), ("t_out", ctypes.c_void_p)]
+
+
 _vp, _i64, _i32, _f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_float
-_MAT, _LORA = ctypes.POINTER(Nf4Mat), ctypes.POINTER(LoraArgs)
+_MAT, _LORA, _SEG = ctypes.POINTER(Nf4Mat), ctypes.POINTER(LoraArgs), ctypes.POINTER(Segment)
 
 # name -> (restype, argtypes); must list every symbol include/nf4ll.h declares.
 SIGNATURES = {
@@ -85,6 +90,7 @@ SIGNATURES = {
     "nf4ll_dequant": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp]),
     "nf4ll_workspace_bytes": (_i64, [_i64, _i64, _i64, _i32]),
     "nf4ll_forward": (_i32, [_MAT, _vp, _i64, _vp, _LORA, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp]),
+    "nf4ll_forward_multi": (_i32, [_MAT, _vp, _i64, _vp, _SEG, _i32, _i64, _vp, _i64, _vp, _i64, _vp, _vp]),
     "nf4ll_forward_static": (_i32, [_MAT, _vp, _i64, _vp, _LORA, _vp, _i64, _vp, _i64, _vp, _vp]),
     "nf4ll_backward_dx": (_i32, [_MAT, _vp, _i64, _LORA, _vp, _i64, _vp, _i64, _i32, _vp, _i64, _vp, _vp]),
     "nf4ll_lora_down": (_i32, [_vp, _i64, _vp, _i64, _f32, _vp, _f32, _i32, _i64, _i64, _vp, _vp, _vp]),

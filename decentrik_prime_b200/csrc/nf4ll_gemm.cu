@@ -94,7 +94,18 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
   const int kb_begin = static_cast<int>(static_cast<int64_t>(nkb_total) * split / p.splits);
   const int kb_end = static_cast<int>(static_cast<int64_t>(nkb_total) * (split + 1) / p.splits);
   const int nkb = kb_end - kb_begin;
-  const bool lora_here = p.has_lora && split == 0;
+  // the LoRA branch of this tile: the projection's, or the one of the stacked segment the tile lies in
+  const float* lora_left = p.lora_left;
+  const __half* lora_right = p.lora_right;
+  float left_scale = p.left_scale;
+  bool has_lora = p.has_lora != 0;
+  if (p.n_seg > 0) {
+    int sg = 0;
+    for (int i = 1; i < p.n_seg; ++i) if (static_cast<int64_t>(tile_o) * BN >= p.seg_begin[i]) sg = i;
+    lora_left = p.seg_left[sg]; lora_right = p.seg_right[sg]; left_scale = p.seg_scale[sg];
+    has_lora = lora_left != nullptr;
+  }
+  const bool lora_here = has_lora && split == 0;
   const bool premask = lora_here && MODE == kBwd && p.mask != nullptr;
 
   const Abort ab{abort_flag, p.status};
@@ -336,7 +347,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
         const int c = d + e * NT, row = c >> 1, h = c & 1;
         la[e] = make_float4(0.f, 0.f, 0.f, 0.f); lb[e] = la[e];
         if (c < LEFT && m0 + row < p.M) {
-          const float4* src = reinterpret_cast<const float4*>(p.lora_left + (m0 + row) * 16 + h * 8);
+          const float4* src = reinterpret_cast<const float4*>(lora_left + (m0 + row) * 16 + h * 8);
           la[e] = __ldg(src); lb[e] = __ldg(src + 1);
         }
       }
@@ -346,10 +357,10 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
         rv[e] = make_uint4(0, 0, 0, 0);
         if (MODE == kFwd) {
           const int row = c >> 1, h = c & 1;           // rows o0.. of B[N,16]
-          if (c < RIGHT && o0 + row < p.NO) rv[e] = __ldg(reinterpret_cast<const uint4*>(p.lora_right + (o0 + row) * 16 + h * 8));
+          if (c < RIGHT && o0 + row < p.NO) rv[e] = __ldg(reinterpret_cast<const uint4*>(lora_right + (o0 + row) * 16 + h * 8));
         } else {
           const int j = c / (BN / 8), c8 = c % (BN / 8);   // columns o0.. of A[16,K]
-          if (c < RIGHT && o0 + c8 * 8 < p.NO) rv[e] = __ldg(reinterpret_cast<const uint4*>(p.lora_right + j * p.K + o0 + c8 * 8));
+          if (c < RIGHT && o0 + c8 * 8 < p.NO) rv[e] = __ldg(reinterpret_cast<const uint4*>(lora_right + j * p.K + o0 + c8 * 8));
         }
       }
 #pragma unroll
@@ -357,10 +368,10 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
         const int c = d + e * NT, row = c >> 1, h = c & 1;
         if (c < LEFT) {
           uint4 v;
-          v.x = pack_half2_rn(la[e].x * p.left_scale, la[e].y * p.left_scale);
-          v.y = pack_half2_rn(la[e].z * p.left_scale, la[e].w * p.left_scale);
-          v.z = pack_half2_rn(lb[e].x * p.left_scale, lb[e].y * p.left_scale);
-          v.w = pack_half2_rn(lb[e].z * p.left_scale, lb[e].w * p.left_scale);
+          v.x = pack_half2_rn(la[e].x * left_scale, la[e].y * left_scale);
+          v.y = pack_half2_rn(la[e].z * left_scale, la[e].w * left_scale);
+          v.z = pack_half2_rn(lb[e].x * left_scale, lb[e].y * left_scale);
+          v.w = pack_half2_rn(lb[e].z * left_scale, lb[e].w * left_scale);
           // chunk (row, h) -> (row/8)*256 + h*128 + (row%8)*16 inside the 128-row tile
           const int mt = row >> 7, r = row & 127;
           *reinterpret_cast<uint4*>(sLL + mt * 4096 + (r >> 3) * 256 + h * 128 + (r & 7) * 16) = v;
@@ -1011,10 +1022,13 @@ int stream_forward_launch(const nf4ll_mat* W, const void* x, int64_t ldx, const 
                           const void* lora_b, float lora_scale, int64_t M, void* y, int64_t ldy, cudaStream_t stream);
 constexpr int64_t kStreamMaxRows = 16;     // at or below this many token rows the forward is a weight-streaming pass
 
+// `segments` (forward only): the weight is several projections stacked along N, each with its own
+// optional LoRA branch; `lora` / `side_out` are then unused.
 static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact, const void* bias,
                     const nf4ll_lora* lora, void* side_out, int64_t M, void* out, int64_t ldo, int accumulate,
-                    void* workspace, int64_t workspace_bytes, int32_t* status, void* stream_v) {
-  const char* who = mode == kFwd ? "nf4ll_forward" : "nf4ll_backward_dx";
+                    void* workspace, int64_t workspace_bytes, int32_t* status, void* stream_v,
+                    const nf4ll_segment* segments = nullptr, int n_segments = 0) {
+  const char* who = segments ? "nf4ll_forward_multi" : (mode == kFwd ? "nf4ll_forward" : "nf4ll_backward_dx");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   if (int rc = check_mat(W, who)) return rc;
   if (M < 0) { set_detail("%s: M=%lld", who, static_cast<long long>(M)); return NF4LL_ERR_SHAPE; }
@@ -1028,7 +1042,26 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
   if (int rc = require_sm100()) return rc;
   int sms = 148;
   if (int rc = device_sms(&sms)) return rc;
+  bool narrow_tiles = false;       // a segment boundary that is not a multiple of 256 columns needs 128-column tiles
+  if (segments) {
+    if (n_segments < 1 || n_segments > kMaxSegments) { set_detail("%s: %d segments (1..%d)", who, n_segments, kMaxSegments); return NF4LL_ERR_SHAPE; }
+    int64_t at = 0;
+    for (int i = 0; i < n_segments; ++i) {
+      if (segments[i].rows <= 0 || segments[i].rows % 128) {
+        set_detail("%s: segment %d has %lld rows (multiples of 128)", who, i, static_cast<long long>(segments[i].rows));
+        return NF4LL_ERR_SHAPE;
+      }
+      if (at % 256) narrow_tiles = true;
+      at += segments[i].rows;
+      if (int rc = check_lora(segments[i].lora, who, false, W->K)) return rc;
+      if (segments[i].lora && !segments[i].t_out) { set_detail("%s: segment %d has LoRA but no t_out", who, i); return NF4LL_ERR_NULL; }
+    }
+    if (at != W->N) { set_detail("%s: segments cover %lld of %lld rows", who, static_cast<long long>(at), static_cast<long long>(W->N)); return NF4LL_ERR_SHAPE; }
+  }
+  const int saved_bn = g_force_bn;
+  if (segments && (narrow_tiles || g_force_bn == 512)) g_force_bn = narrow_tiles ? 128 : 256;
   const Plan pl = make_plan(mode, M, NO, KC, lora ? lora->r : 0, sms);
+  g_force_bn = saved_bn;
   if (pl.total() > 0) {
     if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || workspace_bytes < pl.total()) {
       set_detail("%s: needs a 256-byte aligned workspace of %lld bytes (got %lld)", who,
@@ -1056,6 +1089,22 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
     counters = reinterpret_cast<int*>(ws + pl.left_bytes + pl.bt_bytes);
     counter_words = static_cast<int>(pl.counter_bytes / sizeof(int));
   }
+  if (segments) {
+    int64_t at = 0;
+    p.n_seg = n_segments;
+    for (int i = 0; i < n_segments; ++i) {
+      const nf4ll_lora* l = segments[i].lora;
+      p.seg_begin[i] = at;
+      if (l) {
+        if (int rc = lora_down_launch(act, ldact, l->mask, l->ld_mask, l->keep_scale, l->A, 1.0f, M, W->K, segments[i].t_out,
+                                      nullptr, 0, stream)) return rc;
+        p.seg_left[i] = static_cast<const float*>(segments[i].t_out);
+        p.seg_right[i] = static_cast<const __half*>(l->B) - at * 16;      // indexed by the fused output column
+        p.seg_scale[i] = l->scale;
+      }
+      at += segments[i].rows;
+    }
+  }
   if (lora) {
     // rank-16 projection of the activation, fp32: T = drop(x).A^T (forward) or U = s.dy.B (backward);
     // it lands in the caller's t_out / u_out when given, else in the workspace. The same kernel
@@ -1082,7 +1131,7 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
     p.lora_left = left;
     if (mode == kFwd && M <= kStreamMaxRows && !g_force_bm && !g_force_bn && !g_force_splits)
       return stream_forward_launch(W, act, ldact, bias, p.lora_left, lora->B, lora->scale, M, out, ldo, stream);
-  } else if (mode == kFwd && M <= kStreamMaxRows && !g_force_bm && !g_force_bn && !g_force_splits) {
+  } else if (!segments && mode == kFwd && M <= kStreamMaxRows && !g_force_bm && !g_force_bn && !g_force_splits) {
     return stream_forward_launch(W, act, ldact, bias, nullptr, nullptr, 0.f, M, out, ldo, stream);
   }
   if (pl.splits > 1) {
@@ -1129,6 +1178,14 @@ extern "C" int nf4ll_forward(const nf4ll_mat* W, const void* x, int64_t ldx, con
                              void* t_out, int64_t M, void* y, int64_t ldy, void* workspace, int64_t workspace_bytes,
                              int32_t* status, void* stream) {
   return nf4ll::run_gemm(nf4ll::kFwd, W, x, ldx, bias, lora, t_out, M, y, ldy, 0, workspace, workspace_bytes, status, stream);
+}
+
+extern "C" int nf4ll_forward_multi(const nf4ll_mat* W, const void* x, int64_t ldx, const void* bias,
+                                   const nf4ll_segment* segments, int32_t n_segments, int64_t M, void* y, int64_t ldy,
+                                   void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
+  if (!segments) { nf4ll::set_detail("nf4ll_forward_multi: segments is null"); return NF4LL_ERR_NULL; }
+  return nf4ll::run_gemm(nf4ll::kFwd, W, x, ldx, bias, nullptr, nullptr, M, y, ldy, 0, workspace, workspace_bytes, status, stream,
+                         segments, n_segments);
 }
 
 extern "C" int nf4ll_backward_dx(const nf4ll_mat* W, const void* dy, int64_t lddy, const nf4ll_lora* lora, void* u_out,

@@ -9,6 +9,8 @@ namespace nf4ll {
 
 enum : int { kFwd = 0, kBwd = 1 };
 
+constexpr int kMaxSegments = 4;
+
 struct GemmParams {
   const uint8_t* nib;
   const uint8_t* qabs;
@@ -30,6 +32,12 @@ struct GemmParams {
   const uint8_t* mask;       // backward only: keep-mask of the LoRA input [M, ld_mask], may be null
   int64_t ld_mask;
   float keep_scale;
+  // forward over several projections stacked along N (Q|K|V, gate|up): per segment its own LoRA branch
+  int n_seg;                          // 0: one projection, the fields above apply
+  int64_t seg_begin[kMaxSegments];    // first output column of each segment, ascending, seg_begin[0] = 0
+  const float* seg_left[kMaxSegments];     // [M,16] fp32 T of the segment, or null (no LoRA on it)
+  const __half* seg_right[kMaxSegments];   // lora_B of the segment, offset so that it is indexed by the fused output column
+  float seg_scale[kMaxSegments];
   int splits;              // split of the contraction across blockIdx.z
   float* partial;          // [splits][M_pad][NO] fp32 when splits > 1
   int* counters;           // one per output tile when splits > 1 (zero on entry, zero on exit)

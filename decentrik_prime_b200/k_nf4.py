@@ -77,6 +77,24 @@ class PackedLayer:
                 self.scale2[s0:s0 + n // (QBLOCK * QBLOCKS2)],
                 self.offset2[s0:s0 + n // (QBLOCK * QBLOCKS2)], rows, cols)
 
+    def weight_group(self, names):
+        """Sub-views of several consecutive weights of the layer that share their column count, seen
+        as ONE matrix with the rows stacked (Q|K|V, gate|up: contiguous by construction, reference
+        solution/k_nf4.py:7-10): (packed, qabs, scale2, offset2, total rows, cols, rows per weight)."""
+        start0, _, cols = self.segments[names[0]]
+        at, rows_each = start0, []
+        for name in names:
+            start, rows, c = self.segments[name]
+            if start != at or c != cols:
+                raise ValueError(f"{names} are not consecutive weights with equal column counts")
+            rows_each.append(rows)
+            at += rows * cols
+        n = at - start0
+        b0, q0, s0 = start0 // 2, start0 // QBLOCK, start0 // (QBLOCK * QBLOCKS2)
+        return (self.packed[b0:b0 + n // 2], self.qabs[q0:q0 + n // QBLOCK],
+                self.scale2[s0:s0 + n // (QBLOCK * QBLOCKS2)],
+                self.offset2[s0:s0 + n // (QBLOCK * QBLOCKS2)], sum(rows_each), cols, rows_each)
+
 
 def _quant_parts(linear):
     """(weight, quant state) of a bitsandbytes-style 4-bit linear, checked for the one format the

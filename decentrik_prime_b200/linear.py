@@ -43,6 +43,15 @@ class Nf4Weight:
     def from_layer(cls, layer: PackedLayer, name, code2):
         return cls(*layer.weight(name)[:4], code2, *layer.weight(name)[4:])
 
+    @classmethod
+    def from_layer_group(cls, layer: PackedLayer, names, code2):
+        """Several consecutive weights of a layer as one stacked matrix (for forward_multi); the rows
+        of each are kept in `.rows_each`."""
+        packed, qabs, scale2, offset2, rows, cols, rows_each = layer.weight_group(names)
+        w = cls(packed, qabs, scale2, offset2, code2, rows, cols)
+        w.rows_each = list(rows_each)
+        return w
+
     @property
     def nbytes(self):
         """Algorithmic bytes of the weight stream: nibbles + absmax codes + scale2 + offset2."""
@@ -138,6 +147,37 @@ def forward(w: Nf4Weight, x, bias=None, lora=None, mask=None, keep_scale=1.0, ou
                                _lib.current_stream(x.device)))
     del keep
     return y, t
+
+
+def forward_multi(w: Nf4Weight, x, segments, bias=None, out=None, workspace=None):
+    """One launch for several projections that share x and are stacked row-wise in `w` (Q|K|V,
+    gate|up; the reference's fused W_qkv GEMM, solution/fast_qwen.py:405-413, 947).
+    `segments`: one (rows, lora, mask, keep_scale) per projection, lora as in forward() or None.
+    Returns (y [M, sum rows], [t per segment or None])."""
+    _check_act(x, w.K, "x")
+    M = x.shape[0]
+    y = torch.empty(M, w.N, dtype=torch.float16, device=x.device) if out is None else out
+    _check_act(y, w.N, "out")
+    keep, ts = [], []
+    arr = (_lib.Segment * len(segments))()
+    for i, (rows, lora, mask, keep_scale) in enumerate(segments):
+        if mask is not None and lora is None:
+            raise ValueError("a dropout mask without a LoRA branch has no meaning")
+        s, ref = _lora_struct(lora, mask, keep_scale)
+        t = torch.empty(M, RANK, dtype=torch.float32, device=x.device) if lora is not None else None
+        keep.append(s)
+        ts.append(t)
+        arr[i].rows = int(rows)
+        arr[i].lora = ctypes.pointer(s) if s is not None else None
+        arr[i].t_out = None if t is None else t.data_ptr()
+    h = _lib.lib()
+    ws = _workspace(x.device, _workspace_need(M, w.N, w.K, 0)) if workspace is None else workspace
+    _lib.check(h.nf4ll_forward_multi(ctypes.byref(w._c), x.data_ptr(), x.stride(0),
+                                     None if bias is None else bias.data_ptr(), arr, len(segments), M,
+                                     y.data_ptr(), y.stride(0), ws.data_ptr(), ws.numel(),
+                                     status_word(x.device).data_ptr(), _lib.current_stream(x.device)))
+    del keep
+    return y, ts
 
 
 def backward_dx(w: Nf4Weight, dy, lora=None, mask=None, keep_scale=1.0, out=None, accumulate=False,

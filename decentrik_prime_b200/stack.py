@@ -51,6 +51,11 @@ class DecoderLayerProjections:
             if bias_qkv and name in ("q_proj", "k_proj", "v_proj"):      # Qwen2 has biases on q, k, v only
                 bias = (torch.randn(shapes[name][0], generator=gen) * 0.1).half().to(device)
             self.proj[name] = blocks.Projection(w, bias=bias, lora=name in lora_on, bucket=bucket, seed=seed * 16 + 10 + i)
+        # Q|K|V and gate|up lie row after row in the packed layer: one stacked matrix and one launch each
+        self.w_qkv = linear.Nf4Weight.from_layer_group(self.layer, ("q_proj", "k_proj", "v_proj"), self.code2)
+        self.w_gu = linear.Nf4Weight.from_layer_group(self.layer, ("gate_proj", "up_proj"), self.code2)
+        self.bias_qkv = torch.cat([self.proj[n].bias for n in ("q_proj", "k_proj", "v_proj")]) if bias_qkv else None
+        self.fused_groups = all(r % 128 == 0 for r in self.w_qkv.rows_each + self.w_gu.rows_each)
         # with a bucket the layer's gradients are one contiguous slice: cleared by one fill per backward
         self._grad_slice = bucket.flat[grad_lo:bucket._at] if bucket is not None and bucket._at > grad_lo else None
         self._saved = None
@@ -65,19 +70,38 @@ class DecoderLayerProjections:
         """x [M, hidden] fp16; masks: dict projection name -> uint8 keep-mask [M, K] for the LoRA ones."""
         P, H, KV, M = self.proj, self.hidden, self.kv, x.shape[0]
         qkv = torch.empty(M, H + 2 * KV, dtype=torch.float16, device=x.device)
-        P["q_proj"].forward(x, masks.get("q_proj"), keep_scale, out=qkv[:, :H])
-        P["k_proj"].forward(x, masks.get("k_proj"), keep_scale, out=qkv[:, H:H + KV])
-        P["v_proj"].forward(x, masks.get("v_proj"), keep_scale, out=qkv[:, H + KV:])
+        if self.fused_groups:
+            self._forward_group(self.w_qkv, ("q_proj", "k_proj", "v_proj"), x, masks, keep_scale, self.bias_qkv, qkv)
+        else:
+            P["q_proj"].forward(x, masks.get("q_proj"), keep_scale, out=qkv[:, :H])
+            P["k_proj"].forward(x, masks.get("k_proj"), keep_scale, out=qkv[:, H:H + KV])
+            P["v_proj"].forward(x, masks.get("v_proj"), keep_scale, out=qkv[:, H + KV:])
         a = qkv[:, :H].clone()
         a[:, :KV] += qkv[:, H:H + KV]
         a[:, KV:2 * KV] += qkv[:, H + KV:]
         h1 = x + P["o_proj"].forward(a, masks.get("o_proj"), keep_scale)
-        g = P["gate_proj"].forward(h1, masks.get("gate_proj"), keep_scale)
-        u = P["up_proj"].forward(h1, masks.get("up_proj"), keep_scale)
+        if self.fused_groups:
+            gu = torch.empty(M, 2 * self.inter, dtype=torch.float16, device=x.device)
+            self._forward_group(self.w_gu, ("gate_proj", "up_proj"), h1, masks, keep_scale, None, gu)
+            g, u = gu[:, :self.inter], gu[:, self.inter:]
+        else:
+            g = P["gate_proj"].forward(h1, masks.get("gate_proj"), keep_scale)
+            u = P["up_proj"].forward(h1, masks.get("up_proj"), keep_scale)
         h = linear.swiglu_forward(g, u)
         out = h1 + P["down_proj"].forward(h, masks.get("down_proj"), keep_scale)
         self._saved = (g, u)
         return out
+
+    def _forward_group(self, w, names, x, masks, keep_scale, bias, out):
+        """One launch for projections that share x; each keeps its own saved state for the backward."""
+        segs = []
+        for n in names:
+            pj = self.proj[n]
+            segs.append((pj.w.N, pj.lora, masks.get(n) if pj.has_lora else None, keep_scale))
+        _, ts = linear.forward_multi(w, x, segs, bias=bias, out=out)
+        for n, t in zip(names, ts):
+            pj = self.proj[n]
+            pj._saved = (x, masks.get(n) if pj.has_lora else None, keep_scale, t)
 
     def backward(self, dout, need_dx=True, accumulate_grads=False):
         P, H, KV = self.proj, self.hidden, self.kv

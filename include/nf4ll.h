@@ -107,6 +107,25 @@ int nf4ll_forward(const nf4ll_mat* W, const void* x, int64_t ldx, const void* bi
 /* Size of the scratch buffer built into the library for nf4ll_forward_static. */
 #define NF4LL_STATIC_SCRATCH_BYTES (40 * 1024 * 1024)
 
+/* Forward over several projections that share x and lie row after row in one weight matrix, as the
+ * reference's packed layer stores Q|K|V and gate|up (solution/k_nf4.py:7-10, 61) and as its fused
+ * W_qkv GEMM uses them (solution/fast_qwen.py:405-413, 947; gate and up: 1080-1098): one launch
+ * instead of one per projection, x read once per tile row.
+ *   y[:, segment i] = x . W_i^T (+ bias over all N columns) + scale_i * (drop_i(x) . A_i^T) . B_i^T
+ * W describes the stacked matrix (N = sum of the segments' rows); every segment's row count is a
+ * multiple of 128; a segment with a LoRA branch must give t_out (fp32 [M,r], written by the call: the
+ * backward needs it anyway). At most 4 segments. Workspace: nf4ll_workspace_bytes(M, N, K, 0).
+ * The backward of such a group needs no entry point of its own: dX = [dY_1 | dY_2 | ...] . W is one
+ * nf4ll_backward_dx on the stacked matrix for the base term (LoRA terms per projection). */
+typedef struct {
+  int64_t rows;             /* output columns (= weight rows) of this projection */
+  const nf4ll_lora* lora;   /* its LoRA branch, or NULL */
+  void* t_out;              /* fp32 [M,r] = drop(x) . A^T of this projection; required with lora */
+} nf4ll_segment;
+int nf4ll_forward_multi(const nf4ll_mat* W, const void* x, int64_t ldx, const void* bias,
+                        const nf4ll_segment* segments, int32_t n_segments, int64_t M, void* y, int64_t ldy,
+                        void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
+
 /* nf4ll_forward for callers that can neither allocate device memory nor pass a workspace - a plugin
  * host that bans allocations after start-up, a server whose memory pool is already sealed. It has no
  * counterpart in the reference. Same arguments and results as nf4ll_forward minus the workspace:

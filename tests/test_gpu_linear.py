@@ -84,6 +84,46 @@ def test_split_contraction_on_a_grid_larger_than_one_wave(force):
     run_case(1536, 1536, 2048, bias=True, force=force, seed=5 + force[1])
 
 
+@pytest.mark.parametrize("M", [200, 1300])
+def test_stacked_projections_in_one_launch_match_separate_calls(M):
+    """nf4ll_forward_multi on Q|K|V of a packed layer (LoRA on q and v, bias on all, k narrower than a
+    256-column tile) and on gate|up equals the three / two single-projection calls."""
+    from decentrik_prime_b200 import k_nf4, quantize
+    H, KV, I = 512, 128, 1024
+    shapes = {"q_proj": (H, H), "k_proj": (KV, H), "v_proj": (KV, H), "o_proj": (H, H),
+              "gate_proj": (I, H), "up_proj": (I, H), "down_proj": (H, I)}
+    lin = {n: quantize.random_nf4_weight(*shapes[n], seed=40 + i, device="cuda") for i, n in enumerate(k_nf4.LAYER_WEIGHTS)}
+    layer, code2 = k_nf4.repack_layer(lin, torch.device("cuda"))
+    gen = torch.Generator().manual_seed(M)
+    x = torch.randn(M, H, generator=gen).half().cuda()
+    ks = float(1.0 / torch.tensor(0.95, dtype=torch.float32))
+    def lora(n):
+        A = (torch.randn(16, H, generator=gen) * 0.05).half().cuda()
+        B = (torch.randn(n, 16, generator=gen) * 0.05).half().cuda()
+        return (A, B, 2.0)
+    def mask():
+        return (torch.rand(M, H, generator=gen) >= 0.05).to(torch.uint8).cuda()
+    for names, with_lora in ((("q_proj", "k_proj", "v_proj"), (True, False, True)), (("gate_proj", "up_proj"), (True, True))):
+        ws = [linear.Nf4Weight.from_layer(layer, n, code2) for n in names]
+        bias = [(torch.randn(w.N, generator=gen) * 0.1).half().cuda() for w in ws]
+        loras = [lora(w.N) if on else None for w, on in zip(ws, with_lora)]
+        masks = [mask() if on else None for on in with_lora]
+        ref_y, ref_t = [], []
+        for w, b, l, m in zip(ws, bias, loras, masks):
+            y, t = linear.forward(w, x, bias=b, lora=l, mask=m, keep_scale=ks, want_t=True)
+            ref_y.append(y); ref_t.append(t)
+        wg = linear.Nf4Weight.from_layer_group(layer, names, code2)
+        y, ts = linear.forward_multi(wg, x, [(w.N, l, m, ks) for w, l, m in zip(ws, loras, masks)], bias=torch.cat(bias))
+        linear.check_status()
+        assert_close("stacked y", y, torch.cat(ref_y, 1).double())
+        for t, rt in zip(ts, ref_t):
+            assert (t is None) == (rt is None)
+            if t is not None:
+                assert_close("stacked t", t, rt.double())
+    with pytest.raises(ValueError):
+        linear.forward_multi(wg, x, [(wg.N - 64, None, None, 1.0), (64, None, None, 1.0)])
+
+
 def test_config0_q_proj():
     """BASELINE config 0: W [1536,1536], X [2048,1536], LoRA r=16 alpha=32, dropout 0.05."""
     run_case(1536, 1536, 2048)
