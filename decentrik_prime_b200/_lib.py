@@ -91,6 +91,8 @@ SIGNATURES = {
     "nf4ll_workspace_bytes": (_i64, [_i64, _i64, _i64, _i32]),
     "nf4ll_forward": (_i32, [_MAT, _vp, _i64, _vp, _LORA, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp]),
     "nf4ll_forward_multi": (_i32, [_MAT, _vp, _i64, _vp, _SEG, _i32, _i64, _vp, _i64, _vp, _i64, _vp, _vp]),
+    "nf4ll_forward_gate_up": (_i32, [_MAT, _vp, _i64, _LORA, _LORA, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64,
+                                     _vp, _vp]),
     "nf4ll_forward_static": (_i32, [_MAT, _vp, _i64, _vp, _LORA, _vp, _i64, _vp, _i64, _vp, _vp]),
     "nf4ll_backward_dx": (_i32, [_MAT, _vp, _i64, _LORA, _vp, _i64, _vp, _i64, _i32, _vp, _i64, _vp, _vp]),
     "nf4ll_lora_down": (_i32, [_vp, _i64, _vp, _i64, _f32, _vp, _f32, _i32, _i64, _i64, _vp, _vp, _vp]),

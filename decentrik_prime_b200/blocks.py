@@ -134,11 +134,19 @@ class MlpBlock:
 
     def __init__(self, hidden, inter, seed, device, lora=True, bucket=None, fused_glue=True):
         self.hidden, self.inter = hidden, inter
-        self.fused_glue = fused_glue      # library SwiGLU kernels (reference k_mlp.py) or plain PyTorch
+        # fused_glue: the gated product comes out of the gate|up kernel's epilogue (short batches: the
+        # library's stand-alone kernel, the counterpart of reference k_mlp.py); False: plain PyTorch ops
+        self.fused_glue = fused_glue
         grad_lo = bucket._at if bucket is not None else 0
-        self.gate = make_projection(inter, hidden, seed * 10 + 1, device, lora=lora, bucket=bucket)
-        self.up = make_projection(inter, hidden, seed * 10 + 2, device, lora=lora, bucket=bucket)
-        self.down = make_projection(hidden, inter, seed * 10 + 3, device, lora=lora, bucket=bucket)
+        # the three weights in one packed layer, gate and up row after row as in the reference's layout
+        names = ("gate_proj", "up_proj", "down_proj")
+        shapes = {"gate_proj": (inter, hidden), "up_proj": (inter, hidden), "down_proj": (hidden, inter)}
+        lin = {n: quantize.random_nf4_weight(*shapes[n], seed=seed * 10 + 1 + i, device=device) for i, n in enumerate(names)}
+        self.layer, self.code2 = k_nf4.repack_layer(lin, torch.device(device), names=names)
+        pj = [Projection(linear.Nf4Weight.from_layer(self.layer, n, self.code2), lora=lora, bucket=bucket,
+                         seed=seed * 10 + 3 + i) for i, n in enumerate(names)]
+        self.gate, self.up, self.down = pj
+        self.w_gu = linear.Nf4Weight.from_layer_group(self.layer, ("gate_proj", "up_proj"), self.code2)
         self.projections = (self.gate, self.up, self.down)
         # with a bucket the block's gradients are one contiguous slice: cleared by one fill per backward
         self._grad_slice = bucket.flat[grad_lo:bucket._at] if (bucket is not None and lora) else None
@@ -152,9 +160,17 @@ class MlpBlock:
         return sum(p.flops(M) for p in self.projections)
 
     def forward(self, x, masks=(None, None, None), keep_scale=1.0):
+        if self.fused_glue:
+            g, u, h, tg, tu = linear.forward_gate_up(self.w_gu, x, self.gate.lora, masks[0] if self.gate.has_lora else None,
+                                                     self.up.lora, masks[1] if self.up.has_lora else None, keep_scale)
+            self.gate._saved = (x, masks[0] if self.gate.has_lora else None, keep_scale, tg)
+            self.up._saved = (x, masks[1] if self.up.has_lora else None, keep_scale, tu)
+            y = self.down.forward(h, masks[2], keep_scale)
+            self._saved = (g, u)
+            return y
         g = self.gate.forward(x, masks[0], keep_scale)
         u = self.up.forward(x, masks[1], keep_scale)
-        h = linear.swiglu_forward(g, u) if self.fused_glue else F.silu(g.float()).mul_(u.float()).half()
+        h = F.silu(g.float()).mul_(u.float()).half()
         y = self.down.forward(h, masks[2], keep_scale)
         self._saved = (g, u)
         return y

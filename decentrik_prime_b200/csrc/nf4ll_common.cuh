@@ -352,4 +352,46 @@ __device__ __forceinline__ uint4 drop8(uint4 raw, uint2 m, float keep_scale) {
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Gated SiLU on 8 packed fp16 values (fp32 math), shared by the stand-alone kernels and the fused
+// gate|up epilogue
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
+  const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 v = __half22float2(h[j]);
+    f[2 * j] = v.x;
+    f[2 * j + 1] = v.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  return make_uint4(pack_half2_rn(f[0], f[1]), pack_half2_rn(f[2], f[3]), pack_half2_rn(f[4], f[5]),
+                    pack_half2_rn(f[6], f[7]));
+}
+
+// sigmoid through the special-function unit: ex2.approx and rcp.approx, a few ulp of fp32 - far inside
+// the fp16 rounding of the results
+__device__ __forceinline__ float fast_sigmoid(float a) { return __fdividef(1.0f, 1.0f + __expf(-a)); }
+
+__device__ __forceinline__ uint4 swiglu_fwd8(const uint4& gv, const uint4& uv) {
+  float a[8], b[8], o[8];
+  unpack8(gv, a); unpack8(uv, b);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = a[j] * fast_sigmoid(a[j]) * b[j];
+  return pack8(o);
+}
+
+__device__ __forceinline__ void swiglu_bwd8(const uint4& gv, const uint4& uv, const uint4& dv, uint4& og4, uint4& ou4) {
+  float a[8], b[8], d[8], og[8], ou[8];
+  unpack8(gv, a); unpack8(uv, b); unpack8(dv, d);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float sig = fast_sigmoid(a[j]);
+    ou[j] = d[j] * (a[j] * sig);
+    og[j] = (d[j] * b[j]) * sig * (1.0f + a[j] * (1.0f - sig));
+  }
+  og4 = pack8(og); ou4 = pack8(ou);
+}
+
 }  // namespace nf4ll

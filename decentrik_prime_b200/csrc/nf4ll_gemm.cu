@@ -46,7 +46,8 @@ struct TileCfg {
 template <int MODE, int BM_TILES, int BN>
 __global__ void __launch_bounds__(TileCfg<BM_TILES, BN>::kThreads, 1)
 nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_constant__ CUtensorMap tmap_nib,
-                const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
+                const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_out_u,
+                const __grid_constant__ CUtensorMap tmap_out_h, const GemmParams p) {
   using Cfg = TileCfg<BM_TILES, BN>;
   constexpr int S = Cfg::kStages;
   constexpr int NDW = Cfg::kDequantWarps;
@@ -87,7 +88,13 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
   const int lane = threadIdx.x & 31;
   const int tile_o = blockIdx.x, tile_m = blockIdx.y, split = blockIdx.z;
   const int64_t m0 = static_cast<int64_t>(tile_m) * (BM_TILES * 128);
-  const int64_t o0 = static_cast<int64_t>(tile_o) * BN;
+  // gate|up mode: the tile's 256 weight rows are 128 gate rows and the 128 up rows of the same columns
+  constexpr bool kGuCapable = (MODE == kFwd && BM_TILES == 2 && BN == 256);
+  const bool gu = kGuCapable && p.gu_inter > 0;
+  const int64_t g0 = static_cast<int64_t>(tile_o) * 128;
+  const int64_t o0 = gu ? g0 : static_cast<int64_t>(tile_o) * BN;
+  // weight row behind tile row d
+  auto wrow = [&](int d) -> int64_t { return (gu && d >= 128) ? p.gu_inter + g0 + (d - 128) : o0 + d; };
 
   // contraction range of this split, in 64-wide steps
   const int nkb_total = static_cast<int>(p.KC / 64);
@@ -99,7 +106,9 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
   const __half* lora_right = p.lora_right;
   float left_scale = p.left_scale;
   bool has_lora = p.has_lora != 0;
-  if (p.n_seg > 0) {
+  if (gu) {
+    has_lora = p.seg_left[0] != nullptr || p.seg_left[1] != nullptr;
+  } else if (p.n_seg > 0) {
     int sg = 0;
     for (int i = 1; i < p.n_seg; ++i) if (static_cast<int64_t>(tile_o) * BN >= p.seg_begin[i]) sg = i;
     lora_left = p.seg_left[sg]; lora_right = p.seg_right[sg]; left_scale = p.seg_scale[sg];
@@ -155,7 +164,12 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
         // packed codes first (the dequant warps need them a whole stage before the MMA needs anything)
         if (!wait_or_abort(smem_u32(nib_empty + s), free_parity, ab, 0x0102)) break;
         mbar_arrive_expect_tx(smem_u32(nib_full + s), Cfg::kNibBytes);
-        if (MODE == kFwd) {
+        if (gu) {
+          // two boxes of 128 weight rows: gate, then up
+          tma_load_2d(smem_u32(sNib + s * Cfg::kNibBytes), &tmap_nib, kb * 32, static_cast<int>(g0), smem_u32(nib_full + s));
+          tma_load_2d(smem_u32(sNib + s * Cfg::kNibBytes + 128 * 32), &tmap_nib, kb * 32, static_cast<int>(p.gu_inter + g0),
+                      smem_u32(nib_full + s));
+        } else if (MODE == kFwd) {
           tma_load_2d(smem_u32(sNib + s * Cfg::kNibBytes), &tmap_nib, kb * 32, static_cast<int>(o0), smem_u32(nib_full + s));
         } else {
           tma_load_2d(smem_u32(sNib + s * Cfg::kNibBytes), &tmap_nib, static_cast<int>(o0 / 2), kb * 64, smem_u32(nib_full + s));
@@ -230,11 +244,26 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
           tc_fence_after();
           // rank-16 step: left [128 x 16] K-major, right K-major [BN x 16] (fwd) / MN-major [16 x BN] (bwd);
           // 8x(16 B) core matrices, 128 B between the two K halves, 256 B between 8-row (or 8-column) groups
-          const uint64_t rdesc = make_smem_desc(smem_u32(sLR), 128, 256, kSwizzleNone);
+          if (gu) {
+            // two branches: gate columns from (T_gate, B_gate), up columns from (T_up, B_up), N = 128 each
+            constexpr uint32_t idesc_half = make_idesc_f16(128, 128, 0, 0);
+            const uint32_t right = smem_u32(sLL) + 2 * Cfg::kLoraLeftBytes;
 #pragma unroll
-          for (int mt = 0; mt < BM_TILES; ++mt) {
-            const uint64_t ldesc = make_smem_desc(smem_u32(sLL + mt * 4096), 128, 256, kSwizzleNone);
-            tc_mma_f16(tmem_base + mt * BN, ldesc, rdesc, idesc_main, 0u);
+            for (int mt = 0; mt < BM_TILES; ++mt) {
+#pragma unroll
+              for (int br = 0; br < 2; ++br) {
+                const uint64_t ldesc = make_smem_desc(smem_u32(sLL) + br * Cfg::kLoraLeftBytes + mt * 4096, 128, 256, kSwizzleNone);
+                const uint64_t rdesc = make_smem_desc(right + br * 4096, 128, 256, kSwizzleNone);
+                tc_mma_f16(tmem_base + mt * BN + br * 128, ldesc, rdesc, idesc_half, 0u);
+              }
+            }
+          } else {
+            const uint64_t rdesc = make_smem_desc(smem_u32(sLR), 128, 256, kSwizzleNone);
+#pragma unroll
+            for (int mt = 0; mt < BM_TILES; ++mt) {
+              const uint64_t ldesc = make_smem_desc(smem_u32(sLL + mt * 4096), 128, 256, kSwizzleNone);
+              tc_mma_f16(tmem_base + mt * BN, ldesc, rdesc, idesc_main, 0u);
+            }
           }
           tc_commit(smem_u32(lora_done));     // the borrowed weight stage may be overwritten after this
           if (premask) {
@@ -284,7 +313,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
       for (int e = 0; e < PER; ++e) {
         const int d = t + e * 64;
         if (MODE == kFwd) {
-          int64_t n = o0 + d;
+          int64_t n = wrow(d);
           if (n >= p.N) n = p.N - 1;               // tail rows: any valid block; their output is never stored
           qb[e] = (n * p.K) / 64 + kb_begin;
         } else {
@@ -334,7 +363,53 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
 
     // --- LoRA operands: staged by these warps while the first weight codes are still on their way.
     // All loads are issued before the first store, so the cost is one trip to memory.
-    if (lora_here) {
+    if (kGuCapable && gu && lora_here) {
+      // gate|up: two left operands (T_gate, T_up: 256 rows x 16 each) and the tile's 128 rows of B_gate and
+      // B_up; a branch without LoRA contributes zeros. Layout: [left gate | left up | right gate, right up].
+      constexpr int NT = NDW * 32;
+      constexpr int LEFT = 2 * BM_TILES * 128 * 2, RIGHT = 256 * 2;
+      constexpr int LPT = LEFT / NT, RPT = RIGHT / NT;
+      float4 la[LPT], lb[LPT];
+      uint4 rv[RPT];
+#pragma unroll
+      for (int e = 0; e < LPT; ++e) {
+        const int c = d + e * NT, br = c / (BM_TILES * 128 * 2), cc = c % (BM_TILES * 128 * 2), row = cc >> 1, h = cc & 1;
+        la[e] = make_float4(0.f, 0.f, 0.f, 0.f); lb[e] = la[e];
+        const float* left = p.seg_left[br];
+        if (left && m0 + row < p.M) {
+          const float4* src = reinterpret_cast<const float4*>(left + (m0 + row) * 16 + h * 8);
+          la[e] = __ldg(src); lb[e] = __ldg(src + 1);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < RPT; ++e) {
+        const int c = d + e * NT, row = c >> 1, h = c & 1, br = row >> 7, r = row & 127;
+        rv[e] = make_uint4(0, 0, 0, 0);
+        if (p.seg_left[br] && g0 + r < p.gu_inter)
+          rv[e] = __ldg(reinterpret_cast<const uint4*>(p.seg_right[br] + (g0 + r) * 16 + h * 8));
+      }
+      uint8_t* sRight = sLL + 2 * Cfg::kLoraLeftBytes;
+#pragma unroll
+      for (int e = 0; e < LPT; ++e) {
+        const int c = d + e * NT, br = c / (BM_TILES * 128 * 2), cc = c % (BM_TILES * 128 * 2), row = cc >> 1, h = cc & 1;
+        const float sc = p.seg_scale[br];
+        uint4 v;
+        v.x = pack_half2_rn(la[e].x * sc, la[e].y * sc);
+        v.y = pack_half2_rn(la[e].z * sc, la[e].w * sc);
+        v.z = pack_half2_rn(lb[e].x * sc, lb[e].y * sc);
+        v.w = pack_half2_rn(lb[e].z * sc, lb[e].w * sc);
+        const int mt = row >> 7, r = row & 127;
+        *reinterpret_cast<uint4*>(sLL + br * Cfg::kLoraLeftBytes + mt * 4096 + (r >> 3) * 256 + h * 128 + (r & 7) * 16) = v;
+      }
+#pragma unroll
+      for (int e = 0; e < RPT; ++e) {
+        const int c = d + e * NT, row = c >> 1, h = c & 1;
+        *reinterpret_cast<uint4*>(sRight + (row >> 3) * 256 + h * 128 + (row & 7) * 16) = rv[e];
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(lora_full));
+    } else if (lora_here) {
       constexpr int NT = NDW * 32;
       constexpr int LEFT = BM_TILES * 128 * 2;         // 16-byte chunks (8 fp16) of the left operand
       constexpr int RIGHT = BN * 2;
@@ -518,6 +593,58 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
       const uint32_t row_addr = stage + r_in * 128;
       const int key = r_in & 7;
       const bool leader = (q == 0 && lane == 0);
+      if (kGuCapable && gu) {
+        // gate|up: this warp group drains one 128-row accumulator: g (columns 0-127), u (128-255), and
+        // h = silu(g) * u computed from the rounded fp16 values, as the stand-alone kernel would read them.
+        // Staging: six boxes of 128 rows x 64 columns (g, g, u, u, h, h), one TMA store each.
+        const uint32_t stage_gu = smem_u32(smem) + grp * 98304;
+        const uint32_t row_gu = stage_gu + r_in * 128;
+        const int mt = grp;
+        const uint32_t tacc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + mt * BN;
+#pragma unroll 1
+        for (int jb = 0; jb < 2; ++jb) {
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int j = jb * 2 + half;
+            uint32_t vg[32], vu[32];
+            __syncwarp();
+            tmem_ld32(tacc + j * 32, vg);
+            tmem_ld32(tacc + 128 + j * 32, vu);
+            tmem_ld_wait();
+#pragma unroll
+            for (int g8 = 0; g8 < 4; ++g8) {
+              uint4 gq, uq;
+              gq.x = pack_half2_rn(__uint_as_float(vg[g8 * 8 + 0]), __uint_as_float(vg[g8 * 8 + 1]));
+              gq.y = pack_half2_rn(__uint_as_float(vg[g8 * 8 + 2]), __uint_as_float(vg[g8 * 8 + 3]));
+              gq.z = pack_half2_rn(__uint_as_float(vg[g8 * 8 + 4]), __uint_as_float(vg[g8 * 8 + 5]));
+              gq.w = pack_half2_rn(__uint_as_float(vg[g8 * 8 + 6]), __uint_as_float(vg[g8 * 8 + 7]));
+              uq.x = pack_half2_rn(__uint_as_float(vu[g8 * 8 + 0]), __uint_as_float(vu[g8 * 8 + 1]));
+              uq.y = pack_half2_rn(__uint_as_float(vu[g8 * 8 + 2]), __uint_as_float(vu[g8 * 8 + 3]));
+              uq.z = pack_half2_rn(__uint_as_float(vu[g8 * 8 + 4]), __uint_as_float(vu[g8 * 8 + 5]));
+              uq.w = pack_half2_rn(__uint_as_float(vu[g8 * 8 + 6]), __uint_as_float(vu[g8 * 8 + 7]));
+              const uint4 hq = swiglu_fwd8(gq, uq);
+              const uint32_t off = ((half * 4 + g8) ^ key) << 4;
+              sts128(row_gu + (0 + jb) * 16384 + off, gq);
+              sts128(row_gu + (2 + jb) * 16384 + off, uq);
+              sts128(row_gu + (4 + jb) * 16384 + off, hq);
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        named_barrier(bar_id, 128);
+        if (leader) {
+          const int row_g = static_cast<int>(m0 + mt * 128);
+          for (int jb = 0; jb < 2; ++jb) {
+            const int64_t col0 = g0 + jb * 64;
+            if (col0 >= p.gu_inter) break;
+            tma_store_2d(&tmap_out, stage_gu + (0 + jb) * 16384, static_cast<int>(col0), row_g);
+            tma_store_2d(&tmap_out_u, stage_gu + (2 + jb) * 16384, static_cast<int>(col0), row_g);
+            tma_store_2d(&tmap_out_h, stage_gu + (4 + jb) * 16384, static_cast<int>(col0), row_g);
+          }
+          bulk_commit();
+          bulk_wait_read_all();
+        }
+      } else
       if (!direct && p.coop) {
         // shared reduction, first half: every box of the tile that another split owns goes to this
         // split's slab as fp32, four boxes per staging round, rounds dealt to the warp groups in turn
@@ -562,7 +689,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
         }
         if (pending) flush();
       }
-      for (int mt = grp; mt < BM_TILES && !(!direct && p.coop); mt += G) {
+      for (int mt = grp; mt < BM_TILES && !(!direct && p.coop) && !gu; mt += G) {
         const uint32_t tacc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + mt * BN;
         const int row_g = static_cast<int>(m0 + mt * 128);
         if (direct) {
@@ -946,8 +1073,8 @@ static int device_sms(int* sms) {
 }
 
 template <int MODE, int BM_TILES, int BN>
-static int launch_cfg(const CUtensorMap& map, const CUtensorMap& nib_map, const CUtensorMap& out_map, const GemmParams& p,
-                      const Plan& pl, cudaStream_t stream) {
+static int launch_cfg(const CUtensorMap& map, const CUtensorMap& nib_map, const CUtensorMap& out_map, const CUtensorMap& out_u,
+                      const CUtensorMap& out_h, const GemmParams& p, const Plan& pl, cudaStream_t stream) {
   using Cfg = TileCfg<BM_TILES, BN>;
   auto kernel = nf4_gemm_kernel<MODE, BM_TILES, BN>;
   NF4LL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
@@ -955,7 +1082,7 @@ static int launch_cfg(const CUtensorMap& map, const CUtensorMap& nib_map, const 
   // split-K with a shared reduction: the splits of a tile wait for one another, which is only legal
   // when the whole grid is resident at once (cooperative launch)
   PdlLaunch lc(grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, 0, 0, p.coop != 0);
-  NF4LL_CUDA(cudaLaunchKernelEx(&lc.cfg, kernel, map, nib_map, out_map, p));
+  NF4LL_CUDA(cudaLaunchKernelEx(&lc.cfg, kernel, map, nib_map, out_map, out_u, out_h, p));
   NF4LL_CUDA(cudaGetLastError());
   return NF4LL_OK;
 }
@@ -963,10 +1090,11 @@ static int launch_cfg(const CUtensorMap& map, const CUtensorMap& nib_map, const 
 template <int MODE>
 static int launch(const CUtensorMap& map, const CUtensorMap& nib_map, const CUtensorMap& out_map, const GemmParams& p,
                   const Plan& pl, cudaStream_t stream) {
-  if (pl.bm_tiles == 2 && pl.bn == 256) return launch_cfg<MODE, 2, 256>(map, nib_map, out_map, p, pl, stream);
-  if (pl.bm_tiles == 1 && pl.bn == 256) return launch_cfg<MODE, 1, 256>(map, nib_map, out_map, p, pl, stream);
-  if (pl.bm_tiles == 2 && pl.bn == 128) return launch_cfg<MODE, 2, 128>(map, nib_map, out_map, p, pl, stream);
-  return launch_cfg<MODE, 1, 128>(map, nib_map, out_map, p, pl, stream);
+  // the two extra output maps are only read in the gate|up mode
+  if (pl.bm_tiles == 2 && pl.bn == 256) return launch_cfg<MODE, 2, 256>(map, nib_map, out_map, out_map, out_map, p, pl, stream);
+  if (pl.bm_tiles == 1 && pl.bn == 256) return launch_cfg<MODE, 1, 256>(map, nib_map, out_map, out_map, out_map, p, pl, stream);
+  if (pl.bm_tiles == 2 && pl.bn == 128) return launch_cfg<MODE, 2, 128>(map, nib_map, out_map, out_map, out_map, p, pl, stream);
+  return launch_cfg<MODE, 1, 128>(map, nib_map, out_map, out_map, out_map, p, pl, stream);
 }
 
 static int check_mat(const nf4ll_mat* W, const char* who) {
@@ -1159,7 +1287,88 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
   return rc;
 }
 
+// Rows [begin, begin + rows) of a weight as a weight of its own (same columns).
+static nf4ll_mat sub_rows(const nf4ll_mat* W, int64_t begin, int64_t rows) {
+  nf4ll_mat m = *W;
+  const int64_t e0 = begin * W->K;
+  m.nib = W->nib + e0 / 2;
+  m.qabs = W->qabs + e0 / 64;
+  m.scale2 = W->scale2 + e0 / 16384;
+  m.offset2 = W->offset2 + e0 / 16384;
+  m.N = rows;
+  return m;
+}
+
+// gate|up forward with the gated-SiLU product in the epilogue
+static int run_gate_up(const nf4ll_mat* W, const void* x, int64_t ldx, const nf4ll_lora* lora_gate, const nf4ll_lora* lora_up,
+                       void* t_gate, void* t_up, int64_t M, void* g, int64_t ldg, void* u, int64_t ldu, void* h, int64_t ldh,
+                       void* workspace, int64_t workspace_bytes, int32_t* status, void* stream_v) {
+  const char* who = "nf4ll_forward_gate_up";
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (int rc = check_mat(W, who)) return rc;
+  if (M < 0 || W->N % 2) { set_detail("%s: M=%lld, %lld stacked rows", who, (long long)M, (long long)W->N); return NF4LL_ERR_SHAPE; }
+  if (M == 0) return NF4LL_OK;
+  const int64_t I = W->N / 2;
+  if ((I * W->K) % 16384) { set_detail("%s: each half must hold whole second-level blocks", who); return NF4LL_ERR_SHAPE; }
+  if (int rc = check_act(x, ldx, W->K, who, "x")) return rc;
+  if (int rc = check_act(g, ldg, I, who, "g")) return rc;
+  if (int rc = check_act(u, ldu, I, who, "u")) return rc;
+  if (int rc = check_act(h, ldh, I, who, "h")) return rc;
+  if (int rc = check_lora(lora_gate, who, false, W->K)) return rc;
+  if (int rc = check_lora(lora_up, who, false, W->K)) return rc;
+  if ((lora_gate && !t_gate) || (lora_up && !t_up)) { set_detail("%s: a LoRA branch needs its t_out", who); return NF4LL_ERR_NULL; }
+  if (int rc = require_sm100()) return rc;
+  if (M <= 128 || I % 128 || g_force_bm || g_force_bn || g_force_splits) {
+    // short batches and odd widths: the two projections on their own, then the stand-alone gated product
+    const nf4ll_mat wg = sub_rows(W, 0, I), wu = sub_rows(W, I, I);
+    if (int rc = run_gemm(kFwd, &wg, x, ldx, nullptr, lora_gate, t_gate, M, g, ldg, 0, workspace, workspace_bytes, status, stream_v)) return rc;
+    if (int rc = run_gemm(kFwd, &wu, x, ldx, nullptr, lora_up, t_up, M, u, ldu, 0, workspace, workspace_bytes, status, stream_v)) return rc;
+    return nf4ll_swiglu_forward(g, ldg, u, ldu, h, ldh, M, I, stream_v);
+  }
+  GemmParams p{};
+  p.nib = W->nib; p.qabs = W->qabs; p.scale2 = W->scale2; p.offset2 = W->offset2; p.code2 = W->code2;
+  p.N = W->N; p.K = W->K; p.M = M; p.NO = W->N; p.KC = W->K;
+  p.out = static_cast<__half*>(g); p.ldo = ldg;
+  p.splits = 1; p.status = status; p.debug = g_debug;
+  p.gu_inter = I;
+  const nf4ll_lora* br[2] = {lora_gate, lora_up};
+  void* tout[2] = {t_gate, t_up};
+  for (int i = 0; i < 2; ++i) {
+    if (!br[i]) continue;
+    if (int rc = lora_down_launch(x, ldx, br[i]->mask, br[i]->ld_mask, br[i]->keep_scale, br[i]->A, 1.0f, M, W->K, tout[i],
+                                  nullptr, 0, stream)) return rc;
+    p.seg_left[i] = static_cast<const float*>(tout[i]);
+    p.seg_right[i] = static_cast<const __half*>(br[i]->B);
+    p.seg_scale[i] = br[i]->scale;
+  }
+  p.has_lora = (lora_gate || lora_up) ? 1 : 0;
+  Plan pl{};
+  pl.bm_tiles = 2; pl.bn = 256; pl.splits = 1; pl.pair = 0;
+  pl.tiles_o = I / 128;
+  pl.tiles_m = (M + 255) / 256;
+  CUtensorMap map, nib_map, mg, mu, mh;
+  if (int rc = make_tile_map(&map, x, M, W->K, ldx, false)) return rc;
+  if (int rc = make_nib_map(&nib_map, W->nib, W->N, W->K, kFwd, 128)) return rc;
+  if (int rc = make_tile_map(&mg, g, M, I, ldg, false)) return rc;
+  if (int rc = make_tile_map(&mu, u, M, I, ldu, false)) return rc;
+  if (int rc = make_tile_map(&mh, h, M, I, ldh, false)) return rc;
+  cudaEvent_t ev0 = g_ev_start, ev1 = g_ev_stop;
+  g_ev_start = g_ev_stop = nullptr;
+  if (ev0) NF4LL_CUDA(cudaEventRecord(ev0, stream));
+  const int rc = launch_cfg<kFwd, 2, 256>(map, nib_map, mg, mu, mh, p, pl, stream);
+  if (rc == NF4LL_OK && ev1) NF4LL_CUDA(cudaEventRecord(ev1, stream));
+  return rc;
+}
+
 }  // namespace nf4ll
+
+extern "C" int nf4ll_forward_gate_up(const nf4ll_mat* W, const void* x, int64_t ldx, const nf4ll_lora* lora_gate,
+                                     const nf4ll_lora* lora_up, void* t_gate, void* t_up, int64_t M, void* g, int64_t ldg,
+                                     void* u, int64_t ldu, void* h, int64_t ldh, void* workspace, int64_t workspace_bytes,
+                                     int32_t* status, void* stream) {
+  return nf4ll::run_gate_up(W, x, ldx, lora_gate, lora_up, t_gate, t_up, M, g, ldg, u, ldu, h, ldh, workspace, workspace_bytes,
+                            status, stream);
+}
 
 extern "C" int64_t nf4ll_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t r) {
   using namespace nf4ll;

@@ -38,6 +38,10 @@ struct GemmParams {
   const float* seg_left[kMaxSegments];     // [M,16] fp32 T of the segment, or null (no LoRA on it)
   const __half* seg_right[kMaxSegments];   // lora_B of the segment, offset so that it is indexed by the fused output column
   float seg_scale[kMaxSegments];
+  // forward over gate|up with the gated-SiLU product in the epilogue: the weight is [2*gu_inter, K]
+  // (gate rows, then up rows), a tile is 128 gate + 128 up columns, seg_* [0] / [1] hold the two LoRA
+  // branches (lora_B not offset), and the three outputs g, u, h go through three tensor maps
+  int64_t gu_inter;        // 0: not this mode
   int splits;              // split of the contraction across blockIdx.z
   float* partial;          // [splits][M_pad][NO] fp32 when splits > 1
   int* counters;           // one per output tile when splits > 1 (zero on entry, zero on exit)

@@ -180,6 +180,31 @@ def forward_multi(w: Nf4Weight, x, segments, bias=None, out=None, workspace=None
     return y, ts
 
 
+def forward_gate_up(w: Nf4Weight, x, lora_gate=None, mask_gate=None, lora_up=None, mask_up=None, keep_scale=1.0,
+                    workspace=None):
+    """(g, u, h, t_gate, t_up) of an MLP's first half in one launch: `w` is gate_proj and up_proj stacked
+    ([2I, K], Nf4Weight.from_layer_group), h = silu(g) * u is formed in the kernel's epilogue (reference:
+    two GEMMs + gated_silu, solution/fast_qwen.py:1080-1108). g and u are views of one [M, 2I] buffer."""
+    _check_act(x, w.K, "x")
+    M, I = x.shape[0], w.N // 2
+    gu = torch.empty(M, 2 * I, dtype=torch.float16, device=x.device)
+    g, u = gu[:, :I], gu[:, I:]
+    h = torch.empty(M, I, dtype=torch.float16, device=x.device)
+    sg, rg = _lora_struct(lora_gate, mask_gate, keep_scale)
+    su, ru = _lora_struct(lora_up, mask_up, keep_scale)
+    tg = torch.empty(M, RANK, dtype=torch.float32, device=x.device) if lora_gate is not None else None
+    tu = torch.empty(M, RANK, dtype=torch.float32, device=x.device) if lora_up is not None else None
+    r = RANK if (lora_gate is not None or lora_up is not None) else 0
+    ws = _workspace(x.device, _workspace_need(M, I, w.K, r)) if workspace is None else workspace
+    _lib.check(_lib.lib().nf4ll_forward_gate_up(ctypes.byref(w._c), x.data_ptr(), x.stride(0), rg, ru,
+                                                None if tg is None else tg.data_ptr(), None if tu is None else tu.data_ptr(),
+                                                M, g.data_ptr(), g.stride(0), u.data_ptr(), u.stride(0), h.data_ptr(),
+                                                h.stride(0), ws.data_ptr(), ws.numel(), status_word(x.device).data_ptr(),
+                                                _lib.current_stream(x.device)))
+    del sg, su
+    return g, u, h, tg, tu
+
+
 def backward_dx(w: Nf4Weight, dy, lora=None, mask=None, keep_scale=1.0, out=None, accumulate=False,
                 want_u=False, workspace=None):
     """dx (+)= dy . W + keep_scale * mask (.) ((scale * dy . B) . A). Returns (dx, u) with

@@ -126,6 +126,22 @@ int nf4ll_forward_multi(const nf4ll_mat* W, const void* x, int64_t ldx, const vo
                         const nf4ll_segment* segments, int32_t n_segments, int64_t M, void* y, int64_t ldy,
                         void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
 
+/* gate|up forward with the gated-SiLU product in the epilogue. W is gate_proj and up_proj stacked
+ * ([2I, K], gate rows first: how the reference's packed layer stores them, solution/k_nf4.py:7-10, 61).
+ * One launch computes
+ *   g = x . Wg^T + LoRA_gate,   u = x . Wu^T + LoRA_up,   h = fp16(silu(g) * u)
+ * where a tile holds 128 gate and the matching 128 up columns, so the product is formed from the
+ * accumulators on their way out (from g and u as rounded to fp16: h is bit-identical to
+ * nf4ll_swiglu_forward on the stored g, u). Replaces the two GEMMs and the gated_silu kernel of
+ * solution/fast_qwen.py:1080-1108 (k_mlp.py:21-29). g and u are still written: the backward needs them.
+ * A LoRA branch needs its t_out (fp32 [M,r]). I must be a multiple of 8 (of 128 for the fused path;
+ * other widths, batches of at most 128 rows and calls under nf4ll_tune_override run the two
+ * projections and the stand-alone product instead). Workspace: nf4ll_workspace_bytes(M, I, K, r). */
+int nf4ll_forward_gate_up(const nf4ll_mat* W, const void* x, int64_t ldx, const nf4ll_lora* lora_gate,
+                          const nf4ll_lora* lora_up, void* t_gate, void* t_up, int64_t M, void* g, int64_t ldg,
+                          void* u, int64_t ldu, void* h, int64_t ldh, void* workspace, int64_t workspace_bytes,
+                          int32_t* status, void* stream);
+
 /* nf4ll_forward for callers that can neither allocate device memory nor pass a workspace - a plugin
  * host that bans allocations after start-up, a server whose memory pool is already sealed. It has no
  * counterpart in the reference. Same arguments and results as nf4ll_forward minus the workspace:

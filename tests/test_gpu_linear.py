@@ -124,6 +124,38 @@ def test_stacked_projections_in_one_launch_match_separate_calls(M):
         linear.forward_multi(wg, x, [(wg.N - 64, None, None, 1.0), (64, None, None, 1.0)])
 
 
+@pytest.mark.parametrize("M,lora_up", [(300, True), (1100, False), (100, True)])
+def test_gate_up_forward_with_the_gated_product_in_its_epilogue(M, lora_up):
+    """nf4ll_forward_gate_up against the two single-projection forwards and the stand-alone gated-SiLU
+    kernel: g, u within the GEMM tolerance, h bit-identical to the stand-alone kernel applied to the
+    stored g, u; M = 100 takes the composite path for short batches."""
+    from decentrik_prime_b200 import k_nf4, quantize
+    H, I = 512, 896
+    names = ("gate_proj", "up_proj")
+    lin = {n: quantize.random_nf4_weight(I, H, seed=80 + i, device="cuda") for i, n in enumerate(names)}
+    layer, code2 = k_nf4.repack_layer(lin, torch.device("cuda"), names=names)
+    gen = torch.Generator().manual_seed(M)
+    x = torch.randn(M, H, generator=gen).half().cuda()
+    ks = float(1.0 / torch.tensor(0.95, dtype=torch.float32))
+    def lora():
+        return ((torch.randn(16, H, generator=gen) * 0.05).half().cuda(), (torch.randn(I, 16, generator=gen) * 0.05).half().cuda(), 2.0)
+    def mask():
+        return (torch.rand(M, H, generator=gen) >= 0.05).to(torch.uint8).cuda()
+    lg, mg = lora(), mask()
+    lu, mu = (lora(), mask()) if lora_up else (None, None)
+    wg, wu = (linear.Nf4Weight.from_layer(layer, n, code2) for n in names)
+    g0, tg0 = linear.forward(wg, x, lora=lg, mask=mg, keep_scale=ks, want_t=True)
+    u0, tu0 = linear.forward(wu, x, lora=lu, mask=mu, keep_scale=ks, want_t=True)
+    w = linear.Nf4Weight.from_layer_group(layer, names, code2)
+    g, u, h, tg, tu = linear.forward_gate_up(w, x, lg, mg, lu, mu, ks)
+    linear.check_status()
+    assert_close("g", g, g0.double())
+    assert_close("u", u, u0.double())
+    assert_close("t_gate", tg, tg0.double())
+    assert (tu is None) == (tu0 is None)
+    assert torch.equal(h, linear.swiglu_forward(g.contiguous(), u.contiguous()))
+
+
 def test_config0_q_proj():
     """BASELINE config 0: W [1536,1536], X [2048,1536], LoRA r=16 alpha=32, dropout 0.05."""
     run_case(1536, 1536, 2048)
