@@ -21,6 +21,8 @@
 // one W row (= one quantisation block, 128 bytes), 8 rows per 1024-byte swizzle atom. Forward reads
 // it as a K-major B operand (contraction along the row), backward as an MN-major one (contraction
 // across rows), so the same NF4 bytes serve W and W^T.
+#include <cstdlib>
+
 #include "nf4ll_gemm_shared.cuh"
 
 namespace nf4ll {
@@ -1209,7 +1211,10 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
   // one CTA per SM (shared memory): a split-K grid of at most `sms` CTAs is resident as a whole
   {
     const int64_t ctas = pl.tiles_o * pl.tiles_m * pl.splits * (pl.pair ? 2 : 1);
-    p.coop = (pl.splits > 1 && ctas <= sms && !(g_debug & 8)) ? 1 : 0;
+    // NF4LL_NO_COOP=1 keeps the last-CTA reduction everywhere: a profiler that replays kernels one by one
+    // cannot launch the cooperative cluster variant
+    static const bool no_coop = [] { const char* e = std::getenv("NF4LL_NO_COOP"); return e && e[0] == '1'; }();
+    p.coop = (pl.splits > 1 && ctas <= sms && !(g_debug & 8) && !no_coop) ? 1 : 0;
   }
   int* counters = nullptr;
   int counter_words = 0;
