@@ -81,13 +81,17 @@ class DecoderLayerProjections:
         a[:, KV:2 * KV] += qkv[:, H + KV:]
         h1 = x + P["o_proj"].forward(a, masks.get("o_proj"), keep_scale)
         if self.fused_groups:
-            gu = torch.empty(M, 2 * self.inter, dtype=torch.float16, device=x.device)
-            self._forward_group(self.w_gu, ("gate_proj", "up_proj"), h1, masks, keep_scale, None, gu)
-            g, u = gu[:, :self.inter], gu[:, self.inter:]
+            # gate, up and the gated product in one launch
+            pg, pu = P["gate_proj"], P["up_proj"]
+            mg = masks.get("gate_proj") if pg.has_lora else None
+            mu = masks.get("up_proj") if pu.has_lora else None
+            g, u, h, tg, tu = linear.forward_gate_up(self.w_gu, h1, pg.lora, mg, pu.lora, mu, keep_scale)
+            pg._saved = (h1, mg, keep_scale, tg)
+            pu._saved = (h1, mu, keep_scale, tu)
         else:
             g = P["gate_proj"].forward(h1, masks.get("gate_proj"), keep_scale)
             u = P["up_proj"].forward(h1, masks.get("up_proj"), keep_scale)
-        h = linear.swiglu_forward(g, u)
+            h = linear.swiglu_forward(g, u)
         out = h1 + P["down_proj"].forward(h, masks.get("down_proj"), keep_scale)
         self._saved = (g, u)
         return out
