@@ -246,13 +246,15 @@ def run_ours(args):
     sampler = ClockSampler(local) if rank == 0 else None
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
-    torch.cuda.profiler.start()      # `ncu --profile-from-start off` captures the timed region only
+    if args.profile_leg == "step":
+        torch.cuda.profiler.start()      # `ncu --profile-from-start off` captures the timed region only
     t0.record()
     for i in range(args.steps):
         step(i, dev_x[i % N_INPUT_SETS], dev_dy[i % N_INPUT_SETS], mask_sets[i % N_INPUT_SETS], timed=True)
     t1.record()
     barrier()
-    torch.cuda.profiler.stop()
+    if args.profile_leg == "step":
+        torch.cuda.profiler.stop()
     ms = t0.elapsed_time(t1)
     clocks = sampler.stop() if sampler else None
     linear.check_status(dev)
@@ -344,8 +346,12 @@ def run_ours(args):
                         "ms_per_step": e2e_ms / args.steps},
                 "gpu_launches": 15 * args.steps, "clocks": clocks}
         if world == 1 and not args.no_stream:
+            if args.profile_leg == "stream":
+                torch.cuda.profiler.start()
             line["weight_stream"] = {"unit": "GB/s of NF4 bytes", "peak_gbs": pk["hbm_gbs"], "peak_source": pk["source"],
                                      "cases": weight_stream_numbers(dev, pk["hbm_gbs"])}
+            if args.profile_leg == "stream":
+                torch.cuda.profiler.stop()
         if world == 1 and not args.no_cpu:
             tf, dt, cores = time_cpu(128, 2, 1)
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
@@ -547,6 +553,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-stream", action="store_true", help="skip the small-batch weight-stream numbers")
+    ap.add_argument("--profile-leg", default="step", choices=("step", "stream"),
+                    help="which leg cudaProfilerStart/Stop brackets (for `ncu --profile-from-start off`): the timed "
+                         "steps, or the small-batch weight-stream measurements")
     ap.add_argument("--workload", default="mlp", choices=("mlp", "stack1.5b", "stack7b"),
                     help="mlp = the default bench line (BASELINE config 1); stack* = configs 2 / 3")
     args = ap.parse_args()
