@@ -363,9 +363,9 @@ def run_ours(args):
 
 
 def run_stack(args):
-    """Secondary workloads (not the driver's default line): the full projection stack of BASELINE
-    config 2 (`--workload stack1.5b`: 28 layers, 4 packed sequences of 64..512 tokens, one GPU) and
-    config 3 (`--workload stack7b`: Qwen2.5-7B shapes, M = 16384 packed rows split by rows over the
+    """Secondary workloads (not the default line): the full projection stack of benchmark
+    configuration 2 (`--workload stack1.5b`: 28 layers, 4 packed sequences of 64..512 tokens, one GPU) and
+    configuration 3 (`--workload stack7b`: Qwen2.5-7B shapes, M = 16384 packed rows split by rows over the
     ranks = strong scaling, LoRA gradients all-reduced once per step). Only projections and the
     minimal glue of decentrik_prime_b200/stack.py run; FLOPs are the projections' algorithmic FLOPs."""
     import torch
@@ -448,7 +448,7 @@ def run_stack(args):
 
 def weight_stream_numbers(dev, peak_gbs):
     """Secondary metric of the path: NF4 bytes streamed per second by the forward at decode-sized
-    batches (BASELINE config 4: Qwen2.5-32B shapes, LoRA r=16 fused, M in {1, 8, 64}). Distinct weight
+    batches (benchmark configuration 4: Qwen2.5-32B shapes, LoRA r=16 fused, M in {1, 8, 64}). Distinct weight
     copies larger than L2 (126 MB) rotate inside one CUDA graph so that every launch reads its NF4
     bytes from HBM; the figure is algorithmic bytes (0.516 B per weight) over the median replay time."""
     import statistics
@@ -557,7 +557,7 @@ def main():
                     help="which leg cudaProfilerStart/Stop brackets (for `ncu --profile-from-start off`): the timed "
                          "steps, or the small-batch weight-stream measurements")
     ap.add_argument("--workload", default="mlp", choices=("mlp", "stack1.5b", "stack7b"),
-                    help="mlp = the default bench line (BASELINE config 1); stack* = configs 2 / 3")
+                    help="mlp = the default bench line (benchmark configuration 1); stack* = configs 2 / 3")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

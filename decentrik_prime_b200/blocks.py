@@ -115,7 +115,7 @@ class Projection:
 
 
 def make_projection(n_out, n_in, seed, device, lora=False, bias=False, bucket=None, code2=None):
-    """A projection with a seeded synthetic NF4 weight ~ N(0, 0.02) (BASELINE config 0 construction)."""
+    """A projection with a seeded synthetic NF4 weight ~ N(0, 0.02) (benchmark configuration 0 construction)."""
     lin = quantize.random_nf4_weight(n_out, n_in, seed=seed, device=device, code2=code2)
     layer, c2 = k_nf4.repack_layer({"w": lin}, torch.device(device), names=("w",))
     w = linear.Nf4Weight.from_layer(layer, "w", c2)
@@ -128,7 +128,7 @@ def make_projection(n_out, n_in, seed, device, lora=False, bias=False, bucket=No
 
 
 class MlpBlock:
-    """gate/up/down of one decoder layer with LoRA on every projection (BASELINE config 1). The
+    """gate/up/down of one decoder layer with LoRA on every projection (benchmark configuration 1). The
     SiLU-gated product between up and down is either the library's fused kernel pair (the
     counterpart of the reference's gated_silu kernels) or plain PyTorch ops (fused_glue=False)."""
 

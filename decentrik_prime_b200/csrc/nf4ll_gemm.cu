@@ -1435,7 +1435,7 @@ extern "C" void nf4ll_debug_flags(int32_t flags) { nf4ll::g_debug = flags; }
 // that runs where cudaMalloc is illegal. For them the scratch of nf4ll_forward lives in a fixed
 // array in this library's device image. The array exists once per GPU that loads the library (each
 // such GPU gives up NF4LL_STATIC_SCRATCH_BYTES until the process exits), so its size is a
-// compromise: it covers one BASELINE config-0 forward (M = 2048 against a 1536 x 1536 weight with
+// compromise: it covers one benchmark configuration-0 forward (M = 2048 against a 1536 x 1536 weight with
 // LoRA, including split-K partial sums) and nothing much larger.
 //
 // In host code the array's name is only a handle; the device address is asked from the runtime

@@ -1,5 +1,5 @@
 """All seven projections of every decoder layer, packed the way the reference packs them, driven
-through the fused NF4 + LoRA linear: the projection stack of BASELINE configs 2 and 3.
+through the fused NF4 + LoRA linear: the projection stack of benchmark configurations 2 and 3.
 
 Per layer the 4-bit weights q, k, v, o, gate, up, down live in one flat PackedLayer buffer
 (k_nf4.repack_layer, same order and segment table as reference solution/k_nf4.py:126-173), so Q|K|V

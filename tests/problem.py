@@ -1,4 +1,4 @@
-"""Seeded synthetic problems for the NF4 + LoRA linear, built the way BASELINE config 0 describes:
+"""Seeded synthetic problems for the NF4 + LoRA linear, built the way benchmark configuration 0 describes:
 fp16 weight ~ N(0, 0.02) quantised to NF4 (block 64, double-quantised absmax), fp16 activations
 ~ N(0, 1), LoRA r=16 / alpha=32 with kaiming-uniform A and B ~ N(0, 0.01), dropout p=0.05 with the
 keep-mask drawn from the seed, keep_scale = 1 / float32(1 - p)."""

@@ -1,5 +1,5 @@
 """Fused NF4 + LoRA linear (forward, backward-dX, dA/dB) through the C ABI against the CPU oracle
-on identical seeded inputs. Tolerance (BASELINE north_star): max-abs-err <= 2e-2 and rel-L2 <= 1e-3
+on identical seeded inputs. Tolerance (the task statement): max-abs-err <= 2e-2 and rel-L2 <= 1e-3
 against the fp32/fp64-accumulated oracle O1; dequantised weights bit-exact."""
 
 import pytest
@@ -157,7 +157,7 @@ def test_gate_up_forward_with_the_gated_product_in_its_epilogue(M, lora_up):
 
 
 def test_config0_q_proj():
-    """BASELINE config 0: W [1536,1536], X [2048,1536], LoRA r=16 alpha=32, dropout 0.05."""
+    """benchmark configuration 0: W [1536,1536], X [2048,1536], LoRA r=16 alpha=32, dropout 0.05."""
     run_case(1536, 1536, 2048)
 
 
@@ -198,7 +198,7 @@ def test_autograd_function_matches_raw_calls():
 
 
 def test_full_size_linearity_property():
-    """At a BASELINE-size shape (1.5B gate_proj, M=2048) the oracle is too slow to run in full, so use
+    """At a full-size shape (1.5B gate_proj, M=2048) the oracle is too slow to run in full, so use
     properties of the map: a sampled set of output rows equals the oracle on those rows, and
     forward(x1 + x2) = forward(x1) + forward(x2) within fp16 rounding (no bias, no dropout)."""
     N, K, M = 8960, 1536, 2048

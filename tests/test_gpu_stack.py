@@ -1,4 +1,4 @@
-"""The projection stack (BASELINE config 2 in miniature): two decoder layers of seven NF4 projections
+"""The projection stack (benchmark configuration 2 in miniature): two decoder layers of seven NF4 projections
 each, LoRA on q and v, a packed varlen batch, forward and hand-written backward, against the same
 computation done projection by projection with the CPU oracle and the same fp16 glue."""
 
@@ -81,7 +81,7 @@ def test_two_layer_stack_matches_oracle():
                 assert rel <= 5e-3, (i, n, err, rel)
 
 
-def test_stack_flops_match_survey_figures():
+def test_stack_flops_per_token():
     """Algorithmic FLOPs per token per layer of the Qwen2.5-1.5B and 7B shapes: 4*N*K per projection
     (forward + backward-dX) plus the LoRA terms on q and v."""
     base_15b = 4 * (1536 * 1536 * 2 + 256 * 1536 * 2 + 8960 * 1536 * 3)
