@@ -187,7 +187,7 @@ class ClockSampler:
 def run_ours(args):
     import torch
     import torch.distributed as dist
-    from decentrik_prime_b200 import _lib, blocks, linear
+    from decentrik_prime_b200 import _lib, blocks, dp, linear
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -224,14 +224,21 @@ def run_ours(args):
             # every ROOFLINE_EVERY-th timed step has its tensor-core launches bracketed by events: the
             # event records cost ~3 % of a step, so the other steps run without them
             _hook_block(blk, ev_pairs if i % ROOFLINE_EVERY == 0 else None, M)
+        slot = i % N_WEIGHT_SETS
+        if sync is not None:
+            sync.wait_slot(slot)          # this layer's gradients of 8 steps ago have been exchanged
         y = blk.forward(x, masks, keep_scale)
         dx = blk.backward(dy)
-        if world > 1:
-            lo = (i % N_WEIGHT_SETS) * per_layer
-            dist.all_reduce(bucket.flat[lo:lo + per_layer])
+        if sync is not None:
+            # the exchange runs on a side stream under the next step's compute
+            sync.launch(slot, bucket.flat[slot * per_layer:(slot + 1) * per_layer])
         return y, dx
 
+    sync = dp.GradSync(dev, N_WEIGHT_SETS) if world > 1 else None
+
     def barrier():
+        if sync is not None:
+            sync.wait_all()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
@@ -251,6 +258,8 @@ def run_ours(args):
     t0.record()
     for i in range(args.steps):
         step(i, dev_x[i % N_INPUT_SETS], dev_dy[i % N_INPUT_SETS], mask_sets[i % N_INPUT_SETS], timed=True)
+    if sync is not None:
+        sync.wait_all()                   # the last exchanges are inside the timed region
     t1.record()
     barrier()
     if args.profile_leg == "step":
@@ -299,6 +308,8 @@ def run_ours(args):
             ev_done[s].record(main)
             with torch.cuda.stream(copy_out):
                 copy_out.wait_event(ev_done[s])
+                if sync is not None and sync.done[i % N_WEIGHT_SETS] is not None:
+                    copy_out.wait_event(sync.done[i % N_WEIGHT_SETS])    # the gradients leave the device summed
                 out_y[s].copy_(y, non_blocking=True)
                 out_dx[s].copy_(dx, non_blocking=True)
                 lo = (i % N_WEIGHT_SETS) * per_layer

@@ -18,3 +18,39 @@ def shard_rows(n_rows, world, rank, multiple=128):
     lo = (units * rank) // world * multiple
     hi = (units * (rank + 1)) // world * multiple
     return min(lo, n_rows), min(hi, n_rows)
+
+
+class GradSync:
+    """All-reduce of gradient-bucket slices on a side stream, so that the exchange of one step's LoRA
+    gradients overlaps the next step's compute. A slice is identified by a slot number; whoever writes
+    the slice again calls `wait_slot` first, and `wait_all` joins everything (end of a timed region,
+    before the optimiser reads the gradients)."""
+
+    def __init__(self, device, n_slots, group=None):
+        import torch
+        self.stream = torch.cuda.Stream(device)
+        self.done = [None] * n_slots
+        self.group = group
+
+    def launch(self, slot, tensor):
+        """Sum `tensor` (a view of the bucket) over the ranks, after everything queued so far on the
+        current stream."""
+        import torch
+        import torch.distributed as dist
+        self.stream.wait_stream(torch.cuda.current_stream(tensor.device))
+        with torch.cuda.stream(self.stream):
+            dist.all_reduce(tensor, group=self.group)
+            ev = torch.cuda.Event()
+            ev.record(self.stream)
+        self.done[slot] = ev
+
+    def wait_slot(self, slot):
+        import torch
+        if self.done[slot] is not None:
+            torch.cuda.current_stream().wait_event(self.done[slot])
+            self.done[slot] = None
+
+    def wait_all(self):
+        import torch
+        torch.cuda.current_stream().wait_stream(self.stream)
+        self.done = [None] * len(self.done)
