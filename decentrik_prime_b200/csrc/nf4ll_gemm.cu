@@ -646,8 +646,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
           bulk_commit();
           bulk_wait_read_all();
         }
-      } else
-      if (!direct && p.coop) {
+      } else if (!direct && p.coop) {
         // shared reduction, first half: every box of the tile that another split owns goes to this
         // split's slab as fp32, four boxes per staging round, rounds dealt to the warp groups in turn
         constexpr int NB = BM_TILES * (BN / 32);
@@ -691,7 +690,9 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
         }
         if (pending) flush();
       }
-      for (int mt = grp; mt < BM_TILES && !(!direct && p.coop) && !gu; mt += G) {
+      // plain paths: the whole accumulator goes out as fp16 (no split) or as this split's fp32 slab
+      const bool plain = !gu && (direct || !p.coop);
+      for (int mt = grp; plain && mt < BM_TILES; mt += G) {
         const uint32_t tacc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + mt * BN;
         const int row_g = static_cast<int>(m0 + mt * 128);
         if (direct) {
@@ -1126,7 +1127,7 @@ static int check_act(const void* ptr, int64_t ld, int64_t cols, const char* who,
   return NF4LL_OK;
 }
 
-static int check_lora(const nf4ll_lora* l, const char* who, bool need_mask_ld, int64_t K) {
+static int check_lora(const nf4ll_lora* l, const char* who, int64_t K) {
   if (!l) return NF4LL_OK;
   if (l->r != 16) { set_detail("%s: LoRA rank %d", who, l->r); return NF4LL_ERR_RANK; }
   if (!l->A || !l->B) { set_detail("%s: LoRA A/B null", who); return NF4LL_ERR_NULL; }
@@ -1135,7 +1136,7 @@ static int check_lora(const nf4ll_lora* l, const char* who, bool need_mask_ld, i
     set_detail("%s: LoRA A/B must be 16-byte aligned", who);
     return NF4LL_ERR_ALIGN;
   }
-  if (l->mask && (need_mask_ld || true) && ((reinterpret_cast<uintptr_t>(l->mask) & 15) || l->ld_mask % 16 || l->ld_mask < K)) {
+  if (l->mask && ((reinterpret_cast<uintptr_t>(l->mask) & 15) || l->ld_mask % 16 || l->ld_mask < K)) {
     set_detail("%s: mask must be 16-byte aligned with ld_mask a multiple of 16 and >= K", who);
     return NF4LL_ERR_ALIGN;
   }
@@ -1166,7 +1167,7 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
   const int64_t NO = mode == kFwd ? W->N : W->K, KC = mode == kFwd ? W->K : W->N;
   if (int rc = check_act(act, ldact, KC, who, mode == kFwd ? "x" : "dy")) return rc;
   if (int rc = check_act(out, ldo, NO, who, mode == kFwd ? "y" : "dx")) return rc;
-  if (int rc = check_lora(lora, who, mode == kBwd, W->K)) return rc;
+  if (int rc = check_lora(lora, who, W->K)) return rc;
   if (bias && (reinterpret_cast<uintptr_t>(bias) & 15)) { set_detail("%s: bias must be 16-byte aligned", who); return NF4LL_ERR_ALIGN; }
   if (M > (int64_t(1) << 30)) { set_detail("%s: M too large", who); return NF4LL_ERR_SHAPE; }
   if (int rc = require_sm100()) return rc;
@@ -1183,7 +1184,7 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
       }
       if (at % 256) narrow_tiles = true;
       at += segments[i].rows;
-      if (int rc = check_lora(segments[i].lora, who, false, W->K)) return rc;
+      if (int rc = check_lora(segments[i].lora, who, W->K)) return rc;
       if (segments[i].lora && !segments[i].t_out) { set_detail("%s: segment %d has LoRA but no t_out", who, i); return NF4LL_ERR_NULL; }
     }
     if (at != W->N) { set_detail("%s: segments cover %lld of %lld rows", who, static_cast<long long>(at), static_cast<long long>(W->N)); return NF4LL_ERR_SHAPE; }
@@ -1319,8 +1320,8 @@ static int run_gate_up(const nf4ll_mat* W, const void* x, int64_t ldx, const nf4
   if (int rc = check_act(g, ldg, I, who, "g")) return rc;
   if (int rc = check_act(u, ldu, I, who, "u")) return rc;
   if (int rc = check_act(h, ldh, I, who, "h")) return rc;
-  if (int rc = check_lora(lora_gate, who, false, W->K)) return rc;
-  if (int rc = check_lora(lora_up, who, false, W->K)) return rc;
+  if (int rc = check_lora(lora_gate, who, W->K)) return rc;
+  if (int rc = check_lora(lora_up, who, W->K)) return rc;
   if ((lora_gate && !t_gate) || (lora_up && !t_up)) { set_detail("%s: a LoRA branch needs its t_out", who); return NF4LL_ERR_NULL; }
   if (int rc = require_sm100()) return rc;
   if (M <= 128 || I % 128 || g_force_bm || g_force_bn || g_force_splits) {

@@ -9,7 +9,7 @@
 // for a deeper activation ring. Nothing is multicast except tcgen05.commit's mbarrier arrive.
 //
 // Synchronisation between the two CTAs uses mbarriers only (every wait bounded): the rank-1 CTA's
-// MMA warp relays "my stage s is loaded and dequantised" to a barrier in the rank-0 CTA with a
+// MMA warp relays "my stage s is loaded and dequantised" to the stage barrier of the rank-0 CTA with a
 // remote arrive; rank 0 frees stages / publishes the accumulator to both CTAs with a multicast commit.
 #include "nf4ll_gemm_shared.cuh"
 
@@ -18,7 +18,7 @@ namespace nf4ll {
 template <int BM_TILES>
 struct PairCfg {
   static constexpr int kStages = (BM_TILES == 2) ? 4 : 6;
-  static constexpr int kDequantWarps = 8;                 // 256 threads: two per quantisation block, 128 blocks per stage
+  static constexpr int kDequantWarps = 8;                 // two teams of 128 threads on alternate stages, one block per thread
   static constexpr int kThreads = 32 * (4 + kDequantWarps);
   static constexpr int kABytes = BM_TILES * 128 * 128;    // per stage: this CTA's 128 rows x 64 fp16 per accumulator
   static constexpr int kBBytes = 128 * 128;               // per stage: this CTA's 128 dequantised blocks
@@ -128,7 +128,6 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
   uint64_t* empty = bars + 2 * S;       // [S] the pair's MMAs on the stage are done (multicast commit)
   uint64_t* nib_full = bars + 3 * S;    // [S]
   uint64_t* nib_empty = bars + 4 * S;   // [S]
-  uint64_t* peer_ready = bars + 5 * S;  // [S] rank 0 only: rank 1's stage is loaded and dequantised
   uint64_t* lora_full = bars + 6 * S;
   uint64_t* acc_full = lora_full + 1;
   uint64_t* pre_full = lora_full + 2;
@@ -168,7 +167,6 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
       mbar_init(smem_u32(empty + s), 1);
       mbar_init(smem_u32(nib_full + s), 3);
       mbar_init(smem_u32(nib_empty + s), NDW / 2);
-      mbar_init(smem_u32(peer_ready + s), 1);
     }
     mbar_init(smem_u32(lora_full), NDW);
     mbar_init(smem_u32(acc_full), 1);
@@ -607,7 +605,9 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
         }
         if (pending) flush();
       }
-      for (int u = grp; u < BM_TILES * HALVES && !(!direct && p.coop); u += G) {
+      // plain paths: the whole accumulator goes out as fp16 (no split) or as this split's fp32 slab
+      const bool plain = direct || !p.coop;
+      for (int u = grp; plain && u < BM_TILES * HALVES; u += G) {
         const int mt = u / HALVES, ch = u % HALVES;
         const uint32_t tacc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + mt * BN + ch * 128;
         const int row_g = static_cast<int>(m0 + mt * 256);
