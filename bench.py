@@ -218,21 +218,52 @@ def run_ours(args):
 
     ev_pairs = []      # (start, stop, flops) of tensor-core kernels inside the timed region
 
+    graphs = {}        # (weight set, id of x) -> (CUDAGraph, outputs): whole steps captured once, replayed afterwards
+
     def step(i, x, dy, masks, timed=False):
         blk = layers[i % N_WEIGHT_SETS]
+        hooked = timed and i % ROOFLINE_EVERY == 0
         if timed:
             # every ROOFLINE_EVERY-th timed step has its tensor-core launches bracketed by events: the
             # event records cost ~3 % of a step, so the other steps run without them
-            _hook_block(blk, ev_pairs if i % ROOFLINE_EVERY == 0 else None, M)
+            _hook_block(blk, ev_pairs if hooked else None, M)
         slot = i % N_WEIGHT_SETS
         if sync is not None:
             sync.wait_slot(slot)          # this layer's gradients of 8 steps ago have been exchanged
-        y = blk.forward(x, masks, keep_scale)
-        dx = blk.backward(dy)
+        g = None if hooked else graphs.get((slot, x.data_ptr()))
+        if g is not None:
+            g[0].replay()                 # the same launches, issued by the GPU front end instead of Python
+            y, dx = g[1]
+        else:
+            y = blk.forward(x, masks, keep_scale)
+            dx = blk.backward(dy)
         if sync is not None:
             # the exchange runs on a side stream under the next step's compute
             sync.launch(slot, bucket.flat[slot * per_layer:(slot + 1) * per_layer])
         return y, dx
+
+    def capture_steps(xs, dys):
+        """One CUDA graph per (weight set, input set) pair the loops below use: the step's launches are
+        fixed, so the ~0.5 ms of Python per step need not race the GPU. Falls back to eager on failure."""
+        if args.no_graphs:
+            return
+        side = torch.cuda.Stream(dev)
+        try:
+            with torch.cuda.stream(side):
+                for i in range(N_WEIGHT_SETS):
+                    x, dy, masks = xs[i % len(xs)], dys[i % len(dys)], mask_sets[i % N_INPUT_SETS]
+                    blk = layers[i % N_WEIGHT_SETS]
+                    blk._ev_sink = None
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side):
+                        y = blk.forward(x, masks, keep_scale)
+                        dx = blk.backward(dy)
+                    graphs[(i, x.data_ptr())] = (g, (y, dx))
+            torch.cuda.synchronize()
+        except Exception as exc:      # capture is an optimisation, never a requirement
+            graphs.clear()
+            torch.cuda.synchronize()
+            print(f"[bench] CUDA graph capture failed ({type(exc).__name__}: {exc}); running eagerly", file=sys.stderr)
 
     sync = dp.GradSync(dev, N_WEIGHT_SETS) if world > 1 else None
 
@@ -248,6 +279,7 @@ def run_ours(args):
         step(i, dev_x[i % N_INPUT_SETS], dev_dy[i % N_INPUT_SETS], mask_sets[i % N_INPUT_SETS])
     barrier()
     linear.check_status(dev)
+    capture_steps(dev_x, dev_dy)
     _fill_event_pool(6 * args.steps + 6)
     torch.cuda.synchronize()
     sampler = ClockSampler(local) if rank == 0 else None
@@ -318,6 +350,7 @@ def run_ours(args):
                 y.record_stream(copy_out); dx.record_stream(copy_out)
         main.wait_stream(copy_out)
 
+    capture_steps(in_x, in_dy)
     e2e_loop(max(args.warmup, 1))
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -346,7 +379,10 @@ def run_ours(args):
                            "lora_rank": 16, "dropout": P_DROP, "parallelism": f"dp{world}",
                            "tokens_per_s": world * M * args.steps / (ms * 1e-3),
                            "l2": f"inputs larger than L2: {N_WEIGHT_SETS} weight sets and {N_INPUT_SETS} input sets rotate; "
-                                 "one step touches > 300 MB of activations"},
+                                 "one step touches > 300 MB of activations",
+                           "launch": ("cuda graphs: one captured step per weight set, replayed; every third timed step "
+                                      "of the value loop issued eagerly with event hooks") if graphs
+                           else "eager: every launch issued from python"},
                 "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                              "frac": (achieved / peak) if achieved else None, "traffic": None,
                              "peak_source": pk["source"] + " sustained bf16",
@@ -564,6 +600,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-stream", action="store_true", help="skip the small-batch weight-stream numbers")
+    ap.add_argument("--no-graphs", action="store_true", help="issue every step from Python instead of replaying CUDA graphs")
     ap.add_argument("--profile-leg", default="step", choices=("step", "stream"),
                     help="which leg cudaProfilerStart/Stop brackets (for `ncu --profile-from-start off`): the timed "
                          "steps, or the small-batch weight-stream measurements")
