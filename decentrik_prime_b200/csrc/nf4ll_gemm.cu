@@ -10,13 +10,18 @@
 //
 // One CTA computes a (BM_TILES*128) x BN output tile. Roles by warp:
 //   warp 0        TMA producer: 128x64 fp16 activation boxes (128-byte swizzle) and the tile's packed
-//                 4-bit codes (BN quantisation blocks x 32 bytes) into shared-memory rings
+//                 4-bit codes (BN quantisation blocks x 32 bytes) into shared-memory rings; after a
+//                 split contraction it streams other splits' partial sums back in
 //   warp 1        allocates tensor memory; one lane issues every tcgen05.mma and commit
-//   warps 2-3     stage the two rank-16 LoRA operands (canonical no-swizzle layout), then recover the
-//                 fp32 absmax of every block of each stage (code2[q] * scale2 + offset2) into shared memory
-//   warps 4..     BN threads: each owns one 64-weight quantisation block per ring stage: 2 x 128-bit
-//                 shared loads of codes, block table in registers, 8 x 128-bit swizzled shared
-//                 stores; afterwards the same warps drain tensor memory (epilogue)
+//   warps 2-3     recover the fp32 absmax of every block of each stage (code2[q] * scale2 + offset2)
+//                 into shared memory
+//   warps 4..     BN threads in two teams that take alternate stages, two 64-weight quantisation
+//                 blocks per thread: 128-bit shared loads of codes, block table in registers, 8 x
+//                 128-bit swizzled shared stores per block. Before that they stage the rank-16 LoRA
+//                 operands (and, in the backward with dropout, scale the LoRA product in tensor
+//                 memory by the keep-mask); afterwards they drain tensor memory (epilogue)
+// Variants of the forward: several projections stacked along N with one LoRA branch per segment,
+// and gate|up tiles (128 gate + 128 up columns) whose epilogue also writes silu(g) * u.
 // The weight tile in shared memory is the same in both directions: rows of 64 consecutive weights of
 // one W row (= one quantisation block, 128 bytes), 8 rows per 1024-byte swizzle atom. Forward reads
 // it as a K-major B operand (contraction along the row), backward as an MN-major one (contraction

@@ -273,6 +273,40 @@ def test_mlp_block_fused_glue_matches_pytorch_glue():
         assert rel <= 2e-3, (err, rel)
 
 
+def test_block_step_replays_from_a_cuda_graph():
+    """Every launch of a block step (cluster, cooperative and programmatic-dependent launches included)
+    can be captured into a CUDA graph; the replay gives the eager results bit for bit (the gradient
+    reductions use atomics, so gradients are compared with a tolerance)."""
+    from decentrik_prime_b200 import blocks
+    dev = torch.device("cuda")
+    bucket = blocks.GradBucket(blocks.MlpBlock.grad_numel(1536, 1024), dev)
+    blk = blocks.MlpBlock(1536, 1024, seed=21, device=dev, bucket=bucket)     # down_proj: 1536-wide output, split contraction
+    gen = torch.Generator().manual_seed(2)
+    M = 2048
+    x = torch.randn(M, 1536, generator=gen).half().cuda()
+    dy = torch.randn(M, 1536, generator=gen).half().cuda()
+    masks = [(torch.rand(M, k, generator=gen) >= 0.05).to(torch.uint8).cuda() for k in (1536, 1536, 1024)]
+    ks = 1.0 / 0.95
+    for _ in range(2):
+        y0 = blk.forward(x, masks, ks)
+        dx0 = blk.backward(dy)
+    g0 = bucket.flat.clone()
+    y0, dx0 = y0.clone(), dx0.clone()
+    side = torch.cuda.Stream(dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            y1 = blk.forward(x, masks, ks)
+            dx1 = blk.backward(dy)
+    torch.cuda.synchronize()
+    for _ in range(3):
+        graph.replay()
+    linear.check_status()
+    assert torch.equal(y1, y0) and torch.equal(dx1, dx0)
+    err, rel = nf4_oracle.errors(bucket.flat, g0.double())
+    assert rel <= 1e-5, (err, rel)
+
+
 def test_split_contraction_is_stable_under_back_to_back_launches():
     """The split-contraction path (partial sums through scratch, the splits of a tile share the final
     reduction) must give the same bits on every launch: 100 forwards queued back to back without host
