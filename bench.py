@@ -34,6 +34,7 @@ HIDDEN, INTER, M_ROWS, P_DROP = 1536, 8960, 2048, 0.05
 WORKLOAD = "qwen2.5-1.5b-mlp-block-M2048"
 METRIC = "nf4_lora_linear_fwd_bwd_tflops_M2048"
 N_WEIGHT_SETS, N_INPUT_SETS = 8, 4
+NCU_DRAM_BYTES_PER_LAUNCH = 53.0e6
 ROOFLINE_EVERY = 3      # timed steps whose tensor-core launches are bracketed by events: every third
 
 
@@ -384,7 +385,10 @@ def run_ours(args):
                                       "of the value loop issued eagerly with event hooks") if graphs
                            else "eager: every launch issued from python"},
                 "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                             "frac": (achieved / peak) if achieved else None, "traffic": None,
+                             "frac": (achieved / peak) if achieved else None,
+                             # DRAM bytes per tensor-core launch (read + written), mean over the five launches of a
+                             # step, from the ncu capture summarised in profiles/nf4_gemm_kernels_mlp_block_M2048.md
+                             "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "traffic_unit": "bytes per launch (ncu, one step)",
                              "peak_source": pk["source"] + " sustained bf16",
                              "frac_of_burst": (achieved / pk["tflops_burst"]) if achieved else None,
                              "kernel": "nf4_gemm_kernel (forward and backward-dX launches)",
