@@ -213,6 +213,8 @@ int lora_down_launch(const void* act, int64_t ldact, const uint8_t* mask, int64_
   int64_t ks = (2 * static_cast<int64_t>(sms)) / row_groups;     // at most two CTAs per SM: one wave, no tail
   if (ks > units) ks = units;
   if (ks < 1) ks = 1;
+  // decode-sized batches are all latency: eight CTAs in one cluster (no zero-fill, no atomics) beat more CTAs + a memset
+  if (ks > 8 && M * C <= (int64_t(1) << 21)) ks = 8;
   const int64_t c_per_cta = (units + ks - 1) / ks * (kDownWarps * 32);
   ks = (C + c_per_cta - 1) / c_per_cta;
   dim3 grid(static_cast<unsigned>(row_groups), static_cast<unsigned>(ks));

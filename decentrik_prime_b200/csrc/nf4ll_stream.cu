@@ -52,6 +52,12 @@ struct StreamParams {
 template <int NT, bool FULL4>
 __global__ void __launch_bounds__(kStreamWarps * 32, 4)
 nf4_stream_kernel(const StreamParams p) {
+  // Launched as a programmatic dependent of the kernel before it. With a LoRA branch that kernel is the
+  // rank-16 projection T = x . A^T, itself launched after everything earlier on the stream has
+  // finished: x and the weights can be read at once and only the epilogue, which needs T, waits, so
+  // the weight stream hides the projection. Without LoRA the predecessor may be x's producer: wait first.
+  if (p.t32 == nullptr) pdl_wait();
+  pdl_launch_dependents();
   __shared__ float s_code2[256];
   __shared__ float s_part[kStreamWarps][16][8 * NT + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -140,6 +146,7 @@ nf4_stream_kernel(const StreamParams p) {
     s_part[warp][g + 8][8 * i + 2 * t + 1] = acc[i][3];
   }
   __syncthreads();
+  if (p.t32 != nullptr) pdl_wait();              // T comes from the kernel this one was launched behind
   for (int idx = threadIdx.x; idx < 16 * 8 * NT; idx += kStreamWarps * 32) {
     const int r = idx & 15, tok = idx >> 4;      // consecutive threads -> consecutive output columns
     if (tok < p.M) {
@@ -174,12 +181,10 @@ int stream_forward_launch(const nf4ll_mat* W, const void* x, int64_t ldx, const 
   const bool full4 = (W->K % 256) == 0;
   const cudaStream_t st = stream;
   const int th = kStreamWarps * 32;
-  if (M <= 8) {
-    if (full4) nf4_stream_kernel<1, true><<<grid, th, 0, st>>>(p); else nf4_stream_kernel<1, false><<<grid, th, 0, st>>>(p);
-  } else {
-    if (full4) nf4_stream_kernel<2, true><<<grid, th, 0, st>>>(p); else nf4_stream_kernel<2, false><<<grid, th, 0, st>>>(p);
-  }
-  NF4LL_CUDA(cudaGetLastError());
+  PdlLaunch lc(dim3(grid), dim3(th), 0, st);
+  void (*kernel)(const StreamParams) = (M <= 8) ? (full4 ? nf4_stream_kernel<1, true> : nf4_stream_kernel<1, false>)
+                                                : (full4 ? nf4_stream_kernel<2, true> : nf4_stream_kernel<2, false>);
+  NF4LL_CUDA(cudaLaunchKernelEx(&lc.cfg, kernel, p));
   return NF4LL_OK;
 }
 
