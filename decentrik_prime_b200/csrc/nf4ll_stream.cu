@@ -27,7 +27,6 @@ __device__ __forceinline__ void mma16816_acc(float (&c)[4], uint32_t a0, uint32_
 // The 16 levels rounded to fp16, as byte planes for decode_word (same structure as a block table).
 __device__ __forceinline__ BlockTable level_table() { return make_block_table(1.0f); }
 
-constexpr int kStreamWarps = 8;
 
 struct StreamParams {
   const uint8_t* nib;
@@ -49,8 +48,10 @@ struct StreamParams {
 
 // NT = number of 8-token tiles (1: M <= 8, 2: M <= 16). FULL4: the row holds a multiple of four
 // quantisation blocks (every Qwen2.5 projection does), so the group-of-four loop needs no tail tests.
-template <int NT, bool FULL4>
-__global__ void __launch_bounds__(kStreamWarps * 32, 4)
+// kStreamWarps: warps per CTA that split the contraction (8; 16 for long rows under few CTAs, where eight
+// warps per CTA would leave the SMs half empty).
+template <int NT, bool FULL4, int kStreamWarps>
+__global__ void __launch_bounds__(kStreamWarps * 32, NT == 1 ? 32 / kStreamWarps : (kStreamWarps == 8 ? 2 : 1))
 nf4_stream_kernel(const StreamParams p) {
   // Launched as a programmatic dependent of the kernel before it. With a LoRA branch that kernel is the
   // rank-16 projection T = x . A^T, itself launched after everything earlier on the stream has
@@ -62,7 +63,7 @@ nf4_stream_kernel(const StreamParams p) {
   __shared__ float s_part[kStreamWarps][16][8 * NT + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  s_code2[threadIdx.x] = p.code2[threadIdx.x];
+  if (threadIdx.x < 256) s_code2[threadIdx.x] = p.code2[threadIdx.x];
   __syncthreads();
 
   const int64_t n0 = static_cast<int64_t>(blockIdx.x) * 16;
@@ -180,10 +181,16 @@ int stream_forward_launch(const nf4ll_mat* W, const void* x, int64_t ldx, const 
   const unsigned grid = static_cast<unsigned>(W->N / 16);
   const bool full4 = (W->K % 256) == 0;
   const cudaStream_t st = stream;
-  const int th = kStreamWarps * 32;
-  PdlLaunch lc(dim3(grid), dim3(th), 0, st);
-  void (*kernel)(const StreamParams) = (M <= 8) ? (full4 ? nf4_stream_kernel<1, true> : nf4_stream_kernel<1, false>)
-                                                : (full4 ? nf4_stream_kernel<2, true> : nf4_stream_kernel<2, false>);
+  int dev = 0, sms = 148;
+  NF4LL_CUDA(cudaGetDevice(&dev));
+  NF4LL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  // few CTAs (narrow outputs) with long rows: sixteen warps per CTA keep the SMs occupied
+  const bool wide = full4 && grid < 3u * static_cast<unsigned>(sms) && W->K / 64 >= 256;
+  void (*kernel)(const StreamParams);
+  if (wide) kernel = (M <= 8) ? nf4_stream_kernel<1, true, 16> : nf4_stream_kernel<2, true, 16>;
+  else kernel = (M <= 8) ? (full4 ? nf4_stream_kernel<1, true, 8> : nf4_stream_kernel<1, false, 8>)
+                         : (full4 ? nf4_stream_kernel<2, true, 8> : nf4_stream_kernel<2, false, 8>);
+  PdlLaunch lc(dim3(grid), dim3(wide ? 512 : 256), 0, st);
   NF4LL_CUDA(cudaLaunchKernelEx(&lc.cfg, kernel, p));
   return NF4LL_OK;
 }
