@@ -452,10 +452,33 @@ def run_stack(args):
     masks = [masks[i % n_mask_sets] for i in range(layers)]
     keep_scale = 1.0 / float(torch.tensor(1.0 - P_DROP, dtype=torch.float32))
 
+    graph = [None]
+
     def step():
-        st.step(x, dy, masks, keep_scale)
+        if graph[0] is not None:
+            graph[0].replay()
+        else:
+            st.step(x, dy, masks, keep_scale)
         if world > 1:
             dist.all_reduce(st.bucket.flat)
+
+    def capture():
+        """The ~1000 launches of a stack step as one CUDA graph: issued from Python they cost more host time
+        than GPU time at the small configuration. Falls back to eager on failure."""
+        if args.no_graphs:
+            return
+        side = torch.cuda.Stream(dev)
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(g, stream=side):
+                    st.step(x, dy, masks, keep_scale)
+            torch.cuda.synchronize()
+            graph[0] = g
+        except Exception as exc:
+            graph[0] = None
+            torch.cuda.synchronize()
+            print(f"[bench] CUDA graph capture failed ({type(exc).__name__}: {exc}); running eagerly", file=sys.stderr)
 
     def barrier():
         if world > 1:
@@ -467,6 +490,9 @@ def run_stack(args):
         step()
     barrier()
     linear.check_status(dev)
+    capture()
+    step()
+    barrier()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
     for _ in range(steps):
@@ -491,7 +517,8 @@ def run_stack(args):
                 "data": "synthetic",
                 "config": {"workload": args.workload, "rows": M_total, "rows_per_gpu": M, "layers": layers, "hidden": hidden,
                            "intermediate": inter, "kv": kv, "lora": "r=16 on q_proj, v_proj", "note": note,
-                           "tflops": flops * steps / (ms * 1e-3) / 1e12, "parallelism": f"dp{world}"}}
+                           "tflops": flops * steps / (ms * 1e-3) / 1e12, "parallelism": f"dp{world}",
+                           "launch": "cuda graph of the whole step, replayed" if graph[0] is not None else "eager"}}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
