@@ -124,13 +124,13 @@ def test_stacked_projections_in_one_launch_match_separate_calls(M):
         linear.forward_multi(wg, x, [(wg.N - 64, None, None, 1.0), (64, None, None, 1.0)])
 
 
-@pytest.mark.parametrize("M,lora_up", [(300, True), (1100, False), (100, True)])
-def test_gate_up_forward_with_the_gated_product_in_its_epilogue(M, lora_up):
+@pytest.mark.parametrize("M,lora_up,I", [(300, True, 896), (1100, False, 896), (100, True, 896), (300, True, 960)])
+def test_gate_up_forward_with_the_gated_product_in_its_epilogue(M, lora_up, I):
     """nf4ll_forward_gate_up against the two single-projection forwards and the stand-alone gated-SiLU
     kernel: g, u within the GEMM tolerance, h bit-identical to the stand-alone kernel applied to the
-    stored g, u; M = 100 takes the composite path for short batches."""
+    stored g, u; M = 100 (short batch) and I = 960 (not a multiple of 128) take the composite path."""
     from decentrik_prime_b200 import k_nf4, quantize
-    H, I = 512, 896
+    H = 512
     names = ("gate_proj", "up_proj")
     lin = {n: quantize.random_nf4_weight(I, H, seed=80 + i, device="cuda") for i, n in enumerate(names)}
     layer, code2 = k_nf4.repack_layer(lin, torch.device("cuda"), names=names)
