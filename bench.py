@@ -7,16 +7,22 @@ Workload (`config.workload` = "qwen2.5-1.5b-mlp-block-M2048"): the gate, up (153
 down (8960 -> 1536) projections of one Qwen2.5-1.5B decoder layer, NF4 weights (block 64,
 double-quantised absmax) drawn N(0, 0.02) from a seed, LoRA r=16 / alpha=32 with dropout p=0.05 on
 every projection, M = 2048 packed token rows per GPU, forward + backward-dX + dA/dB, frozen base
-(no dW). The SiLU-gated product between up and down is PyTorch. One step = one forward and one
-backward of the block. Metric: algorithmic TFLOP/s, FLOPs = sum over projections of
+(no dW). The SiLU-gated product between up and down runs in the library's kernels. One step = one
+forward and one backward of the block. Metric: algorithmic TFLOP/s, FLOPs = sum over projections of
 4*M*N*K + 6*M*16*(N+K) (dequantisation, bias, dropout and epilogues count as zero).
 
 With N > 1 (torchrun, one rank per GPU) token rows are data-parallel: each rank runs the same block
 on its own 2048 rows (weak scaling), NF4 weights replicated, and the fp32 LoRA-gradient bucket is
 all-reduced with NCCL every step inside the timed region.
 
-`--impl reference` times the reference's own CPU arithmetic for the same block (oracle O2: dequant
-into fp16, fp32-accumulated GEMMs rounded to fp16 where the reference rounds) on the host cores.
+Besides the headline numbers the line carries, at N = 1, benchmark configuration 0 (one q_proj linear),
+configuration 2 (the 1.5B projection stack) and configuration 4 (small-batch weight streaming, with a
+roofline object of its own), and at every N configuration 3 (Qwen2.5-7B shapes, 16384 packed rows split by
+rows over the ranks: strong scaling, LoRA gradients all-reduced per layer under the backward).
+
+`--impl reference` times the reference's own CPU arithmetic for the same block at the same M = 2048
+(oracle O2: dequant into fp16, fp32-accumulated GEMMs rounded to fp16 where the reference rounds) on
+all host cores; it runs as many of the requested steps as fit a time budget of about 100 s.
 """
 
 import argparse
@@ -34,7 +40,10 @@ HIDDEN, INTER, M_ROWS, P_DROP = 1536, 8960, 2048, 0.05
 WORKLOAD = "qwen2.5-1.5b-mlp-block-M2048"
 METRIC = "nf4_lora_linear_fwd_bwd_tflops_M2048"
 N_WEIGHT_SETS, N_INPUT_SETS = 8, 4
+# mean DRAM bytes (read + written) per tensor-core launch of a step, from an ncu capture of one step (not a
+# measurement of this run); reported with that label
 NCU_DRAM_BYTES_PER_LAUNCH = 53.0e6
+CPU_BUDGET_S = 100.0
 ROOFLINE_EVERY = 9      # timed steps whose tensor-core launches are bracketed by events: every ninth (9 and the 8 weight sets are coprime)
 
 
@@ -107,32 +116,45 @@ def cpu_problem(M, seed=0):
     return parts, x, dy, masks, keep_scale
 
 
-def time_cpu(M, steps, warmup):
+def time_cpu(M, steps, warmup, budget_s=CPU_BUDGET_S):
+    """(TFLOP/s, seconds per step, cores, timed steps): at most `steps` timed steps, fewer when the time
+    budget runs out first (every step is the whole block at M rows, dequantisation included)."""
     import torch
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     prob = cpu_problem(M)
+    t_start = time.perf_counter()
     for _ in range(warmup):
         cpu_block_step(*prob)
-    t0 = time.perf_counter()
-    for _ in range(steps):
+    done, t0 = 0, time.perf_counter()
+    while done < max(steps, 1):
         cpu_block_step(*prob)
-    dt = (time.perf_counter() - t0) / max(steps, 1)
-    return block_flops(M) / dt / 1e12, dt, cores
+        done += 1
+        if time.perf_counter() - t_start > budget_s:
+            break
+    dt = (time.perf_counter() - t0) / done
+    return block_flops(M) / dt / 1e12, dt, cores, done
+
+
+def block_config(world):
+    """The same dictionary in both arms (the driver compares them)."""
+    return {"workload": WORKLOAD, "rows_per_gpu": M_ROWS, "hidden": HIDDEN, "intermediate": INTER,
+            "lora_rank": 16, "dropout": P_DROP, "parallelism": f"dp{world}",
+            "l2": f"inputs larger than L2: {N_WEIGHT_SETS} weight sets and {N_INPUT_SETS} input sets rotate; "
+                  "one step touches > 300 MB of activations"}
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    M = 256
-    tf, dt, cores = time_cpu(M, max(args.steps, 1), max(min(args.warmup, 1), 0))
-    sample = f"same block, M={M} of {M_ROWS} rows per step, dequantisation of all three weights included"
+    tf, dt, cores, done = time_cpu(M_ROWS, args.steps, 1 if args.warmup > 0 else 0)
+    sample = (f"the same block at the same M={M_ROWS} rows, dequantisation of all three weights included in every step; "
+              f"{done} of the {args.steps} requested steps timed (time budget {CPU_BUDGET_S:.0f} s)")
     line = {"impl": "reference", "metric": METRIC, "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+            "steps": args.steps, "steps_timed": done, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "rows_per_gpu": M_ROWS, "hidden": HIDDEN, "intermediate": INTER,
-                       "lora_rank": 16, "dropout": P_DROP},
+            "config": block_config(args.gpus),
             "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -151,7 +173,7 @@ class ClockSampler:
         self.proc = None
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             pass
@@ -202,26 +224,32 @@ def run_ours(args):
     h = _lib.lib()
     M = M_ROWS
     keep_scale = 1.0 / float(torch.tensor(1.0 - P_DROP, dtype=torch.float32))
+    sampler = ClockSampler(local) if rank == 0 else None      # runs from before the warm-up to the end of the e2e leg
 
     # replicated weights: several distinct layers so that consecutive steps stream different NF4 bytes
     bucket = blocks.GradBucket(N_WEIGHT_SETS * blocks.MlpBlock.grad_numel(HIDDEN, INTER), dev)
     layers = [blocks.MlpBlock(HIDDEN, INTER, seed=100 + i, device=dev, lora=True, bucket=bucket) for i in range(N_WEIGHT_SETS)]
     per_layer = blocks.MlpBlock.grad_numel(HIDDEN, INTER)
     gen = torch.Generator().manual_seed(1234 + rank)       # every rank has its own rows
-    host_x = [torch.randn(M, HIDDEN, generator=gen).half().pin_memory() for _ in range(N_INPUT_SETS)]
-    host_dy = [torch.randn(M, HIDDEN, generator=gen).half().pin_memory() for _ in range(N_INPUT_SETS)]
-    dev_x = [t.to(dev) for t in host_x]
-    dev_dy = [t.to(dev) for t in host_dy]
+    # x and dy of a step lie back to back in one pinned buffer: one host-to-device copy per step
+    host_in = [torch.randn(2, M, HIDDEN, generator=gen).half().pin_memory() for _ in range(N_INPUT_SETS)]
+    dev_in = [t.to(dev) for t in host_in]
     gdev = torch.Generator(device=dev).manual_seed(77 + rank)
     mask_sets = [[(torch.rand(M, k, device=dev, generator=gdev) >= P_DROP).to(torch.uint8) for k in (HIDDEN, HIDDEN, INTER)]
                  for _ in range(N_INPUT_SETS)]
     flops = block_flops(M)
 
     ev_pairs = []      # (start, stop, flops) of tensor-core kernels inside the timed region
+    graphs = {}        # (weight set, id of the input buffer) -> CUDAGraph: whole steps captured once, replayed afterwards
+    launches_per_step = [None]
 
-    graphs = {}        # (weight set, id of x) -> (CUDAGraph, outputs): whole steps captured once, replayed afterwards
+    def run_block(blk, inp, masks, out):
+        """One forward + backward of a block through the public API; y and dx land in `out` ([2, M, HIDDEN])."""
+        y = blk.forward(inp[0], masks, keep_scale, out=out[0])
+        dx = blk.backward(inp[1], out=out[1])
+        return y, dx
 
-    def step(i, x, dy, masks, timed=False):
+    def step(i, inp, masks, out, timed=False):
         blk = layers[i % N_WEIGHT_SETS]
         hooked = timed and i % ROOFLINE_EVERY == 0
         if timed:
@@ -231,20 +259,17 @@ def run_ours(args):
         slot = i % N_WEIGHT_SETS
         if sync is not None:
             sync.wait_slot(slot)          # this layer's gradients of 8 steps ago have been exchanged
-        g = None if hooked else graphs.get((slot, x.data_ptr()))
+        g = None if hooked else graphs.get((slot, inp.data_ptr()))
         if g is not None:
-            g[0].replay()                 # the same launches, issued by the GPU front end instead of Python
-            y, dx = g[1]
+            g.replay()                    # the same launches, issued by the GPU front end instead of Python
         else:
-            y = blk.forward(x, masks, keep_scale)
-            dx = blk.backward(dy)
+            run_block(blk, inp, masks, out)
         if sync is not None:
             # the exchange runs on a side stream under the next step's compute
             sync.launch(slot, bucket.flat[slot * per_layer:(slot + 1) * per_layer])
-        return y, dx
 
-    def capture_steps(xs, dys):
-        """One CUDA graph per (weight set, input set) pair the loops below use: the step's launches are
+    def capture_steps(inputs, outs):
+        """One CUDA graph per (weight set, input buffer) pair the loops below use: the step's launches are
         fixed, so the ~0.5 ms of Python per step need not race the GPU. Falls back to eager on failure."""
         if args.no_graphs:
             return
@@ -252,14 +277,13 @@ def run_ours(args):
         try:
             with torch.cuda.stream(side):
                 for i in range(N_WEIGHT_SETS):
-                    x, dy, masks = xs[i % len(xs)], dys[i % len(dys)], mask_sets[i % N_INPUT_SETS]
+                    inp, out, masks = inputs[i % len(inputs)], outs[i % len(outs)], mask_sets[i % N_INPUT_SETS]
                     blk = layers[i % N_WEIGHT_SETS]
                     blk._ev_sink = None
                     g = torch.cuda.CUDAGraph()
                     with torch.cuda.graph(g, stream=side):
-                        y = blk.forward(x, masks, keep_scale)
-                        dx = blk.backward(dy)
-                    graphs[(i, x.data_ptr())] = (g, (y, dx))
+                        run_block(blk, inp, masks, out)
+                    graphs[(i, inp.data_ptr())] = g
             torch.cuda.synchronize()
         except Exception as exc:      # capture is an optimisation, never a requirement
             graphs.clear()
@@ -276,21 +300,26 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     # ---------------- device-resident throughput ("value")
-    for i in range(args.warmup):
-        step(i, dev_x[i % N_INPUT_SETS], dev_dy[i % N_INPUT_SETS], mask_sets[i % N_INPUT_SETS])
+    dev_out = [torch.empty(2, M, HIDDEN, dtype=torch.float16, device=dev) for _ in range(N_INPUT_SETS)]
+    for i in range(max(args.warmup, 3)):
+        if i == 1:
+            n0 = h.nf4ll_launch_count()
+        step(i, dev_in[i % N_INPUT_SETS], mask_sets[i % N_INPUT_SETS], dev_out[i % N_INPUT_SETS])
+        if i == 1:
+            # kernels of the library in one step, counted by the library itself (+1: the gradient fill is PyTorch's)
+            launches_per_step[0] = int(h.nf4ll_launch_count() - n0) + 1
     barrier()
     linear.check_status(dev)
-    capture_steps(dev_x, dev_dy)
+    capture_steps(dev_in, dev_out)
     _fill_event_pool(6 * args.steps + 6)
     torch.cuda.synchronize()
-    sampler = ClockSampler(local) if rank == 0 else None
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     if args.profile_leg == "step":
         torch.cuda.profiler.start()      # `ncu --profile-from-start off` captures the timed region only
     t0.record()
     for i in range(args.steps):
-        step(i, dev_x[i % N_INPUT_SETS], dev_dy[i % N_INPUT_SETS], mask_sets[i % N_INPUT_SETS], timed=True)
+        step(i, dev_in[i % N_INPUT_SETS], mask_sets[i % N_INPUT_SETS], dev_out[i % N_INPUT_SETS], timed=True)
     if sync is not None:
         sync.wait_all()                   # the last exchanges are inside the timed region
     t1.record()
@@ -298,7 +327,6 @@ def run_ours(args):
     if args.profile_leg == "step":
         torch.cuda.profiler.stop()
     ms = t0.elapsed_time(t1)
-    clocks = sampler.stop() if sampler else None
     linear.check_status(dev)
     for blk in layers:
         blk._ev_sink = None
@@ -307,23 +335,27 @@ def run_ours(args):
     n_kern = len(ev_pairs)
 
     # ---------------- end to end through the public API with host buffers ("e2e")
-    # x and dy start in pinned host memory every step; y, dx and the LoRA gradients are read back.
+    # Per step: ONE copy in (x | dy, pinned host -> device) and ONE copy out (y | dx | LoRA gradients, device ->
+    # pinned host), on two copy streams, double-buffered around the compute stream.
     copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     main = torch.cuda.current_stream(dev)
     slots = 2
-    in_x = [torch.empty(M, HIDDEN, dtype=torch.float16, device=dev) for _ in range(slots)]
-    in_dy = [torch.empty(M, HIDDEN, dtype=torch.float16, device=dev) for _ in range(slots)]
-    out_y = [torch.empty(M, HIDDEN, dtype=torch.float16).pin_memory() for _ in range(slots)]
-    out_dx = [torch.empty(M, HIDDEN, dtype=torch.float16).pin_memory() for _ in range(slots)]
-    out_g = [torch.empty(per_layer, dtype=torch.float32).pin_memory() for _ in range(slots)]
+    act_elems = 2 * M * HIDDEN
+    in_buf = [torch.empty(2, M, HIDDEN, dtype=torch.float16, device=dev) for _ in range(slots)]
+    # outputs and gradients share one device buffer (fp16 words; the fp32 gradients take two each)
+    out_words = act_elems + 2 * per_layer
+    out_dev = [torch.empty(out_words, dtype=torch.float16, device=dev) for _ in range(slots)]
+    out_act = [o[:act_elems].view(2, M, HIDDEN) for o in out_dev]
+    out_grad = [o[act_elems:].view(torch.float32) for o in out_dev]
+    out_host = [torch.empty(out_words, dtype=torch.float16).pin_memory() for _ in range(slots)]
     ev_in = [torch.cuda.Event() for _ in range(slots)]
     ev_done = [torch.cuda.Event() for _ in range(slots)]
     ev_free = [torch.cuda.Event() for _ in range(slots)]
     ev_out = [torch.cuda.Event() for _ in range(slots)]
-    h2d = 2 * M * HIDDEN * 2
-    d2h = 2 * M * HIDDEN * 2 + per_layer * 4
+    h2d = act_elems * 2
+    d2h = out_words * 2
 
-    def e2e_loop(n):
+    def e2e_loop(n, compute=True):
         for s in range(slots):
             ev_free[s].record(main)
             ev_out[s].record(copy_out)
@@ -331,28 +363,26 @@ def run_ours(args):
             s = i % slots
             with torch.cuda.stream(copy_in):
                 copy_in.wait_event(ev_free[s])              # compute of step i-2 has consumed the slot
-                in_x[s].copy_(host_x[i % N_INPUT_SETS], non_blocking=True)
-                in_dy[s].copy_(host_dy[i % N_INPUT_SETS], non_blocking=True)
+                in_buf[s].copy_(host_in[i % N_INPUT_SETS], non_blocking=True)
                 ev_in[s].record(copy_in)
             main.wait_event(ev_in[s])
             main.wait_event(ev_out[s])                      # results of step i-2 have left the device
-            y, dx = step(i, in_x[s], in_dy[s], mask_sets[i % N_INPUT_SETS])
+            if compute:
+                step(i, in_buf[s], mask_sets[i % N_INPUT_SETS], out_act[s])
+                if sync is not None and sync.done[i % N_WEIGHT_SETS] is not None:
+                    main.wait_event(sync.done[i % N_WEIGHT_SETS])       # the gradients leave the device summed
+                lo = (i % N_WEIGHT_SETS) * per_layer
+                out_grad[s].copy_(bucket.flat[lo:lo + per_layer], non_blocking=True)
             ev_free[s].record(main)
             ev_done[s].record(main)
             with torch.cuda.stream(copy_out):
                 copy_out.wait_event(ev_done[s])
-                if sync is not None and sync.done[i % N_WEIGHT_SETS] is not None:
-                    copy_out.wait_event(sync.done[i % N_WEIGHT_SETS])    # the gradients leave the device summed
-                out_y[s].copy_(y, non_blocking=True)
-                out_dx[s].copy_(dx, non_blocking=True)
-                lo = (i % N_WEIGHT_SETS) * per_layer
-                out_g[s].copy_(bucket.flat[lo:lo + per_layer], non_blocking=True)
+                out_host[s].copy_(out_dev[s], non_blocking=True)
                 ev_out[s].record(copy_out)
-                y.record_stream(copy_out); dx.record_stream(copy_out)
         main.wait_stream(copy_out)
 
-    capture_steps(in_x, in_dy)
-    e2e_loop(max(args.warmup, 1))
+    capture_steps(in_buf, out_act)
+    e2e_loop(max(args.warmup, 3))
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -360,85 +390,159 @@ def run_ours(args):
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
+    linear.check_status(dev)
+    # the host-side ceiling of that loop: the same copies on the same streams with no compute between them
+    e2e_loop(3, compute=False)
+    barrier()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    e2e_loop(args.steps, compute=False)
+    c1.record()
+    barrier()
+    copy_ms = c0.elapsed_time(c1)
+    clocks = sampler.stop() if sampler else None
+
+    # ---------------- configuration 3 on every N (strong scaling), the other configurations at N = 1
+    extra = {}
+    if not args.no_extras:
+        del graphs, layers, dev_in, in_buf, out_dev
+        torch.cuda.empty_cache()
+        extra["config3_stack7b"] = stack_numbers("stack7b", dev, world, rank, args)
+        if world == 1:
+            extra["config0_q_proj"] = config0_numbers(dev)
+            extra["config2_stack1.5b"] = stack_numbers("stack1.5b", dev, world, rank, args)
 
     # ---------------- max over ranks
     if world > 1:
-        t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
+        t = torch.tensor([ms, e2e_ms, copy_ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = t.tolist()
+        ms, e2e_ms, copy_ms = t.tolist()
     if rank == 0:
         pk = peaks()
         value = world * flops * args.steps / (ms * 1e-3) / 1e12
         e2e_val = world * flops * args.steps / (e2e_ms * 1e-3) / 1e12
         achieved = kern_flops / (kern_ms * 1e-3) / 1e12 if kern_ms > 0 else None
-        # the tensor-core kernels run back to back inside a long step: the sustained peak applies
-        peak = pk["tflops_sustained"]
+        # a timed region of under a second runs at boost clocks: the burst figure is the peak to compare with;
+        # a longer one settles under the power cap, where the sustained figure applies
+        burst = ms < 1000.0
+        peak = pk["tflops_burst"] if burst else pk["tflops_sustained"]
         line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-                "config": {"workload": WORKLOAD, "rows_per_gpu": M, "hidden": HIDDEN, "intermediate": INTER,
-                           "lora_rank": 16, "dropout": P_DROP, "parallelism": f"dp{world}",
-                           "tokens_per_s": world * M * args.steps / (ms * 1e-3),
-                           "l2": f"inputs larger than L2: {N_WEIGHT_SETS} weight sets and {N_INPUT_SETS} input sets rotate; "
-                                 "one step touches > 300 MB of activations",
-                           "launch": ("cuda graphs: one captured step per weight set, replayed; every ninth timed step "
-                                      "of the value loop issued eagerly with event hooks") if graphs
-                           else "eager: every launch issued from python"},
+                "config": block_config(world),
+                "tokens_per_s": world * M * args.steps / (ms * 1e-3),
+                "launch": ("cuda graphs: one captured step per weight set, replayed; every ninth timed step "
+                           "of the value loop issued eagerly with event hooks") if not args.no_graphs
+                else "eager: every launch issued from python",
                 "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                              "frac": (achieved / peak) if achieved else None,
-                             # DRAM bytes per tensor-core launch (read + written), mean over the five launches of a
-                             # step, from the ncu capture summarised in profiles/nf4_gemm_kernels_mlp_block_M2048.md
-                             "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "traffic_unit": "bytes per launch (ncu, one step)",
-                             "peak_source": pk["source"] + " sustained bf16",
+                             "peak_source": pk["source"] + (" burst bf16 (timed region under 1 s)" if burst
+                                                            else " sustained bf16 (timed region over 1 s)"),
                              "frac_of_burst": (achieved / pk["tflops_burst"]) if achieved else None,
-                             "kernel": "nf4_gemm_kernel (forward and backward-dX launches)",
+                             "frac_of_sustained": (achieved / pk["tflops_sustained"]) if achieved else None,
+                             "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
+                             "traffic_source": "ncu capture of one step (mean DRAM bytes read + written per tensor-core launch), "
+                                               "not a measurement of this run",
+                             # NF4 bytes of the six weight passes of a step + every activation matrix a launch reads or
+                             # writes (x, g, u, h | h, y | dy, dh | dg, dx | du, dx read + written), over the five launches
+                             "algorithmic_bytes_per_launch": (6 * INTER * HIDDEN * 0.516113
+                                                              + 2 * M * (6 * HIDDEN + 7 * INTER)) / 5,
+                             "kernel": "nf4_gemm_kernel / nf4_gemm_pair_kernel (forward and backward-dX launches)",
                              "launches_timed": n_kern, "avg_launch_us": kern_ms * 1e3 / max(n_kern, 1)},
                 "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                        "ms_per_step": e2e_ms / args.steps},
-                "gpu_launches": 15 * args.steps, "clocks": clocks}
+                        "ms_per_step": e2e_ms / args.steps, "copies_per_step": 2,
+                        "copy_only_ms_per_step": copy_ms / args.steps,
+                        "copy_only_gbs_per_gpu": (h2d + d2h) * args.steps / (copy_ms * 1e-3) / 1e9,
+                        "note": "copy_only = the same two copies per step on the same streams with no compute: the host-side "
+                                "ceiling of this loop at this N"},
+                "gpu_launches": (launches_per_step[0] or 0) * args.steps, "gpu_launches_per_step": launches_per_step[0],
+                "clocks": clocks}
+        line.update(extra)
         if world == 1 and not args.no_stream:
             if args.profile_leg == "stream":
                 torch.cuda.profiler.start()
-            line["weight_stream"] = {"unit": "GB/s of NF4 bytes", "peak_gbs": pk["hbm_gbs"], "peak_source": pk["source"],
-                                     "cases": weight_stream_numbers(dev, pk["hbm_gbs"])}
+            cases = weight_stream_numbers(dev, pk["hbm_gbs"])
             if args.profile_leg == "stream":
                 torch.cuda.profiler.stop()
+            line["weight_stream"] = {"unit": "GB/s of NF4 bytes", "peak_gbs": pk["hbm_gbs"], "peak_source": pk["source"],
+                                     "cases": cases}
+            best = max(cases, key=lambda c: c["gbs"])
+            worst = min(cases, key=lambda c: c["gbs"])
+            line["roofline_weight_stream"] = {
+                "bound": "hbm", "achieved": best["gbs"], "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": best["gbs"] / pk["hbm_gbs"],
+                "case": f"{best['shape']} M={best['M']}", "worst": worst["gbs"], "worst_case": f"{worst['shape']} M={worst['M']}",
+                "worst_frac": worst["gbs"] / pk["hbm_gbs"], "peak_source": pk["source"] + " copy bandwidth",
+                "algorithmic_bytes": "0.516113 B per weight: nibbles + absmax codes + scale2 + offset2",
+                "traffic": None, "traffic_source": "see the ncu summary of the streaming kernel (DRAM bytes read = algorithmic bytes)"}
         if world == 1 and not args.no_cpu:
-            tf, dt, cores = time_cpu(128, 2, 1)
+            tf, dt, cores, done = time_cpu(M_ROWS, 3, 1, budget_s=30.0)
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                                    "sample": "same block with M=128 of 2048 rows, 2 steps after 1 warm-up, "
+                                    "sample": f"the same block at the same M={M_ROWS} rows, {done} steps after 1 warm-up, "
                                               "dequantisation of all three weights included"}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_stack(args):
-    """Secondary workloads (not the default line): the full projection stack of benchmark
-    configuration 2 (`--workload stack1.5b`: 28 layers, 4 packed sequences of 64..512 tokens, one GPU) and
-    configuration 3 (`--workload stack7b`: Qwen2.5-7B shapes, M = 16384 packed rows split by rows over the
-    ranks = strong scaling, LoRA gradients all-reduced once per step). Only projections and the
-    minimal glue of decentrik_prime_b200/stack.py run; FLOPs are the projections' algorithmic FLOPs."""
+def config0_numbers(dev):
+    """Benchmark configuration 0 on the GPU: one q_proj linear 1536 x 1536 at M = 2048 with LoRA and dropout,
+    forward + backward-dX + dA/dB; 48 output tiles on 148 SMs, so the plan splits the contraction. Several
+    weight copies rotate inside one CUDA graph; algorithmic FLOPs 4MNK + 6Mr(N+K)."""
+    import torch
+    from decentrik_prime_b200 import blocks, linear
+    N = K = 1536
+    M = M_ROWS
+    copies = 24
+    ps = [blocks.make_projection(N, K, seed=500 + i, device=dev, lora=True) for i in range(copies)]
+    gen = torch.Generator().manual_seed(9)
+    x = torch.randn(M, K, generator=gen).half().to(dev)
+    dy = torch.randn(M, N, generator=gen).half().to(dev)
+    mask = (torch.rand(M, K, generator=gen) >= P_DROP).to(torch.uint8).to(dev)
+    ks = 1.0 / float(torch.tensor(1.0 - P_DROP, dtype=torch.float32))
+
+    def run():
+        for p_ in ps:
+            p_.forward(x, mask, ks)
+            p_.backward(dy, accumulate_grads=False)
+
+    side = torch.cuda.Stream(dev)
+    with torch.cuda.stream(side):
+        run()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            run()
+        times = []
+        for _ in range(10):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(side); graph.replay(); b.record(side)
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e-3 / copies)
+    linear.check_status(dev)
+    t = statistics.median(times)
+    fl = ps[0].flops(M)
+    return {"workload": "q_proj 1536x1536, M=2048, LoRA r=16 + dropout, fwd + bwd-dX + dA/dB", "us": t * 1e6,
+            "tflops": fl / t / 1e12, "gflop": fl / 1e9, "weight_copies": copies}
+
+
+def stack_numbers(workload, dev, world, rank, args):
+    """Benchmark configurations 2 (`stack1.5b`: 28 layers of Qwen2.5-1.5B shapes, 4 packed sequences of 64..512
+    tokens, one GPU) and 3 (`stack7b`: Qwen2.5-7B shapes, 16384 packed rows split by rows over the ranks =
+    strong scaling; each layer's LoRA gradients all-reduced on a side stream under the remaining backward).
+    All seven projections of every layer run; what lies between them is decentrik_prime_b200/stack.py's glue.
+    Returns tokens/s and the projections' algorithmic TFLOP/s (max over ranks)."""
     import torch
     import torch.distributed as dist
     from decentrik_prime_b200 import dp, linear, stack
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    if args.workload == "stack1.5b":
-        hidden, inter, kv, layers, distinct = 1536, 8960, 256, 28, 28
+    if workload == "stack1.5b":
+        hidden, inter, kv, layers, distinct = 1536, 8960, 256, 28, 8
         lens, M_total = stack.pack_lengths(4, 64, 512, seed=2)
-        note = f"4 sequences of lengths {lens}"
+        note = f"4 sequences of lengths {lens}; 8 distinct weight sets (193 MB of NF4 bytes) reused over 28 layers"
     else:
         hidden, inter, kv, layers, distinct = 3584, 18944, 512, 28, 2
-        lens, M_total = stack.pack_lengths(32, 256, 512, seed=3)
-        M_total = 16384          # the configuration's fixed packed row count
-        note = "32 sequences packed to 16384 rows; 2 distinct weight sets reused over 28 layers"
+        M_total = 16384
+        note = "32 sequences packed to 16384 rows; 2 distinct weight sets (240 MB of NF4 bytes) reused over 28 layers"
     lo, hi = dp.shard_rows(M_total, world, rank)
     M = hi - lo
     st = stack.ProjectionStack(hidden, inter, kv, layers, dev, seed=7, distinct_layers=distinct)
@@ -451,22 +555,29 @@ def run_stack(args):
              for _ in range(n_mask_sets)]
     masks = [masks[i % n_mask_sets] for i in range(layers)]
     keep_scale = 1.0 / float(torch.tensor(1.0 - P_DROP, dtype=torch.float32))
-
+    sync = dp.GradSync(dev, distinct) if world > 1 else None
     graph = [None]
 
     def step():
         if graph[0] is not None:
             graph[0].replay()
         else:
-            st.step(x, dy, masks, keep_scale)
-        if world > 1:
-            dist.all_reduce(st.bucket.flat)
+            st.step(x, dy, masks, keep_scale, sync=sync)
+        if sync is not None:
+            sync.wait_all()
 
-    def capture():
-        """The ~1000 launches of a stack step as one CUDA graph: issued from Python they cost more host time
-        than GPU time at the small configuration. Falls back to eager on failure."""
-        if args.no_graphs:
-            return
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    steps, warmup = min(args.steps, 10), 3
+    for _ in range(warmup):
+        step()
+    barrier()
+    linear.check_status(dev)
+    if world == 1 and not args.no_graphs:
+        # the ~1000 launches of a stack step as one CUDA graph (one GPU: no collective inside)
         side = torch.cuda.Stream(dev)
         try:
             g = torch.cuda.CUDAGraph()
@@ -479,20 +590,8 @@ def run_stack(args):
             graph[0] = None
             torch.cuda.synchronize()
             print(f"[bench] CUDA graph capture failed ({type(exc).__name__}: {exc}); running eagerly", file=sys.stderr)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    steps, warmup = min(args.steps, 20), min(max(args.warmup, 3), 5)
-    for _ in range(warmup):
         step()
-    barrier()
-    linear.check_status(dev)
-    capture()
-    step()
-    barrier()
+        barrier()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
     for _ in range(steps):
@@ -501,24 +600,42 @@ def run_stack(args):
     barrier()
     ms = t0.elapsed_time(t1)
     linear.check_status(dev)
+    flops = float(st.flops(M))
     if world > 1:
         t = torch.tensor([ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = t.item()
-        fl = torch.tensor([float(st.flops(M))], dtype=torch.float64, device=dev)
+        fl = torch.tensor([flops], dtype=torch.float64, device=dev)
         dist.all_reduce(fl)
         flops = fl.item()
-    else:
-        flops = float(st.flops(M))
+    del st, graph
+    torch.cuda.empty_cache()
+    return {"workload": workload, "rows": M_total, "rows_per_gpu": M, "layers": layers, "hidden": hidden, "intermediate": inter,
+            "kv": kv, "lora": "r=16 on q_proj, v_proj", "scaling": "strong" if workload == "stack7b" else "single GPU",
+            "tokens_per_s": M_total * steps / (ms * 1e-3), "tflops": flops * steps / (ms * 1e-3) / 1e12,
+            "ms_per_step": ms / steps, "steps": steps, "warmup": warmup, "note": note,
+            "launch": "cuda graph of the whole step, replayed" if world == 1 and not args.no_graphs else
+                      "eager, per-layer gradient all-reduce on a side stream"}
+
+
+def run_stack(args):
+    """`--workload stack1.5b | stack7b`: the projection-stack configurations as a line of their own."""
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    res = stack_numbers(args.workload, dev, world, rank, args)
     if rank == 0:
-        line = {"metric": "nf4_lora_projection_stack_tokens_per_s", "value": M_total * steps / (ms * 1e-3), "unit": "tokens/s",
-                "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True,
-                "scaling": "strong" if args.workload == "stack7b" else "weak", "vs_baseline": None, "dtype": "f16",
-                "data": "synthetic",
-                "config": {"workload": args.workload, "rows": M_total, "rows_per_gpu": M, "layers": layers, "hidden": hidden,
-                           "intermediate": inter, "kv": kv, "lora": "r=16 on q_proj, v_proj", "note": note,
-                           "tflops": flops * steps / (ms * 1e-3) / 1e12, "parallelism": f"dp{world}",
-                           "launch": "cuda graph of the whole step, replayed" if graph[0] is not None else "eager"}}
+        line = {"metric": "nf4_lora_projection_stack_tokens_per_s", "value": res["tokens_per_s"], "unit": "tokens/s",
+                "n_gpus": world, "steps": res["steps"], "warmup": res["warmup"], "ms_per_step": res["ms_per_step"],
+                "higher_is_better": True, "scaling": "strong" if args.workload == "stack7b" else "weak", "vs_baseline": None,
+                "dtype": "f16", "data": "synthetic", "config": res}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -631,6 +748,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-stream", action="store_true", help="skip the small-batch weight-stream numbers")
+    ap.add_argument("--no-extras", action="store_true", help="skip benchmark configurations 0, 2 and 3")
     ap.add_argument("--no-graphs", action="store_true", help="issue every step from Python instead of replaying CUDA graphs")
     ap.add_argument("--profile-leg", default="step", choices=("step", "stream"),
                     help="which leg cudaProfilerStart/Stop brackets (for `ncu --profile-from-start off`): the timed "

@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB_PATH = os.path.join(HERE, "libnf4ll.so")
-SOURCES = ("nf4ll_api.cu", "nf4ll_dequant.cu", "nf4ll_gemm.cu", "nf4ll_gemm2.cu", "nf4ll_lora.cu", "nf4ll_swiglu.cu", "nf4ll_stream.cu")
+SOURCES = ("nf4ll_api.cu", "nf4ll_dequant.cu", "nf4ll_gemm.cu", "nf4ll_gemm2.cu", "nf4ll_lora.cu", "nf4ll_swiglu.cu", "nf4ll_stream.cu", "nf4ll_swap.cu")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "--fmad=true", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "-shared"]
@@ -37,25 +37,49 @@ def needs_build():
     if not os.path.exists(LIB_PATH):
         return True
     built = os.path.getmtime(LIB_PATH)
-    deps = sources() + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
-    deps += [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE) if f.endswith(".h")]
+    deps = sources() + _headers()
     return any(os.path.getmtime(d) > built for d in deps)
 
 
+def _headers():
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
+    return deps + [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE) if f.endswith(".h")]
+
+
 def build(force=False, verbose=False):
-    """Compile csrc/*.cu into libnf4ll.so with nvcc for sm_100a (cross-compiles without a GPU)."""
+    """Compile csrc/*.cu into libnf4ll.so with nvcc for sm_100a (cross-compiles without a GPU).
+    Every source becomes an object file under decentrik_prime_b200/build/ (compiled in parallel, only
+    when it or a header is newer than its object), then the objects are linked into the library."""
     if not force and not needs_build():
         return LIB_PATH
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", INCLUDE, "-I", CSRC, "-o", LIB_PATH + ".tmp", *sources()]
-    if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-    res = subprocess.run(cmd, capture_output=True, text=True)
+    from concurrent.futures import ThreadPoolExecutor
+    objdir = os.path.join(HERE, "build")
+    os.makedirs(objdir, exist_ok=True)
+    newest_header = max(os.path.getmtime(h) for h in _headers())
+    flags = [f for f in NVCC_FLAGS if f != "-shared"]
+
+    def compile_one(src):
+        obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
+        if not force and os.path.exists(obj) and os.path.getmtime(obj) > max(os.path.getmtime(src), newest_header):
+            return obj, ""
+        cmd = [_nvcc(), *flags, "-I", INCLUDE, "-I", CSRC, "-c", "-o", obj, src]
+        if verbose:
+            cmd[1:1] = ["-Xptxas", "-v"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
+        return obj, res.stdout + res.stderr
+
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
+        results = list(pool.map(compile_one, sources()))
+    link = [_nvcc(), "-shared", "-Xcompiler", "-fPIC", "-gencode", "arch=compute_100a,code=sm_100a",
+            "-o", LIB_PATH + ".tmp", *[obj for obj, _ in results]]
+    res = subprocess.run(link, capture_output=True, text=True)
     if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
+        raise RuntimeError("link failed:\n" + " ".join(link) + "\n" + res.stdout + res.stderr)
     os.replace(LIB_PATH + ".tmp", LIB_PATH)
     if verbose:
-        print(res.stdout + res.stderr)
+        print("".join(log for _, log in results))
     return LIB_PATH
 
 
@@ -98,7 +122,10 @@ SIGNATURES = {
     "nf4ll_lora_down": (_i32, [_vp, _i64, _vp, _i64, _f32, _vp, _f32, _i32, _i64, _i64, _vp, _vp, _vp]),
     "nf4ll_lora_grads": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _f32, _vp, _vp, _f32, _i32, _i64, _i64, _i64,
                                 _vp, _vp, _i32, _vp]),
-    "nf4ll_tune_override": (None, [_i32, _i32, _i32]),
+    "nf4ll_workspace_bytes_tuned": (_i64, [_i64, _i64, _i64, _i32, _i32, _i32, _i32]),
+    "nf4ll_tune_override": (None, [_i32, _i32, _i32, _i32]),
+    "nf4ll_test_expire_wait": (None, [ctypes.c_uint32]),
+    "nf4ll_launch_count": (_i64, []),
     "nf4ll_kernel_events": (None, [_vp, _vp]),
     "nf4ll_swiglu_forward": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "nf4ll_swiglu_backward": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _vp]),

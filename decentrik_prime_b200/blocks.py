@@ -159,23 +159,25 @@ class MlpBlock:
     def flops(self, M):
         return sum(p.flops(M) for p in self.projections)
 
-    def forward(self, x, masks=(None, None, None), keep_scale=1.0):
+    def forward(self, x, masks=(None, None, None), keep_scale=1.0, out=None):
+        """y = down(silu(gate(x)) * up(x)); `out` (optional) receives y."""
         if self.fused_glue:
             g, u, h, tg, tu = linear.forward_gate_up(self.w_gu, x, self.gate.lora, masks[0] if self.gate.has_lora else None,
                                                      self.up.lora, masks[1] if self.up.has_lora else None, keep_scale)
             self.gate._saved = (x, masks[0] if self.gate.has_lora else None, keep_scale, tg)
             self.up._saved = (x, masks[1] if self.up.has_lora else None, keep_scale, tu)
-            y = self.down.forward(h, masks[2], keep_scale)
+            y = self.down.forward(h, masks[2], keep_scale, out=out)
             self._saved = (g, u)
             return y
         g = self.gate.forward(x, masks[0], keep_scale)
         u = self.up.forward(x, masks[1], keep_scale)
         h = F.silu(g.float()).mul_(u.float()).half()
-        y = self.down.forward(h, masks[2], keep_scale)
+        y = self.down.forward(h, masks[2], keep_scale, out=out)
         self._saved = (g, u)
         return y
 
-    def backward(self, dy, need_dx=True, accumulate_grads=False):
+    def backward(self, dy, need_dx=True, accumulate_grads=False, out=None):
+        """d(input) of the block (into `out` when given) and the LoRA gradients of its three projections."""
         g, u = self._saved
         if self._grad_slice is not None and not accumulate_grads:
             self._grad_slice.zero_()
@@ -189,9 +191,10 @@ class MlpBlock:
             dhf = dh.float()
             du = (dhf * gf * sig).half()
             dg = (dhf * u.float() * sig * (1.0 + gf * (1.0 - sig))).half()
-        dx = self.gate.backward(dg, need_dx=need_dx, accumulate_grads=accumulate_grads)
-        # d(input) of gate and up are summed into one buffer (the reference adds them in fp16,
-        # solution/fast_qwen.py:1320-1323; here the add happens on the fp32 accumulator)
+        dx = self.gate.backward(dg, out=out, need_dx=need_dx, accumulate_grads=accumulate_grads)
+        # d(input) of gate and up are summed into one buffer: the second launch adds its fp32 result to the
+        # fp16 values the first one stored and rounds again (two roundings, like the reference's fp16 add,
+        # solution/fast_qwen.py:1320-1323)
         dx = self.up.backward(du, out=dx, accumulate=need_dx, need_dx=need_dx, accumulate_grads=accumulate_grads)
         self._saved = None
         return dx

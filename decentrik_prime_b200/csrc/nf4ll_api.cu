@@ -7,6 +7,9 @@
 namespace nf4ll {
 
 static thread_local char g_detail[512] = "";
+static thread_local int64_t g_launches = 0;
+
+void count_launch() { ++g_launches; }
 
 void set_detail(const char* fmt, ...) {
   va_list ap;
@@ -51,6 +54,8 @@ extern "C" const char* nf4ll_error_string(int code) {
 }
 
 extern "C" const char* nf4ll_last_error_detail(void) { return nf4ll::g_detail; }
+
+extern "C" int64_t nf4ll_launch_count(void) { return nf4ll::g_launches; }
 
 extern "C" int nf4ll_read_status(const int32_t* status, void* stream) {
   using namespace nf4ll;

@@ -13,11 +13,13 @@ namespace nf4ll {
 // Launch configuration with the attributes this library uses: programmatic dependent launch (only
 // for kernels that call pdl_wait() first thing), an optional thread-block cluster, an optional
 // cooperative launch (whole grid resident at once; not combined with the programmatic attribute).
+void count_launch();   // definition in nf4ll_api.cu: one more kernel launched by the calling thread
+
 struct PdlLaunch {
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[3];
   PdlLaunch(dim3 grid, dim3 block, size_t smem, cudaStream_t stream, unsigned cluster_x = 0, unsigned cluster_y = 0,
-            bool cooperative = false) {
+            bool cooperative = false, bool counted = true) {
     cfg = cudaLaunchConfig_t{};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
     int n = 0;
@@ -38,6 +40,7 @@ struct PdlLaunch {
       ++n;
     }
     cfg.attrs = attr; cfg.numAttrs = n;
+    if (counted) count_launch();       // a configuration built only to query occupancy is not a launch
   }
 };
 

@@ -60,6 +60,7 @@ extern "C" int nf4ll_dequant(const uint8_t* nib, const uint8_t* qabs, const floa
   int64_t blocks = (n_half + kDequantThreads - 1) / kDequantThreads;
   const int64_t cap = static_cast<int64_t>(sms) * 8;   // whole waves of 8 resident CTAs per SM
   if (blocks > cap) blocks = cap;
+  count_launch();
   dequant_kernel<<<static_cast<unsigned>(blocks), kDequantThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const uint4*>(nib), qabs, scale2, offset2, code2, n_half, reinterpret_cast<uint4*>(out_f16));
   NF4LL_CUDA(cudaGetLastError());

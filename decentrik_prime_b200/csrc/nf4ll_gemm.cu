@@ -26,8 +26,6 @@
 // one W row (= one quantisation block, 128 bytes), 8 rows per 1024-byte swizzle atom. Forward reads
 // it as a K-major B operand (contraction along the row), backward as an MN-major one (contraction
 // across rows), so the same NF4 bytes serve W and W^T.
-#include <cstdlib>
-
 #include "nf4ll_gemm_shared.cuh"
 
 namespace nf4ll {
@@ -189,27 +187,32 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
                       static_cast<int>(m0 + mt * 128), smem_u32(full_a + s));
         }
       }
-      if (p.splits > 1 && !*abort_flag && !(p.debug & 4)) {
+      if (p.splits > 1 && !*abort_flag) {
         // split-K: if this CTA turns out to be the last of its tile, stream all slabs back in
         if (wait_or_abort(smem_u32(fix_go), 0, ab, 0x0104) && p.coop && !*abort_flag) {
           // shared reduction: this CTA owns every splits-th box of the tile and streams the other
           // splits' partial sums of exactly those boxes back in
           fence_proxy_async_all();
           constexpr int NB = BM_TILES * (BN / 32);
-          int n = 0;
+          // the boxes go to the warp groups in turn and every group has its own share of the ring's slots:
+          // a slot is then always filled for, and drained by, the same group, in order
+          constexpr int G = NDW / 4, SPG = kFixSlots / G;
+          int cnt0 = 0, cnt1 = 0, mine = 0;
           bool fine = true;
           for (int b = split; fine && b < NB; b += p.splits) {
             const int mt = b / (BN / 32), cb = b % (BN / 32);
             const int64_t col0 = o0 + cb * 32;
             if (col0 >= p.NO) continue;
+            const int grp = (mine++) % G;
             for (int sp = 0; sp < p.splits; ++sp) {
               if (sp == split) continue;
-              const int slot = n % kFixSlots;
-              if (!wait_or_abort(smem_u32(fx_empty + slot), ((n / kFixSlots) & 1) ^ 1, ab, 0x0105)) { fine = false; break; }
+              const int nn = grp ? cnt1 : cnt0;
+              const int slot = grp * SPG + nn % SPG;
+              if (!wait_or_abort(smem_u32(fx_empty + slot), ((nn / SPG) & 1) ^ 1, ab, 0x0105)) { fine = false; break; }
+              if (grp) ++cnt1; else ++cnt0;
               mbar_arrive_expect_tx(smem_u32(fx_full + slot), 16384);
               tma_load_2d(smem_u32(smem) + slot * 16384, &tmap_out, static_cast<int>(col0),
                           static_cast<int>(static_cast<int64_t>(sp) * p.m_pad + m0 + mt * 128), smem_u32(fx_full + slot));
-              ++n;
             }
           }
         } else if (!p.coop && *last_flag) {
@@ -298,7 +301,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
 #pragma unroll
           for (int mt = 0; mt < BM_TILES; ++mt) {
             const uint64_t adesc = make_smem_desc(a_base + mt * 16384 + kk * 32, 16, 1024, kSwizzle128B);
-            if (!(p.debug & 2)) tc_mma_f16(tmem_base + mt * BN, adesc, bdesc, idesc_main, (lora_here || i > 0 || kk > 0) ? 1u : 0u);
+            tc_mma_f16(tmem_base + mt * BN, adesc, bdesc, idesc_main, (lora_here || i > 0 || kk > 0) ? 1u : 0u);
           }
         }
         tc_commit(smem_u32(empty + s));     // frees the stage once these MMAs have read it
@@ -516,11 +519,9 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
       if (!wait_or_abort(smem_u32(empty + s), ph ^ 1, ab, 0x0302)) return false;
       // the last stage holds the LoRA operands until the rank-16 MMAs have read them
       if (lora_here && i == S - 1 && !wait_or_abort(smem_u32(lora_done), 0, ab, 0x0305)) return false;
-      if (!(p.debug & 1)) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
-          dequant_block_to_smem(b_base + s * Cfg::kBBytes + row_off[h], key[h], c[h][0], c[h][1], absmax[h]);
-      }
+      for (int h = 0; h < 2; ++h)
+        dequant_block_to_smem(b_base + s * Cfg::kBBytes + row_off[h], key[h], c[h][0], c[h][1], absmax[h]);
       fence_proxy_async_smem();      // generic-proxy stores -> visible to the tensor core's async proxy
       __syncwarp();
       if (lane == 0) {
@@ -590,7 +591,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
     // 128-row accumulator at a time in boxes of 128 rows x 128 bytes.
     if (ok) ok = wait_or_abort(smem_u32(acc_full), 0, ab, 0x0303);
     const bool direct = (p.splits == 1);
-    if (ok && !(p.debug & 4)) {
+    if (ok) {
       tc_fence_after();
       constexpr int G = NDW / 4;                       // warp groups
       const int grp = ew >> 2;
@@ -782,7 +783,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
         __threadfence();
       }
     }
-    if (!direct && p.coop && !(p.debug & 4)) {
+    if (!direct && p.coop) {
       // shared reduction, second half: once every split of this tile has published its slab, each
       // split finishes the boxes it owns: its own partial sums straight from tensor memory plus the
       // other splits' in ascending order (a fixed order: results do not depend on timing).
@@ -793,7 +794,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
         __threadfence();
         atomicAdd(counter, 1);
         bool seen = false;
-        for (uint32_t i = 0; i < kCoopSpinLimit; ++i) {
+        for (uint32_t i = 0; i < p.spin_limit; ++i) {
           if (ld_acquire_gpu(counter) >= p.splits) { seen = true; break; }
           if ((i & 255u) == 255u && *abort_flag) break;
           __nanosleep(32);
@@ -809,15 +810,14 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
         const int grp = ew >> 2;
         const int r_in = q * 32 + lane;
         const uint32_t ring = smem_u32(smem);
-        int n = 0, mine = 0;
+        constexpr int SPG = kFixSlots / G;       // this group's share of the ring's slots
+        int own = 0, mine = 0;
         bool fine = true;
 #pragma unroll 1
         for (int b = split; fine && b < NB; b += p.splits) {
           const int mt = b / (BN / 32), cb = b % (BN / 32);
           const int64_t col0 = o0 + cb * 32;
           if (col0 >= p.NO) continue;
-          const int n0 = n;
-          n += p.splits - 1;
           if ((mine++) % G != grp) continue;
           uint32_t v[32];
           __syncwarp();
@@ -836,8 +836,8 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
             }
           }
           for (int k = 0; k < p.splits - 1; ++k) {
-            const int nn = n0 + k, slot = nn % kFixSlots;
-            if (!wait_or_abort(smem_u32(fx_full + slot), (nn / kFixSlots) & 1, ab, 0x0305)) { fine = false; break; }
+            const int nn = own++, slot = grp * SPG + nn % SPG;
+            if (!wait_or_abort(smem_u32(fx_full + slot), (nn / SPG) & 1, ab, 0x0305)) { fine = false; break; }
             const uint32_t src = ring + slot * 16384 + r_in * 128;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -868,7 +868,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_const
           }
         }
       }
-    } else if (!direct && !(p.debug & 4)) {
+    } else if (!direct) {
       // split-K fix-up: the last CTA of this output tile to finish sums all slabs in split order
       // (deterministic) and writes the fp16 result. Every dequant thread takes both barriers, also
       // after a failed wait, so that nobody is left behind at a barrier.
@@ -1023,18 +1023,25 @@ static int make_nib_map(CUtensorMap* map, const void* nib, int64_t N, int64_t K,
 struct Plan {
   int pair;                // 1: CTA-pair kernel (tcgen05 cta_group::2), tile (bm_tiles x 256) x 256 per pair
   int bm_tiles, bn, splits;
+  int launch_splits;       // grid depth actually launched: `splits`, except under nf4ll_test_expire_wait
   int64_t tiles_m, tiles_o, m_pad;
   int64_t left_bytes, bt_bytes, counter_bytes, partial_bytes;
   int64_t total() const { return left_bytes + bt_bytes + counter_bytes + partial_bytes; }
 };
 
-static thread_local int g_force_bm = 0, g_force_bn = 0, g_force_splits = 0;
-static thread_local int g_debug = 0;
+// Tile shape / split count forced by a test (zeros: the built-in heuristic). flags bit 0: never use the
+// cooperative (shared) split reduction.
+struct Tune {
+  int bm = 0, bn = 0, splits = 0, flags = 0;
+  bool any() const { return bm || bn || splits; }
+};
+static thread_local Tune g_tune;
+static thread_local uint32_t g_expire_polls = 0;      // nf4ll_test_expire_wait: one-shot
 static thread_local cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;
 
 static int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
 
-static Plan make_plan(int mode, int64_t M, int64_t NO, int64_t KC, int r, int sms) {
+static Plan make_plan(int mode, int64_t M, int64_t NO, int64_t KC, int r, int sms, const Tune& tune) {
   Plan pl;
   // CTA pairs whenever the output is wide enough for a 256-column tile and tall enough to fill the
   // pair's 256 accumulator rows; the single-CTA kernel serves narrow or short problems.
@@ -1045,9 +1052,9 @@ static Plan make_plan(int mode, int64_t M, int64_t NO, int64_t KC, int r, int sm
   if (NO <= 128) pl.bn = 128;
   pl.bm_tiles = (M > 128) ? 2 : 1;
   if (pl.pair) { pl.bn = 256; pl.bm_tiles = (M > 256) ? 2 : 1; }
-  if (g_force_bn == 512) { pl.pair = 1; pl.bn = 256; }          // testing hook: 512 asks for the pair kernel
-  else if (g_force_bn) { pl.pair = 0; pl.bn = g_force_bn; if (!g_force_bm) pl.bm_tiles = (M > 128) ? 2 : 1; }
-  if (g_force_bm) pl.bm_tiles = g_force_bm;
+  if (tune.bn == 512) { pl.pair = 1; pl.bn = 256; }          // testing hook: 512 asks for the pair kernel
+  else if (tune.bn) { pl.pair = 0; pl.bn = tune.bn; if (!tune.bm) pl.bm_tiles = (M > 128) ? 2 : 1; }
+  if (tune.bm) pl.bm_tiles = tune.bm;
   const int64_t bm = pl.bm_tiles * (pl.pair ? 256 : 128);       // rows per tile (per pair or per CTA)
   pl.tiles_m = (M + bm - 1) / bm;
   pl.tiles_o = (NO + pl.bn - 1) / pl.bn;
@@ -1062,9 +1069,10 @@ static Plan make_plan(int mode, int64_t M, int64_t NO, int64_t KC, int r, int sm
     if (splits > 16) splits = 16;
     if (splits < 1) splits = 1;
   }
-  if (g_force_splits) splits = g_force_splits;
+  if (tune.splits) splits = tune.splits;
   if (splits > nkb) splits = static_cast<int>(nkb > 0 ? nkb : 1);
   pl.splits = splits;
+  pl.launch_splits = splits;
   pl.left_bytes = r > 0 ? align256(M * r * 4) : 0;      // fp32 rank-16 projection when the caller does not keep it
   pl.bt_bytes = r > 0 ? align256(KC * r * 2) : 0;      // room for lora_B transposed (backward only uses it)
   pl.counter_bytes = splits > 1 ? align256(ctas * 4) : 0;      // one per CTA-owned block of output rows
@@ -1080,17 +1088,42 @@ static int device_sms(int* sms) {
   return NF4LL_OK;
 }
 
+// Whether a cooperative grid of `ctas` CTAs can be resident at once, given how many CTAs of the kernel fit
+// one SM and how many SMs the device offers.
+bool coop_grid_fits(int64_t ctas, int ctas_per_sm, int sms) {
+  return ctas_per_sm > 0 && sms > 0 && ctas <= static_cast<int64_t>(ctas_per_sm) * sms;
+}
+
 template <int MODE, int BM_TILES, int BN>
 static int launch_cfg(const CUtensorMap& map, const CUtensorMap& nib_map, const CUtensorMap& out_map, const CUtensorMap& out_u,
-                      const CUtensorMap& out_h, const GemmParams& p, const Plan& pl, cudaStream_t stream) {
+                      const CUtensorMap& out_h, const GemmParams& p_in, const Plan& pl, cudaStream_t stream) {
   using Cfg = TileCfg<BM_TILES, BN>;
   auto kernel = nf4_gemm_kernel<MODE, BM_TILES, BN>;
   NF4LL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-  dim3 grid(static_cast<unsigned>(pl.tiles_o), static_cast<unsigned>(pl.tiles_m), static_cast<unsigned>(pl.splits));
-  // split-K with a shared reduction: the splits of a tile wait for one another, which is only legal
-  // when the whole grid is resident at once (cooperative launch)
-  PdlLaunch lc(grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, 0, 0, p.coop != 0);
-  NF4LL_CUDA(cudaLaunchKernelEx(&lc.cfg, kernel, map, nib_map, out_map, out_u, out_h, p));
+  dim3 grid(static_cast<unsigned>(pl.tiles_o), static_cast<unsigned>(pl.tiles_m), static_cast<unsigned>(pl.launch_splits));
+  GemmParams p = p_in;
+  if (p.coop) {
+    // split-K with a shared reduction: the splits of a tile wait for one another, which is only legal when
+    // the whole grid is resident at once (cooperative launch). Ask the runtime how many CTAs of this kernel
+    // an SM holds (fewer SMs or less shared memory may be usable than a bare B200 offers).
+    int per_sm = 0, dev = 0, sms = 0;
+    NF4LL_CUDA(cudaGetDevice(&dev));
+    NF4LL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    NF4LL_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, Cfg::kThreads, Cfg::kSmemBytes));
+    if (!coop_grid_fits(static_cast<int64_t>(grid.x) * grid.y * pl.splits, per_sm, sms)) p.coop = 0;
+  }
+  for (;;) {
+    PdlLaunch lc(grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, 0, 0, p.coop != 0);
+    const cudaError_t err = cudaLaunchKernelEx(&lc.cfg, kernel, map, nib_map, out_map, out_u, out_h, p);
+    if (err == cudaErrorCooperativeLaunchTooLarge && p.coop) {
+      // the runtime disagrees after all: the last-CTA reduction needs no co-residency (counters are already zero)
+      (void)cudaGetLastError();
+      p.coop = 0;
+      continue;
+    }
+    NF4LL_CUDA(err);
+    break;
+  }
   NF4LL_CUDA(cudaGetLastError());
   return NF4LL_OK;
 }
@@ -1153,10 +1186,35 @@ int lora_down_launch(const void* act, int64_t ldact, const uint8_t* mask, int64_
                      cudaStream_t stream);
 int transpose_n16_launch(const void* B, void* Bt, int64_t N, cudaStream_t stream);
 int launch_pair(int mode, int bm_tiles, const CUtensorMap& map, const CUtensorMap& nib_map, const CUtensorMap& out_map,
-                const GemmParams& p, int64_t tiles_o, int64_t tiles_mp, int splits, cudaStream_t stream);
+                const GemmParams& p, int64_t tiles_o, int64_t tiles_mp, int splits, int launch_splits, cudaStream_t stream);
 int stream_forward_launch(const nf4ll_mat* W, const void* x, int64_t ldx, const void* bias, const float* t32,
-                          const void* lora_b, float lora_scale, int64_t M, void* y, int64_t ldy, cudaStream_t stream);
+                          const void* lora_b, float lora_scale, int64_t M, void* y, int64_t ldy, void* scratch,
+                          bool counters_zeroed, int force_slices, cudaStream_t stream);
+int64_t stream_workspace_bytes(int64_t N, int64_t K, int64_t M, int sms, int force_slices);
+int swap_forward_launch(const nf4ll_mat* W, const void* x, int64_t ldx, const void* bias, const float* t32,
+                        const void* lora_b, float lora_scale, int64_t M, void* y, int64_t ldy, void* scratch,
+                        bool counters_zeroed, int force_slices, int32_t* status, cudaStream_t stream);
+int64_t swap_workspace_bytes(int64_t N, int64_t K, int64_t M, int sms, int force_slices);
 constexpr int64_t kStreamMaxRows = 16;     // at or below this many token rows the forward is a weight-streaming pass
+constexpr int64_t kStreamCapRows = 64;     // the streaming kernel's own limit (reachable through the tuning hook)
+constexpr int64_t kSwapMaxRows = 128;      // limit of the swapped-operand kernel (weights as the MMA's M operand)
+
+// Which kernel computes a forward of M rows: the 256 x 256 / 128-row tile kernels (kTiles), the register-level
+// weight-streaming kernel for decode-sized batches (kStream), or the swapped-operand tensor-core kernel for
+// short batches (kSwap). Bits 1 and 2 of the tuning flags force kStream / kSwap up to that kernel's limit.
+enum : int { kTiles = 0, kStream = 1, kSwap = 2 };
+static int forward_kind(int mode, int64_t M, bool stacked, const Tune& tune) {
+  if (mode != kFwd || stacked) return kTiles;
+  if (tune.flags & 2) return M <= kStreamCapRows ? kStream : kTiles;
+  if (tune.flags & 4) return M <= kSwapMaxRows ? kSwap : kTiles;
+  if (tune.any()) return kTiles;
+  if (M <= kStreamMaxRows) return kStream;
+  return kTiles;
+}
+
+static int64_t small_batch_scratch(int kind, int64_t N, int64_t K, int64_t M, int sms, int force_slices) {
+  return kind == kStream ? stream_workspace_bytes(N, K, M, sms, force_slices) : swap_workspace_bytes(N, K, M, sms, force_slices);
+}
 
 // `segments` (forward only): the weight is several projections stacked along N, each with its own
 // optional LoRA branch; `lora` / `side_out` are then unused.
@@ -1194,14 +1252,17 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
     }
     if (at != W->N) { set_detail("%s: segments cover %lld of %lld rows", who, static_cast<long long>(at), static_cast<long long>(W->N)); return NF4LL_ERR_SHAPE; }
   }
-  const int saved_bn = g_force_bn;
-  if (segments && (narrow_tiles || g_force_bn == 512)) g_force_bn = narrow_tiles ? 128 : 256;
-  const Plan pl = make_plan(mode, M, NO, KC, lora ? lora->r : 0, sms);
-  g_force_bn = saved_bn;
-  if (pl.total() > 0) {
-    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || workspace_bytes < pl.total()) {
+  Tune tune = g_tune;
+  if (segments && (narrow_tiles || tune.bn == 512)) tune.bn = narrow_tiles ? 128 : 256;
+  Plan pl = make_plan(mode, M, NO, KC, lora ? lora->r : 0, sms, tune);
+  const int kind = forward_kind(mode, M, segments != nullptr, tune);
+  const int force_slices = (tune.flags & 6) ? tune.splits : 0;
+  const int64_t need = kind != kTiles ? pl.left_bytes + pl.bt_bytes + small_batch_scratch(kind, W->N, W->K, M, sms, force_slices)
+                                      : pl.total();
+  if (need > 0) {
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || workspace_bytes < need) {
       set_detail("%s: needs a 256-byte aligned workspace of %lld bytes (got %lld)", who,
-                 static_cast<long long>(pl.total()), static_cast<long long>(workspace_bytes));
+                 static_cast<long long>(need), static_cast<long long>(workspace_bytes));
       return NF4LL_ERR_WORKSPACE;
     }
   }
@@ -1213,18 +1274,30 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
   p.bias = static_cast<const __half*>(bias);
   p.accumulate = accumulate;
   p.has_lora = lora != nullptr;
-  p.splits = pl.splits; p.m_pad = pl.m_pad; p.status = status; p.debug = g_debug;
-  // one CTA per SM (shared memory): a split-K grid of at most `sms` CTAs is resident as a whole
+  p.splits = pl.splits; p.m_pad = pl.m_pad; p.status = status; p.spin_limit = kCoopSpinLimit;
+  // one CTA per SM (shared memory): a split-K grid of at most `sms` CTAs is resident as a whole; the launch
+  // itself re-checks this against the runtime's occupancy figure for the kernel it picks
   {
     const int64_t ctas = pl.tiles_o * pl.tiles_m * pl.splits * (pl.pair ? 2 : 1);
-    // NF4LL_NO_COOP=1 keeps the last-CTA reduction everywhere: a profiler that replays kernels one by one
-    // cannot launch the cooperative cluster variant
-    static const bool no_coop = [] { const char* e = std::getenv("NF4LL_NO_COOP"); return e && e[0] == '1'; }();
-    p.coop = (pl.splits > 1 && ctas <= sms && !(g_debug & 8) && !no_coop) ? 1 : 0;
+    p.coop = (pl.splits > 1 && coop_grid_fits(ctas, 1, sms) && !(tune.flags & 1)) ? 1 : 0;
+  }
+  const uint32_t expire = g_expire_polls;
+  if (expire && p.coop && pl.splits > 1) {
+    // test hook: launch one split short, so that every tile's counter stays below `splits` and each CTA's
+    // bounded wait on it runs out after `expire` polls
+    g_expire_polls = 0;
+    pl.launch_splits = pl.splits - 1;
+    p.spin_limit = expire;
   }
   int* counters = nullptr;
   int counter_words = 0;
-  if (pl.splits > 1) {
+  if (kind == kStream) {
+    counters = reinterpret_cast<int*>(ws + pl.left_bytes + pl.bt_bytes);      // next-unit counter + one per 16 weight rows
+    counter_words = static_cast<int>(1 + W->N / 16);
+  } else if (kind == kSwap) {
+    counters = reinterpret_cast<int*>(ws + pl.left_bytes + pl.bt_bytes);      // one per tile of 128 weight rows
+    counter_words = static_cast<int>((W->N + 127) / 128);
+  } else if (pl.splits > 1) {
     counters = reinterpret_cast<int*>(ws + pl.left_bytes + pl.bt_bytes);
     counter_words = static_cast<int>(pl.counter_bytes / sizeof(int));
   }
@@ -1268,10 +1341,22 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
       p.mask = lora->mask; p.ld_mask = lora->ld_mask; p.keep_scale = lora->keep_scale;
     }
     p.lora_left = left;
-    if (mode == kFwd && M <= kStreamMaxRows && !g_force_bm && !g_force_bn && !g_force_splits)
-      return stream_forward_launch(W, act, ldact, bias, p.lora_left, lora->B, lora->scale, M, out, ldo, stream);
-  } else if (!segments && mode == kFwd && M <= kStreamMaxRows && !g_force_bm && !g_force_bn && !g_force_splits) {
-    return stream_forward_launch(W, act, ldact, bias, nullptr, nullptr, 0.f, M, out, ldo, stream);
+  }
+  // the measurement hook is one-shot: whichever kernel computes this call's product consumes it
+  cudaEvent_t ev0 = g_ev_start, ev1 = g_ev_stop;
+  g_ev_start = g_ev_stop = nullptr;
+  if (kind != kTiles) {
+    if (ev0) NF4LL_CUDA(cudaEventRecord(ev0, stream));
+    const float* t32 = lora ? p.lora_left : nullptr;
+    const void* lb = lora ? lora->B : nullptr;
+    const float ls = lora ? lora->scale : 0.f;
+    const int rc = kind == kStream
+                       ? stream_forward_launch(W, act, ldact, bias, t32, lb, ls, M, out, ldo, counters, lora != nullptr,
+                                               force_slices, stream)
+                       : swap_forward_launch(W, act, ldact, bias, t32, lb, ls, M, out, ldo, counters, lora != nullptr,
+                                             force_slices, status, stream);
+    if (rc == NF4LL_OK && ev1) NF4LL_CUDA(cudaEventRecord(ev1, stream));
+    return rc;
   }
   if (pl.splits > 1) {
     p.counters = counters;
@@ -1288,10 +1373,9 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
   }
   CUtensorMap nib_map;
   if (int rc = make_nib_map(&nib_map, W->nib, W->N, W->K, mode, pl.pair ? 128 : pl.bn)) return rc;
-  cudaEvent_t ev0 = g_ev_start, ev1 = g_ev_stop;
-  g_ev_start = g_ev_stop = nullptr;
   if (ev0) NF4LL_CUDA(cudaEventRecord(ev0, stream));
-  const int rc = pl.pair ? launch_pair(mode, pl.bm_tiles, map, nib_map, out_map, p, pl.tiles_o, pl.tiles_m, pl.splits, stream)
+  const int rc = pl.pair ? launch_pair(mode, pl.bm_tiles, map, nib_map, out_map, p, pl.tiles_o, pl.tiles_m, pl.splits,
+                                       pl.launch_splits, stream)
                  : (mode == kFwd ? launch<kFwd>(map, nib_map, out_map, p, pl, stream)
                                  : launch<kBwd>(map, nib_map, out_map, p, pl, stream));
   if (rc == NF4LL_OK && ev1) NF4LL_CUDA(cudaEventRecord(ev1, stream));
@@ -1329,7 +1413,7 @@ static int run_gate_up(const nf4ll_mat* W, const void* x, int64_t ldx, const nf4
   if (int rc = check_lora(lora_up, who, W->K)) return rc;
   if ((lora_gate && !t_gate) || (lora_up && !t_up)) { set_detail("%s: a LoRA branch needs its t_out", who); return NF4LL_ERR_NULL; }
   if (int rc = require_sm100()) return rc;
-  if (M <= 128 || I % 128 || g_force_bm || g_force_bn || g_force_splits) {
+  if (M <= 128 || I % 128 || g_tune.any()) {
     // short batches and odd widths: the two projections on their own, then the stand-alone gated product
     const nf4ll_mat wg = sub_rows(W, 0, I), wu = sub_rows(W, I, I);
     if (int rc = run_gemm(kFwd, &wg, x, ldx, nullptr, lora_gate, t_gate, M, g, ldg, 0, workspace, workspace_bytes, status, stream_v)) return rc;
@@ -1340,7 +1424,7 @@ static int run_gate_up(const nf4ll_mat* W, const void* x, int64_t ldx, const nf4
   p.nib = W->nib; p.qabs = W->qabs; p.scale2 = W->scale2; p.offset2 = W->offset2; p.code2 = W->code2;
   p.N = W->N; p.K = W->K; p.M = M; p.NO = W->N; p.KC = W->K;
   p.out = static_cast<__half*>(g); p.ldo = ldg;
-  p.splits = 1; p.status = status; p.debug = g_debug;
+  p.splits = 1; p.status = status; p.spin_limit = kCoopSpinLimit;
   p.gu_inter = I;
   const nf4ll_lora* br[2] = {lora_gate, lora_up};
   void* tout[2] = {t_gate, t_up};
@@ -1354,7 +1438,7 @@ static int run_gate_up(const nf4ll_mat* W, const void* x, int64_t ldx, const nf4
   }
   p.has_lora = (lora_gate || lora_up) ? 1 : 0;
   Plan pl{};
-  pl.bm_tiles = 2; pl.bn = 256; pl.splits = 1; pl.pair = 0;
+  pl.bm_tiles = 2; pl.bn = 256; pl.splits = 1; pl.launch_splits = 1; pl.pair = 0;
   pl.tiles_o = I / 128;
   pl.tiles_m = (M + 255) / 256;
   CUtensorMap map, nib_map, mg, mu, mh;
@@ -1381,16 +1465,56 @@ extern "C" int nf4ll_forward_gate_up(const nf4ll_mat* W, const void* x, int64_t 
                             status, stream);
 }
 
-extern "C" int64_t nf4ll_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t r) {
-  using namespace nf4ll;
-  if (M <= 0 || N <= 0 || K <= 0) return 0;
-  int sms = 148;
-  int dev = 0;
+namespace nf4ll {
+static int sms_or_default() {
+  int sms = 148, dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) {
     int v = 0;
     if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) sms = v;
   }
-  const int64_t f = make_plan(kFwd, M, N, K, r, sms).total(), b = make_plan(kBwd, M, K, N, r, sms).total();
+  return sms;
+}
+
+// Scratch of the forward plan(s) a call may run for W[N,K]: the default tile width and, because a stack of
+// projections whose boundaries are not multiples of 256 columns is planned with 128-column tiles, that one too.
+static int64_t forward_need(int64_t M, int64_t N, int64_t K, int r, int sms, const Tune& tune) {
+  const Plan base = make_plan(kFwd, M, N, K, r, sms, tune);
+  int64_t need = base.total();
+  // the small-batch kernels keep counters and partial sums in the workspace too; with the kernels forced by
+  // the tuning flags a split count may be forced as well
+  const int fs = tune.splits;
+  if (M <= kStreamCapRows) {
+    const int64_t st = base.left_bytes + base.bt_bytes + stream_workspace_bytes(N, K, M, sms, fs);
+    if (st > need) need = st;
+  }
+  if (M <= kSwapMaxRows) {
+    const int64_t st = base.left_bytes + base.bt_bytes + swap_workspace_bytes(N, K, M, sms, fs);
+    if (st > need) need = st;
+  }
+  if (!tune.bn) {
+    Tune narrow = tune;
+    narrow.bn = 128;
+    const int64_t n = make_plan(kFwd, M, N, K, r, sms, narrow).total();
+    if (n > need) need = n;
+  }
+  return need;
+}
+}  // namespace nf4ll
+
+extern "C" int64_t nf4ll_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t r) {
+  return nf4ll_workspace_bytes_tuned(M, N, K, r, 0, 0, 0);
+}
+
+extern "C" int64_t nf4ll_workspace_bytes_tuned(int64_t M, int64_t N, int64_t K, int32_t r, int32_t bm_tiles, int32_t bn,
+                                               int32_t splits) {
+  using namespace nf4ll;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  Tune tune;
+  tune.bm = (bm_tiles == 1 || bm_tiles == 2) ? bm_tiles : 0;
+  tune.bn = (bn == 128 || bn == 256 || bn == 512) ? bn : 0;
+  tune.splits = splits > 0 ? splits : 0;
+  const int sms = sms_or_default();
+  const int64_t f = forward_need(M, N, K, r, sms, tune), b = make_plan(kBwd, M, K, N, r, sms, tune).total();
   return f > b ? f : b;
 }
 
@@ -1417,21 +1541,23 @@ extern "C" int nf4ll_backward_dx(const nf4ll_mat* W, const void* dy, int64_t ldd
 
 // Testing / tuning hook (no counterpart in the reference): force the tile shape and the split count
 // chosen by the calling thread's next calls; zeros restore the built-in heuristic.
-extern "C" void nf4ll_tune_override(int32_t bm_tiles, int32_t bn, int32_t splits) {
-  nf4ll::g_force_bm = (bm_tiles == 1 || bm_tiles == 2) ? bm_tiles : 0;
-  nf4ll::g_force_bn = (bn == 128 || bn == 256 || bn == 512) ? bn : 0;
-  nf4ll::g_force_splits = splits > 0 ? splits : 0;
+extern "C" void nf4ll_tune_override(int32_t bm_tiles, int32_t bn, int32_t splits, int32_t flags) {
+  nf4ll::g_tune.bm = (bm_tiles == 1 || bm_tiles == 2) ? bm_tiles : 0;
+  nf4ll::g_tune.bn = (bn == 128 || bn == 256 || bn == 512) ? bn : 0;
+  nf4ll::g_tune.splits = splits > 0 ? splits : 0;
+  nf4ll::g_tune.flags = flags;
 }
 
-// Measurement hook (no counterpart in the reference): the calling thread's NEXT nf4ll_forward /
-// nf4ll_backward_dx records `start` immediately before and `stop` immediately after its tensor-core
-// kernel on the call's stream (the rank-16 prologue kernel stays outside the pair). One-shot.
+// Measurement hook (no counterpart in the reference): the calling thread's NEXT forward / backward-dX call
+// records `start` immediately before and `stop` immediately after the kernel that computes its product
+// on the call's stream (the rank-16 prologue kernel stays outside the pair). One-shot.
 extern "C" void nf4ll_kernel_events(void* start, void* stop) {
   nf4ll::g_ev_start = static_cast<cudaEvent_t>(start);
   nf4ll::g_ev_stop = static_cast<cudaEvent_t>(stop);
 }
 
-extern "C" void nf4ll_debug_flags(int32_t flags) { nf4ll::g_debug = flags; }
+// Failure-detection test hook (no counterpart in the reference). One-shot.
+extern "C" void nf4ll_test_expire_wait(uint32_t polls) { nf4ll::g_expire_polls = polls; }
 
 // ---------------------------------------------------------------------------------------------
 // Forward without a caller-supplied workspace.
@@ -1481,7 +1607,9 @@ extern "C" int nf4ll_forward_static(const nf4ll_mat* W, const void* x, int64_t l
                                     void* stream) {
   using namespace nf4ll;
   if (!W) { set_detail("nf4ll_forward_static: null weight"); return NF4LL_ERR_NULL; }
-  const int64_t need = nf4ll_workspace_bytes(M, W->N, W->K, lora ? lora->r : 0);
+  if (M < 0 || W->N <= 0 || W->K <= 0) { set_detail("nf4ll_forward_static: bad shape"); return NF4LL_ERR_SHAPE; }
+  // only the forward plan this call will run counts (nf4ll_workspace_bytes also covers the backward)
+  const int64_t need = forward_need(M, W->N, W->K, lora ? lora->r : 0, sms_or_default(), g_tune);
   if (need > static_cast<int64_t>(NF4LL_STATIC_SCRATCH_BYTES)) {
     set_detail("nf4ll_forward_static: this problem needs %lld bytes of scratch, the built-in buffer holds %lld; "
                "use nf4ll_forward with a workspace of your own",

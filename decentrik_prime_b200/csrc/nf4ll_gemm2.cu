@@ -221,25 +221,30 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
                       static_cast<int>(m0 + mt * 256), smem_u32(full_a + s));
         }
       }
-      if (p.splits > 1 && !*abort_flag && !(p.debug & 4)) {
+      if (p.splits > 1 && !*abort_flag) {
         if (wait_or_abort(smem_u32(fix_go), 0, ab, 0x0104) && p.coop && !*abort_flag) {
           // shared reduction (see the single-CTA kernel): stream the other splits' partial sums of the boxes this CTA owns
           fence_proxy_async_all();
           constexpr int NB = BM_TILES * (BN / 32);
-          int n = 0;
+          // the boxes go to the warp groups in turn and every group has its own share of the ring's slots:
+          // a slot is then always filled for, and drained by, the same group, in order
+          constexpr int G = NDW / 4, SPG = kFixSlots / G;
+          int cnt0 = 0, cnt1 = 0, mine = 0;
           bool fine = true;
           for (int b = split; fine && b < NB; b += p.splits) {
             const int mt = b / (BN / 32), cb = b % (BN / 32);
             const int64_t col0 = o0 + cb * 32;
             if (col0 >= p.NO) continue;
+            const int grp = (mine++) % G;
             for (int sp = 0; sp < p.splits; ++sp) {
               if (sp == split) continue;
-              const int slot = n % kFixSlots;
-              if (!wait_or_abort(smem_u32(fx_empty + slot), ((n / kFixSlots) & 1) ^ 1, ab, 0x0105)) { fine = false; break; }
+              const int nn = grp ? cnt1 : cnt0;
+              const int slot = grp * SPG + nn % SPG;
+              if (!wait_or_abort(smem_u32(fx_empty + slot), ((nn / SPG) & 1) ^ 1, ab, 0x0105)) { fine = false; break; }
+              if (grp) ++cnt1; else ++cnt0;
               mbar_arrive_expect_tx(smem_u32(fx_full + slot), 16384);
               tma_load_2d(smem_u32(smem) + slot * 16384, &tmap_out, static_cast<int>(col0),
                           static_cast<int>(static_cast<int64_t>(sp) * p.m_pad + m0 + mt * 256), smem_u32(fx_full + slot));
-              ++n;
             }
           }
         } else if (!p.coop && *last_flag) {
@@ -328,7 +333,7 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
 #pragma unroll
           for (int mt = 0; mt < BM_TILES; ++mt) {
             const uint64_t adesc = make_smem_desc(a_base + mt * 16384 + kk * 32, 16, 1024, kSwizzle128B);
-            if (!(p.debug & 2)) tc_mma2_f16(tmem_base + mt * BN, adesc, bdesc, idesc_main, (lora_here || i > 0 || kk > 0) ? 1u : 0u);
+            tc_mma2_f16(tmem_base + mt * BN, adesc, bdesc, idesc_main, (lora_here || i > 0 || kk > 0) ? 1u : 0u);
           }
         }
         tc_commit2(smem_u32(empty + s));
@@ -483,7 +488,7 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
       if (!wait_or_abort(smem_u32(empty + s), ph ^ 1, ab, 0x0302)) return false;
       // the last stage holds the LoRA operands until the rank-16 MMAs have read them
       if (lora_here && i == S - 1 && !wait_or_abort(smem_u32(lora_done), 0, ab, 0x0305)) return false;
-      if (!(p.debug & 1)) dequant_block_to_smem(b_base + s * Cfg::kBBytes, key, c0, c1, absmax);
+      dequant_block_to_smem(b_base + s * Cfg::kBBytes, key, c0, c1, absmax);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
@@ -549,7 +554,7 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
     // --- epilogue: tensor memory -> registers -> swizzled shared staging -> TMA store (see the single-CTA kernel)
     if (ok) ok = wait_or_abort(smem_u32(acc_full), 0, ab, 0x0303);
     const bool direct = (p.splits == 1);
-    if (ok && !(p.debug & 4)) {
+    if (ok) {
       tc_fence_after();
       constexpr int G = NDW / 4;
       constexpr int HALVES = BN / 128;
@@ -690,7 +695,7 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
         __threadfence();
       }
     }
-    if (!direct && p.coop && !(p.debug & 4)) {
+    if (!direct && p.coop) {
       // shared reduction, second half (see the single-CTA kernel)
       __threadfence();
       named_barrier(1, NDW * 32);
@@ -699,7 +704,7 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
         __threadfence();
         atomicAdd(counter, 1);
         bool seen = false;
-        for (uint32_t i = 0; i < kCoopSpinLimit; ++i) {
+        for (uint32_t i = 0; i < p.spin_limit; ++i) {
           if (ld_acquire_gpu(counter) >= p.splits) { seen = true; break; }
           if ((i & 255u) == 255u && *abort_flag) break;
           __nanosleep(32);
@@ -715,15 +720,14 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
         const int grp = ew >> 2;
         const int r_in = q * 32 + lane;
         const uint32_t ring = smem_u32(smem);
-        int n = 0, mine = 0;
+        constexpr int SPG = kFixSlots / G;       // this group's share of the ring's slots
+        int own = 0, mine = 0;
         bool fine = true;
 #pragma unroll 1
         for (int b = split; fine && b < NB; b += p.splits) {
           const int mt = b / (BN / 32), cb = b % (BN / 32);
           const int64_t col0 = o0 + cb * 32;
           if (col0 >= p.NO) continue;
-          const int n0 = n;
-          n += p.splits - 1;
           if ((mine++) % G != grp) continue;
           uint32_t v[32];
           __syncwarp();
@@ -742,8 +746,8 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
             }
           }
           for (int k = 0; k < p.splits - 1; ++k) {
-            const int nn = n0 + k, slot = nn % kFixSlots;
-            if (!wait_or_abort(smem_u32(fx_full + slot), (nn / kFixSlots) & 1, ab, 0x0305)) { fine = false; break; }
+            const int nn = own++, slot = grp * SPG + nn % SPG;
+            if (!wait_or_abort(smem_u32(fx_full + slot), (nn / SPG) & 1, ab, 0x0305)) { fine = false; break; }
             const uint32_t src = ring + slot * 16384 + r_in * 128;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -774,7 +778,7 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
           }
         }
       }
-    } else if (!direct && !(p.debug & 4)) {
+    } else if (!direct) {
       // split-K fix-up, per CTA: the last CTA (over the splits) that owns these rows of this tile adds the slabs up
       __threadfence();
       named_barrier(1, NDW * 32);
@@ -860,26 +864,47 @@ nf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_
 // ---------------------------------------------------------------------------------------------
 // launch (cluster of two CTAs along x)
 // ---------------------------------------------------------------------------------------------
+bool coop_grid_fits(int64_t ctas, int ctas_per_sm, int sms);
+
 template <int MODE, int BM_TILES>
-static int launch_pair_cfg(const CUtensorMap& map, const CUtensorMap& nib_map, const CUtensorMap& out_map, const GemmParams& p,
-                           int64_t tiles_o, int64_t tiles_mp, int splits, cudaStream_t stream) {
+static int launch_pair_cfg(const CUtensorMap& map, const CUtensorMap& nib_map, const CUtensorMap& out_map, const GemmParams& p_in,
+                           int64_t tiles_o, int64_t tiles_mp, int splits, int launch_splits, cudaStream_t stream) {
   using Cfg = PairCfg<BM_TILES>;
   auto kernel = nf4_gemm_pair_kernel<MODE, BM_TILES>;
   NF4LL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-  PdlLaunch lc(dim3(static_cast<unsigned>(2 * tiles_o), static_cast<unsigned>(tiles_mp), static_cast<unsigned>(splits)),
-               dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, 2, 1, p.coop != 0);
-  NF4LL_CUDA(cudaLaunchKernelEx(&lc.cfg, kernel, map, nib_map, out_map, p));
+  const dim3 grid(static_cast<unsigned>(2 * tiles_o), static_cast<unsigned>(tiles_mp), static_cast<unsigned>(launch_splits));
+  GemmParams p = p_in;
+  if (p.coop) {
+    // the shared split reduction needs every cluster of the grid resident at once: ask the runtime
+    PdlLaunch probe(dim3(grid.x, grid.y, static_cast<unsigned>(splits)), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, 2, 1, false, false);
+    probe.cfg.numAttrs = 1;            // the cluster dimension only
+    int clusters = 0;
+    NF4LL_CUDA(cudaOccupancyMaxActiveClusters(&clusters, kernel, &probe.cfg));
+    if (static_cast<int64_t>(clusters) < static_cast<int64_t>(tiles_o) * tiles_mp * splits) p.coop = 0;
+  }
+  for (;;) {
+    PdlLaunch lc(grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, 2, 1, p.coop != 0);
+    const cudaError_t err = cudaLaunchKernelEx(&lc.cfg, kernel, map, nib_map, out_map, p);
+    if (err == cudaErrorCooperativeLaunchTooLarge && p.coop) {
+      (void)cudaGetLastError();        // fall back to the last-CTA reduction (counters are already zero)
+      p.coop = 0;
+      continue;
+    }
+    NF4LL_CUDA(err);
+    break;
+  }
+  NF4LL_CUDA(cudaGetLastError());
   return NF4LL_OK;
 }
 
 int launch_pair(int mode, int bm_tiles, const CUtensorMap& map, const CUtensorMap& nib_map, const CUtensorMap& out_map,
-                const GemmParams& p, int64_t tiles_o, int64_t tiles_mp, int splits, cudaStream_t stream) {
+                const GemmParams& p, int64_t tiles_o, int64_t tiles_mp, int splits, int launch_splits, cudaStream_t stream) {
   if (mode == kFwd) {
-    return bm_tiles == 2 ? launch_pair_cfg<kFwd, 2>(map, nib_map, out_map, p, tiles_o, tiles_mp, splits, stream)
-                         : launch_pair_cfg<kFwd, 1>(map, nib_map, out_map, p, tiles_o, tiles_mp, splits, stream);
+    return bm_tiles == 2 ? launch_pair_cfg<kFwd, 2>(map, nib_map, out_map, p, tiles_o, tiles_mp, splits, launch_splits, stream)
+                         : launch_pair_cfg<kFwd, 1>(map, nib_map, out_map, p, tiles_o, tiles_mp, splits, launch_splits, stream);
   }
-  return bm_tiles == 2 ? launch_pair_cfg<kBwd, 2>(map, nib_map, out_map, p, tiles_o, tiles_mp, splits, stream)
-                       : launch_pair_cfg<kBwd, 1>(map, nib_map, out_map, p, tiles_o, tiles_mp, splits, stream);
+  return bm_tiles == 2 ? launch_pair_cfg<kBwd, 2>(map, nib_map, out_map, p, tiles_o, tiles_mp, splits, launch_splits, stream)
+                       : launch_pair_cfg<kBwd, 1>(map, nib_map, out_map, p, tiles_o, tiles_mp, splits, launch_splits, stream);
 }
 
 }  // namespace nf4ll

@@ -49,10 +49,10 @@ struct GemmParams {
   int coop;                // split-K: every CTA of the grid is resident at once (cooperative launch), so the splits
                            // of a tile share its reduction instead of leaving it to the last one to finish
   int32_t* status;
-  int debug;               // timing experiments only: bit 0 skips the decode, bit 1 skips the MMAs
+  uint32_t spin_limit;     // polls of a tile counter (each followed by a short sleep) before a split gives up
 };
 
-constexpr uint32_t kCoopSpinLimit = 1u << 22;   // polls (each followed by a short sleep) of a tile counter before giving up
+constexpr uint32_t kCoopSpinLimit = 1u << 22;   // default for GemmParams::spin_limit
 constexpr int kFixSlots = 8;     // 16 KB slots of the split-K fix-up ring (fits every tile shape's operand rings)
 
 struct Abort {

@@ -178,6 +178,7 @@ __global__ void transpose_n16_kernel(const __half* __restrict__ B, __half* __res
 
 int transpose_n16_launch(const void* B, void* Bt, int64_t N, cudaStream_t stream) {
   const int64_t total = N * 16;
+  count_launch();
   transpose_n16_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
       static_cast<const __half*>(B), static_cast<__half*>(Bt), N);
   NF4LL_CUDA(cudaGetLastError());
@@ -219,6 +220,7 @@ int lora_down_launch(const void* act, int64_t ldact, const uint8_t* mask, int64_
   ks = (C + c_per_cta - 1) / c_per_cta;
   dim3 grid(static_cast<unsigned>(row_groups), static_cast<unsigned>(ks));
   if (ks == 1) {
+    count_launch();
     lora_down_kernel<4, kDownDirect, kDownWarps><<<grid, kDownWarps * 32, 0, stream>>>(
         a, ldact, mask, ld_mask, keep_scale, r, scale, M, C, c_per_cta, t, zero_ptr, zero_words);
   } else if (ks <= 8) {
@@ -228,10 +230,12 @@ int lora_down_launch(const void* act, int64_t ldact, const uint8_t* mask, int64_
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = static_cast<unsigned>(ks); attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
+    count_launch();
     NF4LL_CUDA(cudaLaunchKernelEx(&cfg, lora_down_kernel<4, kDownCluster, kDownWarps>, a, ldact, mask, ld_mask, keep_scale, r,
                                   scale, M, C, c_per_cta, t, zero_ptr, zero_words));
   } else {
     NF4LL_CUDA(cudaMemsetAsync(t32, 0, sizeof(float) * 16 * M, stream));
+    count_launch();
     lora_down_kernel<4, kDownAtomic, kDownWarps><<<grid, kDownWarps * 32, 0, stream>>>(
         a, ldact, mask, ld_mask, keep_scale, r, scale, M, C, c_per_cta, t, zero_ptr, zero_words);
   }
@@ -501,6 +505,7 @@ extern "C" int nf4ll_lora_down(const void* x, int64_t ldx, const uint8_t* mask, 
   if (int rc = lora_down_launch(x, ldx, mask, ld_mask, keep_scale, A, 1.0f, M, K, t32, nullptr, 0, st)) return rc;
   if (t16 && M > 0) {
     const int64_t n = M * 16;
+    count_launch();
     scale_to_half_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(static_cast<const float*>(t32),
                                                                               static_cast<__half*>(t16), scale, n);
     NF4LL_CUDA(cudaGetLastError());

@@ -1,0 +1,485 @@
+// Short-batch forward (17 .. 128 token rows) with the roles of the operands swapped: the WEIGHTS are the
+// 128-row M operand of tcgen05.mma and the token rows its N operand (16 .. 128 columns), so no MMA row is
+// padding and the kernel's cost is the stream of NF4 bytes, like the decode-sized kernel's. Replaces, for such
+// batches, the same reference call sites as the big-tile kernel (solution/fast_qwen.py:947, 1037, 1080-1112).
+//
+//   y^T[128 weight rows, tokens] = W_tile[128, K-slice] . x^T          (fp32 in tensor memory)
+//
+// The dequantised weights never touch shared memory: a decode thread owns one weight row of the tile (= one
+// tensor-memory lane), turns the 32 bytes of codes of a quantisation block into 64 fp16 values with 32 loads
+// from a lane-replicated 256-entry table of half2 level pairs (one shift, one logic op and one conflict-free
+// 4-byte shared load per two weights), scales them by the block's absmax and writes them with ONE tcgen05.st
+// into the A-operand region of tensor memory; the MMA reads A from tensor memory and the token tile
+// (TMA, 128-byte swizzle) from shared memory. Codes arrive by TMA in boxes of 128 rows x 128 bytes (four
+// blocks per row: whole 128-byte lines per request), three boxes in flight per CTA.
+//
+// The scale is applied in fp16 (weight = fp16(fp16(NF4[c]) * fp16(absmax))), which differs from the
+// big-tile kernel's bit-exact fp16(NF4[c] * absmax) by a few 2^-11 relative roundings, inside the 1e-3
+// tolerance of the path.
+//
+// A CTA computes one unit = (tile of 128 weight rows) x (slice of the contraction). With more than one
+// slice the units of a tile leave their partial sums in a slab of the workspace and the last one to arrive
+// adds them up in slice order (a fixed order), adds bias and the LoRA term and stores fp16.
+//
+// Warp roles: 0 TMA producer of codes, 1 tensor-memory allocation + MMA issue, 2 TMA producer of token
+// tiles, 3 idle, 4..11 decode (two teams on alternate blocks, one warp per tensor-memory lane quarter) and
+// then the epilogue. Every wait is bounded and reports through the status word.
+#include "nf4ll_gemm_shared.cuh"
+
+namespace nf4ll {
+
+struct SwapParams {
+  const uint8_t* qabs;
+  const float* scale2;
+  const float* offset2;
+  const float* code2;
+  int64_t N, K, M;
+  __half* y;
+  int64_t ldy;
+  const __half* bias;
+  const float* t32;        // [M,16] fp32 = drop(x) . A^T, or null (no LoRA)
+  const __half* lora_b;    // [N,16]
+  float lora_scale;
+  int slices;              // slices of the contraction
+  int groups_per_slice;    // groups of four quantisation blocks per slice
+  float* slab;             // [tiles][slices][NTOK][128] fp32 partial sums (slices > 1)
+  int* counters;           // [tile]: arrivals (zero on entry)
+  int32_t* status;
+};
+
+constexpr int kSwapThreads = 384;
+constexpr int kSwapCSt = 3;                  // coarse stages of codes (four blocks x 128 rows x 32 bytes each)
+constexpr int kSwapCodeBytes = 128 * 128;
+constexpr int kSwapTableBytes = 256 * 128;
+
+template <int NTOK>
+struct SwapCfg {
+  // sub-stages of the A operand in tensor memory (32 columns each) and of the token tiles in shared memory;
+  // three at 64 tokens so that two CTAs fit one SM's shared memory
+  static constexpr int kASt = NTOK == 64 ? 3 : 4;
+  static constexpr int kXBytes = NTOK * 128;                       // one token tile: NTOK rows x 64 fp16
+  static constexpr int kDCols = NTOK < 32 ? 32 : NTOK;             // accumulator columns
+  static constexpr int kTmemCols = 256;                            // accumulator + 4 x 32 A columns, as a power of two
+  static constexpr int kSmemBytes = 1024 + kSwapCSt * kSwapCodeBytes + kASt * kXBytes + kSwapTableBytes + 1024 + 256;
+  static_assert(kDCols + kASt * 32 <= kTmemCols, "tensor memory budget");
+};
+
+// D[tmem] (+)= A[tmem] . B[smem]: the A operand (128 rows x 16 fp16, two per 32-bit column) comes from tensor memory
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ uint32_t lds_u32s(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+
+// address of the table entry of byte I of `w` for this lane: one byte permute isolates the byte, one
+// multiply-add (the other arithmetic pipe) scales it by the entry stride of 128 bytes and adds the lane's base
+template <int I>
+__device__ __forceinline__ uint32_t swap_entry(uint32_t w, uint32_t lane_base) {
+  uint32_t addr;
+  const uint32_t byte = prmt(w, 0u, 0x4440u | I);
+  asm("mad.lo.u32 %0, %1, 128, %2;" : "=r"(addr) : "r"(byte), "r"(lane_base));
+  return addr;
+}
+
+// eight weights of one word of codes (high nibble first), scaled by the block's absmax (both halves of `am2`)
+__device__ __forceinline__ void swap_decode8(uint32_t w, uint32_t lane_base, uint32_t am2, uint32_t* out) {
+  const __half2 a = *reinterpret_cast<const __half2*>(&am2);
+  uint32_t h[4];
+  h[0] = lds_u32s(swap_entry<0>(w, lane_base));
+  h[1] = lds_u32s(swap_entry<1>(w, lane_base));
+  h[2] = lds_u32s(swap_entry<2>(w, lane_base));
+  h[3] = lds_u32s(swap_entry<3>(w, lane_base));
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const __half2 v = __hmul2(*reinterpret_cast<const __half2*>(&h[j]), a);
+    out[j] = *reinterpret_cast<const uint32_t*>(&v);
+  }
+}
+
+template <int NTOK>
+__global__ void __launch_bounds__(kSwapThreads, NTOK <= 64 ? 2 : 1)
+nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_nib, const SwapParams p) {
+  using Cfg = SwapCfg<NTOK>;
+  constexpr int kSwapASt = Cfg::kASt;
+  // x, the weights and code2 may be read at once (what precedes this kernel on the stream is the rank-16
+  // projection kernel, itself started only after all earlier work had finished, or a memset, which orders this
+  // kernel after everything before it); the first write to global memory waits for the predecessor.
+  pdl_launch_dependents();
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sNib = smem;                                         // [kSwapCSt][128 rows][128 B], 128-byte swizzle
+  uint8_t* sX = sNib + kSwapCSt * kSwapCodeBytes;               // [kSwapASt][NTOK rows][128 B], 128-byte swizzle
+  uint32_t* sTbl = reinterpret_cast<uint32_t*>(sX + kSwapASt * Cfg::kXBytes);
+  float* sCode2 = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sTbl) + kSwapTableBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sCode2) + 1024);
+  uint64_t* a_full = bars;                       // [kSwapASt] token tile landed + the team's four warps stored their A rows
+  uint64_t* a_empty = a_full + 4;                // [kSwapASt] the MMAs that read the sub-stage have completed
+  uint64_t* nib_full = a_empty + 4;              // [kSwapCSt] codes landed
+  uint64_t* nib_empty = nib_full + kSwapCSt;     // [kSwapCSt] all eight decode warps have read their blocks
+  uint64_t* acc_full = nib_empty + kSwapCSt;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = abort_flag + 1;
+  uint32_t* sLv = tmem_slot + 4;                 // 16 level bit patterns
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x / p.slices, sl = blockIdx.x - tile * p.slices;
+  const int64_t n0 = static_cast<int64_t>(tile) * 128;
+  const int bpr = static_cast<int>(p.K / 64);
+  const int blk_begin = sl * p.groups_per_slice * 4;
+  int blk_end = blk_begin + p.groups_per_slice * 4;
+  if (blk_end > bpr) blk_end = bpr;
+  const int nblk = blk_end - blk_begin;              // > 0 by construction of the slices
+  const Abort ab{abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kSwapASt; ++s) {
+      mbar_init(smem_u32(a_full + s), 1 + 4);
+      mbar_init(smem_u32(a_empty + s), 1);
+    }
+    for (int s = 0; s < kSwapCSt; ++s) {
+      mbar_init(smem_u32(nib_full + s), 1);
+      mbar_init(smem_u32(nib_empty + s), 8);
+    }
+    mbar_init(smem_u32(acc_full), 1);
+    *abort_flag = 0;
+    *last_flag = 0;
+    mbar_fence_init();
+  }
+  if (threadIdx.x < 16) {
+    constexpr float lv[16] = {NF4LL_LEVELS};
+    float v = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v = (static_cast<int>(threadIdx.x) == j) ? lv[j] : v;
+    sLv[threadIdx.x] = __half_as_ushort(__float2half_rn(v));
+  }
+  if (threadIdx.x < 256) sCode2[threadIdx.x] = p.code2[threadIdx.x];
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncwarp();
+  __syncthreads();
+  tc_fence_after();
+  for (int idx = threadIdx.x; idx < 256 * 32; idx += kSwapThreads) {
+    const int v = idx >> 5;                          // byte value: even element in the high nibble
+    sTbl[idx] = sLv[v >> 4] | (sLv[v & 15] << 16);
+  }
+  __syncthreads();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr uint32_t kACol0 = Cfg::kDCols;
+
+  if (warp == 0) {
+    // ----------------------------------------------------------------------------- codes
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_nib);
+      const int ngrp = (nblk + 3) / 4;
+      int issued = 0;
+      for (int gidx = 0; gidx < ngrp; ++gidx, ++issued) {
+        const int c = gidx % kSwapCSt;
+        if (!wait_or_abort(smem_u32(nib_empty + c), ((gidx / kSwapCSt) & 1) ^ 1, ab, 0x0502)) break;
+        mbar_arrive_expect_tx(smem_u32(nib_full + c), kSwapCodeBytes);
+        tma_load_2d(smem_u32(sNib + c * kSwapCodeBytes), &tmap_nib, (blk_begin + gidx * 4) * 32, static_cast<int>(n0),
+                    smem_u32(nib_full + c));
+      }
+      if (*abort_flag) {
+        for (int gidx = (issued > kSwapCSt ? issued - kSwapCSt : 0); gidx < issued; ++gidx)
+          for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(smem_u32(nib_full + gidx % kSwapCSt), (gidx / kSwapCSt) & 1); ++spin) {}
+      }
+    }
+  } else if (warp == 2) {
+    // ----------------------------------------------------------------------------- token tiles
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_x);
+      int issued = 0;
+      for (int i = 0; i < nblk; ++i, ++issued) {
+        const int sa = i % kSwapASt;
+        if (!wait_or_abort(smem_u32(a_empty + sa), ((i / kSwapASt) & 1) ^ 1, ab, 0x0501)) break;
+        mbar_arrive_expect_tx(smem_u32(a_full + sa), Cfg::kXBytes);
+        tma_load_2d(smem_u32(sX + sa * Cfg::kXBytes), &tmap_x, (blk_begin + i) * 64, 0, smem_u32(a_full + sa));
+      }
+      (void)issued;
+    }
+  } else if (warp == 1) {
+    // ----------------------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(128, NTOK, 0, 0);
+      bool ok = true;
+      for (int i = 0; ok && i < nblk; ++i) {
+        const int sa = i % kSwapASt;
+        if (!wait_or_abort(smem_u32(a_full + sa), (i / kSwapASt) & 1, ab, 0x0503)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t x_base = smem_u32(sX + sa * Cfg::kXBytes);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          const uint64_t bdesc = make_smem_desc(x_base + kk * 32, 16, 1024, kSwizzle128B);
+          tc_mma_f16_ts(tmem_base, tmem_base + kACol0 + sa * 32 + kk * 8, bdesc, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(smem_u32(a_empty + sa));
+      }
+      tc_commit(smem_u32(acc_full));
+      if (!ok) {
+        for (int spin = 0; spin < (1 << 18) && !mbar_try_wait(smem_u32(acc_full), 0); ++spin) {}
+      }
+    }
+  } else if (warp >= 4) {
+    // ----------------------------------------------------------------------------- decode, then epilogue
+    const int q = warp & 3;                       // tensor-memory lane quarter
+    const int team = (warp - 4) >> 2;             // blocks of this parity
+    const int r = q * 32 + lane;                  // weight row inside the tile = tensor-memory lane
+    const int64_t n = n0 + r;
+    const bool row_ok = n < p.N;
+    const int64_t qrow = (row_ok ? n : p.N - 1) * bpr + blk_begin;
+    const uint32_t lane_base = smem_u32(sTbl) + lane * 4;
+    const uint32_t nib_row = smem_u32(sNib) + r * 128;
+    const int key = r & 7;
+    const uint32_t tA = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + kACol0;
+    bool ok = true;
+
+    auto absmax_of = [&](int i) -> float {
+      const int64_t b = qrow + i;
+      return block_absmax(sCode2[__ldg(p.qabs + b)], __ldg(p.scale2 + (b >> 8)), __ldg(p.offset2 + (b >> 8)));
+    };
+    float am_next = (team < nblk) ? absmax_of(team) : 0.f;
+    for (int i = team; ok && i < nblk; i += 2) {
+      const int gidx = i >> 2, j = i & 3, c = gidx % kSwapCSt;
+      const float am = am_next;
+      if (i + 2 < nblk) am_next = absmax_of(i + 2);                     // travels during this block's decode
+      if (!wait_or_abort(smem_u32(nib_full + c), (gidx / kSwapCSt) & 1, ab, 0x0504)) { ok = false; break; }
+      const uint32_t src = nib_row + c * kSwapCodeBytes;
+      const uint4 c0 = lds128(src + (((2 * j) ^ key) << 4));
+      const uint4 c1 = lds128(src + (((2 * j + 1) ^ key) << 4));
+      if (j >= 2 || i + 2 >= nblk) {               // this warp's last block of the coarse stage
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(nib_empty + c));
+      }
+      const int sa = i % kSwapASt;
+      if (!wait_or_abort(smem_u32(a_empty + sa), ((i / kSwapASt) & 1) ^ 1, ab, 0x0505)) { ok = false; break; }
+      const __half2 a2 = __float2half2_rn(am);
+      const uint32_t am2 = *reinterpret_cast<const uint32_t*>(&a2);
+      uint32_t v[32];
+      swap_decode8(c0.x, lane_base, am2, v + 0);  swap_decode8(c0.y, lane_base, am2, v + 4);
+      swap_decode8(c0.z, lane_base, am2, v + 8);  swap_decode8(c0.w, lane_base, am2, v + 12);
+      swap_decode8(c1.x, lane_base, am2, v + 16); swap_decode8(c1.y, lane_base, am2, v + 20);
+      swap_decode8(c1.z, lane_base, am2, v + 24); swap_decode8(c1.w, lane_base, am2, v + 28);
+      __syncwarp();
+      tmem_st32(tA + sa * 32, v);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(a_full + sa));
+    }
+    // a warp that left the loop early (failed wait) still owes nothing: every other waiter sees the abort flag
+
+    // --- epilogue: lane = weight row, columns = tokens
+    if (ok) ok = wait_or_abort(smem_u32(acc_full), 0, ab, 0x0506);
+    pdl_wait();                                 // T and the cleared counters come from the kernel before this one
+    constexpr int kChunks = Cfg::kDCols / 32;
+    const bool direct = p.slices == 1;
+    float bias = 0.f, bs[16];
+    auto load_row_terms = [&]() {
+      if (p.bias && row_ok) bias = __half2float(p.bias[n]);
+      if (p.t32 && row_ok) {
+        float tmp[8];
+        const uint4* bp = reinterpret_cast<const uint4*>(p.lora_b + n * 16);
+        unpack8(__ldg(bp), tmp);
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) bs[jj] = tmp[jj] * p.lora_scale;
+        unpack8(__ldg(bp + 1), tmp);
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) bs[8 + jj] = tmp[jj] * p.lora_scale;
+      }
+    };
+    auto finish = [&](int tok, float v) {
+      // bias, LoRA term, one rounding; 32 lanes store 32 consecutive output columns of one token row
+      if (p.t32) {
+        const float4* tr = reinterpret_cast<const float4*>(p.t32 + static_cast<int64_t>(tok) * 16);
+        float l = 0.f;
+#pragma unroll
+        for (int j4 = 0; j4 < 4; ++j4) {
+          const float4 tv = __ldcg(tr + j4);
+          l = fmaf(tv.x, bs[4 * j4], l); l = fmaf(tv.y, bs[4 * j4 + 1], l);
+          l = fmaf(tv.z, bs[4 * j4 + 2], l); l = fmaf(tv.w, bs[4 * j4 + 3], l);
+        }
+        v += l;
+      }
+      p.y[static_cast<int64_t>(tok) * p.ldy + n] = __float2half_rn(v + bias);
+    };
+    if (ok) {
+      tc_fence_after();
+      if (direct) load_row_terms();
+      for (int ch = team; ch < kChunks; ch += 2) {
+        uint32_t v[32];
+        __syncwarp();
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ch * 32, v);
+        tmem_ld_wait();
+        if (direct) {
+          if (row_ok) {
+#pragma unroll
+            for (int jt = 0; jt < 32; ++jt) {
+              const int tok = ch * 32 + jt;
+              if (tok < p.M) finish(tok, __uint_as_float(v[jt]));
+            }
+          }
+        } else {
+          float* mine = p.slab + ((static_cast<int64_t>(tile) * p.slices + sl) * NTOK) * 128 + r;
+#pragma unroll
+          for (int jt = 0; jt < 32; ++jt) {
+            const int tok = ch * 32 + jt;
+            if (tok < p.M) mine[static_cast<int64_t>(tok) * 128] = __uint_as_float(v[jt]);
+          }
+        }
+      }
+    }
+    if (!direct) {
+      // the unit of a tile that arrives last adds the partial sums up in slice order
+      __threadfence();
+      named_barrier(1, 256);
+      if (threadIdx.x == 128) {
+        const int prev = atomicAdd(p.counters + tile, 1);
+        if (prev == p.slices - 1) *last_flag = 1;
+        __threadfence();
+      }
+      named_barrier(1, 256);
+      if (*last_flag && !*abort_flag) {
+        load_row_terms();
+        const float* all = p.slab + (static_cast<int64_t>(tile) * p.slices * NTOK) * 128 + r;
+        const int tok_end = static_cast<int>(p.M < NTOK ? p.M : NTOK);
+        for (int tok = team; tok < tok_end; tok += 2) {
+          float v = 0.f;
+          for (int s2 = 0; s2 < p.slices; ++s2) v += __ldcg(all + (static_cast<int64_t>(s2) * NTOK + tok) * 128);
+          if (row_ok) finish(tok, v);
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncwarp();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*SwapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int swap_encode(CUtensorMap* map, CUtensorMapDataType type, const void* base, uint64_t inner, uint64_t outer,
+                       uint64_t stride_bytes, uint32_t box_inner, uint32_t box_outer, const char* what) {
+  static SwapEncodeFn cached = nullptr;
+  if (!cached) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    NF4LL_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (qres != cudaDriverEntryPointSuccess || !fn) {
+      set_detail("cuTensorMapEncodeTiled not available from the driver");
+      return NF4LL_ERR_CUDA;
+    }
+    cached = reinterpret_cast<SwapEncodeFn>(fn);
+  }
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {stride_bytes};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = cached(map, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_detail("cuTensorMapEncodeTiled (%s) failed with CUresult %d", what, static_cast<int>(r));
+    return NF4LL_ERR_CUDA;
+  }
+  return NF4LL_OK;
+}
+
+static int swap_ntok(int64_t M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
+
+// Slices of the contraction for W[N,K]: enough units (tiles x slices) for a few CTAs per SM, in whole groups of
+// four quantisation blocks, at least two groups per slice.
+void swap_plan(int64_t N, int64_t K, int sms, int force_slices, int* slices, int* groups_per_slice) {
+  const int groups = static_cast<int>((K / 64 + 3) / 4);
+  const int64_t tiles = (N + 127) / 128;
+  int s = 1;
+  const int64_t want = static_cast<int64_t>(sms) * 4;
+  if (tiles < want) s = static_cast<int>((want + tiles - 1) / tiles);
+  int max_s = groups / 2;
+  if (max_s < 1) max_s = 1;
+  if (s > max_s) s = max_s;
+  if (force_slices > 0) s = force_slices;
+  if (s > groups) s = groups;
+  const int per = (groups + s - 1) / s;
+  *slices = (groups + per - 1) / per;
+  *groups_per_slice = per;
+}
+
+int64_t swap_workspace_bytes(int64_t N, int64_t K, int64_t M, int sms, int force_slices) {
+  int s = 1, per = 0;
+  swap_plan(N, K, sms, force_slices, &s, &per);
+  const int64_t tiles = (N + 127) / 128;
+  const int64_t counters = (tiles * 4 + 255) / 256 * 256;
+  const int64_t slab = s > 1 ? tiles * s * swap_ntok(M) * 128 * 4 : 0;
+  return counters + (slab + 255) / 256 * 256;
+}
+
+template <int NTOK>
+static int swap_launch_cfg(const CUtensorMap& mx, const CUtensorMap& mn, const SwapParams& p, unsigned grid, cudaStream_t stream) {
+  using Cfg = SwapCfg<NTOK>;
+  auto kernel = nf4_swap_kernel<NTOK>;
+  NF4LL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+  PdlLaunch lc(dim3(grid), dim3(kSwapThreads), Cfg::kSmemBytes, stream);
+  NF4LL_CUDA(cudaLaunchKernelEx(&lc.cfg, kernel, mx, mn, p));
+  return NF4LL_OK;
+}
+
+// `scratch`: the tile counters (cleared here unless `counters_zeroed`: the rank-16 projection kernel launched
+// just before has then done it) followed, 256-byte aligned, by the slab.
+int swap_forward_launch(const nf4ll_mat* W, const void* x, int64_t ldx, const void* bias, const float* t32,
+                        const void* lora_b, float lora_scale, int64_t M, void* y, int64_t ldy, void* scratch,
+                        bool counters_zeroed, int force_slices, int32_t* status, cudaStream_t stream) {
+  int dev = 0, sms = 148;
+  NF4LL_CUDA(cudaGetDevice(&dev));
+  NF4LL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  SwapParams p{};
+  p.qabs = W->qabs; p.scale2 = W->scale2; p.offset2 = W->offset2; p.code2 = W->code2;
+  p.N = W->N; p.K = W->K; p.M = M;
+  p.y = static_cast<__half*>(y); p.ldy = ldy;
+  p.bias = static_cast<const __half*>(bias);
+  p.t32 = t32; p.lora_b = static_cast<const __half*>(lora_b); p.lora_scale = lora_scale;
+  p.status = status;
+  swap_plan(W->N, W->K, sms, force_slices, &p.slices, &p.groups_per_slice);
+  const int64_t tiles = (W->N + 127) / 128;
+  const int64_t counter_bytes = (tiles * 4 + 255) / 256 * 256;
+  p.counters = static_cast<int*>(scratch);
+  p.slab = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + counter_bytes);
+  if (p.slices > 1 && !counters_zeroed) NF4LL_CUDA(cudaMemsetAsync(p.counters, 0, tiles * 4, stream));
+  const int ntok = swap_ntok(M);
+  CUtensorMap mx, mn;
+  if (int rc = swap_encode(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x, static_cast<uint64_t>(W->K), static_cast<uint64_t>(M),
+                           static_cast<uint64_t>(ldx) * 2, 64, static_cast<uint32_t>(ntok), "token tile")) return rc;
+  if (int rc = swap_encode(&mn, CU_TENSOR_MAP_DATA_TYPE_UINT8, W->nib, static_cast<uint64_t>(W->K / 2), static_cast<uint64_t>(W->N),
+                           static_cast<uint64_t>(W->K / 2), 128, 128, "codes")) return rc;
+  const unsigned grid = static_cast<unsigned>(tiles * p.slices);
+  switch (ntok) {
+    case 16: return swap_launch_cfg<16>(mx, mn, p, grid, stream);
+    case 32: return swap_launch_cfg<32>(mx, mn, p, grid, stream);
+    case 64: return swap_launch_cfg<64>(mx, mn, p, grid, stream);
+    default: return swap_launch_cfg<128>(mx, mn, p, grid, stream);
+  }
+}
+
+}  // namespace nf4ll

@@ -12,6 +12,7 @@ Call-site mapping to the reference (solution/fast_qwen.py):
   lora_grads   <- d_bq / d_aq / d_bv / d_av (1369-1374)
 """
 
+import contextlib
 import ctypes
 import threading
 
@@ -63,13 +64,31 @@ class _DeviceState(threading.local):
     def __init__(self):
         self.ws = {}
         self.status = {}
+        self.tune = (0, 0, 0)
 
 
 _state = _DeviceState()
 
 
 def _workspace_need(M, N, K, r):
+    if any(_state.tune):
+        return _lib.lib().nf4ll_workspace_bytes_tuned(M, N, K, r, *_state.tune)
     return _lib.lib().nf4ll_workspace_bytes(M, N, K, r)
+
+
+@contextlib.contextmanager
+def tune_override(bm_tiles=0, bn=0, splits=0, flags=0):
+    """Testing / tuning hook: force the tile shape (bm_tiles 1|2, bn 128|256, 512 = CTA-pair kernel) and the
+    split count for this thread's calls inside the block; flags bit 0 keeps split contractions off the
+    cooperative reduction. Workspaces allocated inside the block are sized for the forced plan."""
+    h = _lib.lib()
+    h.nf4ll_tune_override(bm_tiles, bn, splits, flags)
+    _state.tune = (bm_tiles, bn, splits)
+    try:
+        yield
+    finally:
+        h.nf4ll_tune_override(0, 0, 0, 0)
+        _state.tune = (0, 0, 0)
 
 
 def _workspace(device, nbytes):

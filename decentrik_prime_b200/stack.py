@@ -56,9 +56,31 @@ class DecoderLayerProjections:
         self.w_gu = linear.Nf4Weight.from_layer_group(self.layer, ("gate_proj", "up_proj"), self.code2)
         self.bias_qkv = torch.cat([self.proj[n].bias for n in ("q_proj", "k_proj", "v_proj")]) if bias_qkv else None
         self.fused_groups = all(r % 128 == 0 for r in self.w_qkv.rows_each + self.w_gu.rows_each)
+        # backward of a stacked group as ONE launch (reference solution/fast_qwen.py:1338, 1364): gate|up when
+        # neither carries LoRA; K|V when only v does (its lora_B zero-padded over the k rows, so that
+        # [dk | dv] . B_pad = dv . B_v and the one dropout mask of the launch is v's)
+        P = self.proj
+        self.gu_one_backward = not (P["gate_proj"].has_lora or P["up_proj"].has_lora)
+        self.kv_one_backward = P["v_proj"].has_lora and not P["k_proj"].has_lora
+        if self.kv_one_backward:
+            self.w_kv = linear.Nf4Weight.from_layer_group(self.layer, ("k_proj", "v_proj"), self.code2)
+            pv = P["v_proj"]
+            self._Bv_pad = torch.zeros(2 * kv, linear.RANK, dtype=torch.float16, device=device)
+            self._Bvt_pad = torch.zeros(linear.RANK, 2 * kv, dtype=torch.float16, device=device)
+            self._pad_src = pv
+            self.refresh16()
         # with a bucket the layer's gradients are one contiguous slice: cleared by one fill per backward
         self._grad_slice = bucket.flat[grad_lo:bucket._at] if bucket is not None and bucket._at > grad_lo else None
         self._saved = None
+
+    def refresh16(self):
+        """Refresh every fp16 LoRA shadow from its fp32 master (after an optimiser step)."""
+        for p in self.proj.values():
+            if p.has_lora:
+                p.refresh16()
+        if self.kv_one_backward:
+            self._Bv_pad[self.kv:].copy_(self._pad_src.B16)
+            self._Bvt_pad[:, self.kv:].copy_(self._pad_src.B16t)
 
     def grad_numel(self, lora_on):
         return sum(blocks.lora_grad_numel(self.proj[n].w.N, self.proj[n].w.K) for n in lora_on)
@@ -116,8 +138,14 @@ class DecoderLayerProjections:
         ag = accumulate_grads
         dh = P["down_proj"].backward(dout, accumulate_grads=ag)
         dg, du = linear.swiglu_backward(g, u, dh, inplace=True)
-        dh1 = P["gate_proj"].backward(dg, accumulate_grads=ag)
-        dh1 = P["up_proj"].backward(du, out=dh1, accumulate=True, accumulate_grads=ag)
+        gu = g._base
+        if self.gu_one_backward and gu is not None and gu.shape == (g.shape[0], 2 * self.inter):
+            # [dg | du] . W_gu: one launch, one rounding of the sum
+            dh1, _ = linear.backward_dx(self.w_gu, gu)
+            P["gate_proj"]._saved = P["up_proj"]._saved = None
+        else:
+            dh1 = P["gate_proj"].backward(dg, accumulate_grads=ag)
+            dh1 = P["up_proj"].backward(du, out=dh1, accumulate=True, accumulate_grads=ag)
         dh1 += dout                                            # residual around the MLP
         da = P["o_proj"].backward(dh1, accumulate_grads=ag)
         dqkv = torch.empty(da.shape[0], H + 2 * KV, dtype=torch.float16, device=da.device)
@@ -127,8 +155,18 @@ class DecoderLayerProjections:
         dx = None
         if need_dx:
             dx = P["q_proj"].backward(dqkv[:, :H], accumulate_grads=ag)
-            dx = P["k_proj"].backward(dqkv[:, H:H + KV], out=dx, accumulate=True, accumulate_grads=ag)
-            dx = P["v_proj"].backward(dqkv[:, H + KV:], out=dx, accumulate=True, accumulate_grads=ag)
+            if self.kv_one_backward:
+                pv = P["v_proj"]
+                xv, mask_v, ks_v, t_v = pv._saved
+                lora_kv = (pv.A16, self._Bv_pad, pv.scale, self._Bvt_pad)
+                dx, u_v = linear.backward_dx(self.w_kv, dqkv[:, H:], lora=lora_kv, mask=mask_v, keep_scale=ks_v, out=dx,
+                                             accumulate=True, want_u=True)
+                linear.lora_grads(dqkv[:, H + KV:], xv, t_v, u_v, pv.scale, mask=mask_v, keep_scale=ks_v, dA=pv.dA, dB=pv.dB,
+                                  accumulate=ag)
+                pv._saved = P["k_proj"]._saved = None
+            else:
+                dx = P["k_proj"].backward(dqkv[:, H:H + KV], out=dx, accumulate=True, accumulate_grads=ag)
+                dx = P["v_proj"].backward(dqkv[:, H + KV:], out=dx, accumulate=True, accumulate_grads=ag)
             dx += dh1                                          # residual around the attention stand-in
         else:
             # the first layer needs no d(input), only its LoRA gradients (solution/fast_qwen.py:1363-1364)
@@ -148,7 +186,7 @@ class ProjectionStack:
                                                  "up_proj": (inter, hidden), "down_proj": (hidden, inter)}[n])
                         for n in self.lora_on)
         # `distinct_layers` < n_layers reuses weight sets round-robin (benchmarks of very deep stacks on a
-        # budget of set-up time); gradients then accumulate per distinct layer
+        # budget of set-up time); each backward then overwrites the gradients of the layer object it runs on
         n_distinct = n_layers if distinct_layers is None else min(distinct_layers, n_layers)
         self.bucket = blocks.GradBucket(per_layer * n_distinct, device)
         self._distinct = [DecoderLayerProjections(hidden, inter, kv, seed * 1000 + i, device, self.lora_on, self.bucket)
@@ -160,20 +198,33 @@ class ProjectionStack:
     def flops(self, M):
         return sum(layer.flops(M) for layer in self.layers)
 
-    def step(self, x, dy, masks_per_layer, keep_scale, need_input_grad=False):
+    def step(self, x, dy, masks_per_layer, keep_scale, need_input_grad=False, sync=None):
         """Forward through all layers, then backward-dX through all layers. With shared weight sets
         each layer runs forward+backward in turn instead (activation memory of one layer). The first
-        layer's d(input) is only computed on request (the reference skips it: nothing below needs it)."""
+        layer's d(input) is only computed on request (the reference skips it: nothing below needs it).
+        `sync` (a dp.GradSync with one slot per distinct layer): each layer's slice of the gradient bucket is
+        all-reduced on the side stream as soon as its backward has been queued, under the remaining backward."""
+        n_distinct = len(self._distinct)
+
+        def backward(i, d, need_dx):
+            layer = self.layers[i]
+            if sync is not None:
+                sync.wait_slot(i % n_distinct)          # the slice's previous exchange must be over before it is cleared
+            out = layer.backward(d, need_dx=need_dx)
+            if sync is not None and layer._grad_slice is not None:
+                sync.launch(i % n_distinct, layer._grad_slice)
+            return out
+
         if self._shared:
             dx = None
             for i, layer in enumerate(self.layers):
                 out = layer.forward(x, masks_per_layer[i % len(masks_per_layer)], keep_scale)
-                dx = layer.backward(dy, need_dx=True)
+                dx = backward(i, dy, True)
             return out, dx
         acts = [x]
         for i, layer in enumerate(self.layers):
             acts.append(layer.forward(acts[-1], masks_per_layer[i], keep_scale))
         d = dy
         for i in reversed(range(self.n_layers)):
-            d = self.layers[i].backward(d, need_dx=i > 0 or need_input_grad)
+            d = backward(i, d, i > 0 or need_input_grad)
         return acts[-1], d

@@ -89,6 +89,12 @@ int nf4ll_dequant(const uint8_t* nib, const uint8_t* qabs, const float* scale2, 
  * partial sums and tile counters. Always a multiple of 256; the workspace must be 256-byte aligned. */
 int64_t nf4ll_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t r);
 
+/* The same figure for calls made under nf4ll_tune_override(bm_tiles, bn, splits, ...): a forced split
+ * count or tile shape changes the scratch a call needs. nf4ll_workspace_bytes itself never depends on
+ * the calling thread's override. Testing hook; no counterpart in the reference. */
+int64_t nf4ll_workspace_bytes_tuned(int64_t M, int64_t N, int64_t K, int32_t r, int32_t bm_tiles, int32_t bn,
+                                    int32_t splits);
+
 /* Forward:  y[M,N] = x[M,K] . W^T (+ bias) + scale * (drop(x) . A^T) . B^T,  drop(x) = fp16(x * mask * keep_scale)
  * in ONE pass over the NF4 bytes: tiles of W are dequantised into shared memory and fed to
  * tcgen05 MMAs (fp32 accumulation in tensor memory); bias and the LoRA term are added to the fp32
@@ -201,15 +207,32 @@ int nf4ll_swiglu_backward(const void* g, int64_t ldg, const void* u, int64_t ldu
 int nf4ll_read_status(const int32_t* status, void* stream);
 
 /* Testing and tuning hook; no counterpart in the reference. Forces the tile shape (bm_tiles 1|2 =
- * 128|256 rows, bn 128|256 columns, bn 512 = the CTA-pair kernel) and the split count of the contraction for the calling
- * thread's next nf4ll_forward / nf4ll_backward_dx calls; zeros restore the built-in heuristic. */
-void nf4ll_tune_override(int32_t bm_tiles, int32_t bn, int32_t splits);
+ * 128|256 rows, bn 128|256 columns, bn 512 = the CTA-pair kernel) and the split count of the contraction
+ * for the calling thread's next nf4ll_forward / nf4ll_backward_dx calls; zeros restore the built-in
+ * heuristic. flags bit 0: never use the cooperative split reduction (the splits of a tile then leave the
+ * sum to whichever of them finishes last), e.g. under a profiler that replays kernels one at a time.
+ * Size the workspace of such calls with nf4ll_workspace_bytes_tuned. */
+void nf4ll_tune_override(int32_t bm_tiles, int32_t bn, int32_t splits, int32_t flags);
 
 /* Measurement hook; no counterpart in the reference. The calling thread's NEXT nf4ll_forward /
- * nf4ll_backward_dx records the CUDA events `start` / `stop` (cudaEvent_t as void*) right before /
- * after its tensor-core kernel on the call's stream, leaving the small rank-16 prologue kernel
- * outside the pair. One-shot: the pair is forgotten after that call. */
+ * nf4ll_backward_dx / nf4ll_forward_gate_up records the CUDA events `start` / `stop` (cudaEvent_t as
+ * void*) right before / after the kernel that computes its product on the call's stream, leaving the
+ * small rank-16 prologue kernel outside the pair. One-shot: the pair is forgotten after that call. */
 void nf4ll_kernel_events(void* start, void* stop);
+
+/* Measurement hook; no counterpart in the reference. Number of kernels the calling thread has launched
+ * through this library so far (memsets and event records are not kernels). Benchmarks take the difference
+ * across one step to report how many of the library's kernels a step consists of. */
+int64_t nf4ll_launch_count(void);
+
+/* Failure-detection test hook; no counterpart in the reference. The calling thread's NEXT call whose
+ * contraction is split with the cooperative reduction is launched one split short and with a limit of
+ * `polls` polls (instead of 2^22) on the wait for a tile's other splits. Nothing ever completes those
+ * tiles' counters, so every CTA's wait runs out: each one records NF4LL_ERR_DEVICE_WAIT's cause in the
+ * status word, releases its tensor memory and returns; the call's output is undefined, the context stays
+ * usable and later calls are unaffected (the tile counters are cleared before every use). One-shot;
+ * ignored by calls that do not split cooperatively. */
+void nf4ll_test_expire_wait(uint32_t polls);
 
 #ifdef __cplusplus
 }

@@ -32,6 +32,36 @@ def test_every_declared_symbol_is_exported(handle):
     assert set(names) == set(_lib.SIGNATURES), "ctypes signatures out of step with the header"
 
 
+def test_nothing_undeclared_is_exported(handle):
+    """The dynamic symbol table holds exactly the nf4ll_* functions the header declares (no debugging
+    back doors), read from the ELF file with `nm -D`."""
+    import shutil
+    import subprocess
+    nm = shutil.which("nm")
+    if nm is None:
+        pytest.skip("binutils nm not installed")
+    out = subprocess.run([nm, "-D", "--defined-only", _lib.LIB_PATH], capture_output=True, text=True, check=True).stdout
+    exported = sorted({line.split()[-1] for line in out.splitlines() if " T " in line and line.split()[-1].startswith("nf4ll_")})
+    assert exported == declared_symbols()
+
+
+def test_workspace_query_ignores_the_thread_override(handle):
+    """nf4ll_workspace_bytes is a pure function of the shape; a forced split count only shows through
+    nf4ll_workspace_bytes_tuned; the plain figure covers the 128-column plan of stacked projections."""
+    base = handle.nf4ll_workspace_bytes(2048, 1536, 1536, 16)
+    handle.nf4ll_tune_override(0, 0, 4, 0)
+    try:
+        assert handle.nf4ll_workspace_bytes(2048, 1536, 1536, 16) == base
+    finally:
+        handle.nf4ll_tune_override(0, 0, 0, 0)
+    assert handle.nf4ll_workspace_bytes_tuned(2048, 1536, 1536, 16, 0, 0, 4) > base
+    assert handle.nf4ll_workspace_bytes_tuned(2048, 1536, 1536, 16, 0, 0, 0) == base
+    for M in (1, 64, 128, 300, 2048):
+        for N, K in ((256, 256), (1536, 1536), (2048, 1536), (512, 3584), (8960, 1536), (1536, 8960)):
+            plain = handle.nf4ll_workspace_bytes(M, N, K, 16)
+            assert plain % 256 == 0 and plain >= M * 16 * 4
+
+
 def test_version_and_error_strings(handle):
     assert handle.nf4ll_version() == 1
     assert handle.nf4ll_error_string(0) == b"ok"

@@ -27,14 +27,10 @@ def run_case(N, K, M, lora=True, dropout=0.05, bias=False, force=(0, 0, 0), seed
     if padded:          # leading dimensions larger than the row: column slices of wider tensors
         x = torch.cat([d.x, torch.full((M, 64), 7.0, dtype=torch.float16, device="cuda")], 1)[:, :K]
         dy = torch.cat([d.dy, torch.full((M, 8), 7.0, dtype=torch.float16, device="cuda")], 1)[:, :N]
-    h = _lib.lib()
-    h.nf4ll_tune_override(*force)
-    try:
+    with linear.tune_override(*force):
         y, t = linear.forward(d.w, x, bias=d.bias, lora=d.lora, mask=d.mask, keep_scale=d.keep_scale, want_t=True)
         dx, u = linear.backward_dx(d.w, dy, lora=d.lora, mask=d.mask, keep_scale=d.keep_scale, want_u=True)
         linear.check_status()
-    finally:
-        h.nf4ll_tune_override(0, 0, 0)
     assert_close("y", y, ref["y"])
     assert_close("dx", dx, ref["dx"])
     if lora:
@@ -315,12 +311,8 @@ def test_split_contraction_is_stable_under_back_to_back_launches():
     and the hand-over of partial sums between the CTAs of a tile."""
     pr = make_problem(1536, 1536, 2048, seed=61, lora=False, bias=True)
     d = to_device(pr)
-    h = _lib.lib()
-    h.nf4ll_tune_override(0, 0, 1)
-    try:
+    with linear.tune_override(splits=1):
         y0, _ = linear.forward(d.w, d.x, bias=d.bias)
-    finally:
-        h.nf4ll_tune_override(0, 0, 0)
     outs = [linear.forward(d.w, d.x, bias=d.bias)[0] for _ in range(100)]
     linear.check_status()
     assert all(torch.equal(o, outs[0]) for o in outs), "split-K results differ between launches"

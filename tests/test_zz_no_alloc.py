@@ -13,7 +13,7 @@ import torch
 
 from decentrik_prime_b200 import _lib, linear
 from oracle import nf4_oracle
-from tests.problem import make_problem, to_device
+from tests.problem import make_problem, oracle_weight, to_device
 
 pytestmark = pytest.mark.gpu
 MAX_ABS, REL_L2 = 2e-2, 1e-3
@@ -37,7 +37,8 @@ def test_static_scratch_forward_matches_workspace_forward_twice():
     # two different problems in a row through the same built-in buffer: the first splits its contraction
     # (partial sums and tile counters live in the scratch), the second does not
     for N, K, M, seed in ((1536, 1536, 2048, 51), (512, 256, 300, 52)):
-        d = to_device(make_problem(N, K, M, seed=seed, lora=True, dropout=0.05, bias=True))
+        pr = make_problem(N, K, M, seed=seed, lora=True, dropout=0.05, bias=True)
+        d = to_device(pr)
         need = h.nf4ll_workspace_bytes(M, N, K, 16)
         assert need <= 40 * 1024 * 1024
         ws = torch.empty(max(need, 256), dtype=torch.uint8, device="cuda")
@@ -46,12 +47,21 @@ def test_static_scratch_forward_matches_workspace_forward_twice():
         t_ref = torch.empty(M, 16, dtype=torch.float32, device="cuda")
         t_new = torch.full((M, 16), float("nan"), dtype=torch.float32, device="cuda")
         _lib.check(_call(h, False, d, y_ref, t_ref, ws))
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         _lib.check(_call(h, True, d, y_new, t_new))
         linear.check_status()
+        # the call took nothing from the device: not through the runtime, not through torch's allocator
+        assert torch.cuda.mem_get_info()[0] == free_before
         err, rel = nf4_oracle.errors(y_new, y_ref.float())
         assert err <= MAX_ABS and rel <= REL_L2, (N, K, M, err, rel)
         err, rel = nf4_oracle.errors(t_new, t_ref)
         assert err <= MAX_ABS and rel <= REL_L2, (N, K, M, err, rel)
+        # and against the CPU oracle, not only against the library's other entry point
+        ref = nf4_oracle.lora_linear_o1(oracle_weight(pr), pr.x, None, pr.bias, pr.A16, pr.B16, pr.scale, pr.mask, pr.keep_scale)
+        for name, got in (("y", y_new), ("t", t_new)):
+            err, rel = nf4_oracle.errors(got, ref[name])
+            assert err <= MAX_ABS and rel <= REL_L2, (name, N, K, M, err, rel)
 
 
 def test_static_scratch_refuses_problems_that_do_not_fit():
@@ -59,12 +69,9 @@ def test_static_scratch_refuses_problems_that_do_not_fit():
     d = to_device(make_problem(1536, 1536, 2048, seed=53, lora=True, dropout=0.05, bias=True))
     y = torch.empty(2048, 1536, dtype=torch.float16, device="cuda")
     t = torch.empty(2048, 16, dtype=torch.float32, device="cuda")
-    h.nf4ll_tune_override(0, 0, 4)            # four fp32 partial slabs of 12.6 MB each: more than the buffer holds
-    try:
-        assert h.nf4ll_workspace_bytes(2048, 1536, 1536, 16) > 40 * 1024 * 1024
+    with linear.tune_override(splits=4):      # four fp32 partial slabs of 12.6 MB each: more than the buffer holds
+        assert h.nf4ll_workspace_bytes_tuned(2048, 1536, 1536, 16, 0, 0, 4) > 40 * 1024 * 1024
         rc = _call(h, True, d, y, t)
-    finally:
-        h.nf4ll_tune_override(0, 0, 0)
     assert rc == -14
     assert b"built-in buffer" in h.nf4ll_last_error_detail()
     with pytest.raises(ValueError):
