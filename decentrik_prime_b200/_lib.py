@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB_PATH = os.path.join(HERE, "libnf4ll.so")
-SOURCES = ("nf4ll_api.cu", "nf4ll_dequant.cu", "nf4ll_gemm.cu", "nf4ll_gemm2.cu", "nf4ll_lora.cu", "nf4ll_swiglu.cu", "nf4ll_stream.cu", "nf4ll_swap.cu")
+SOURCES = ("nf4ll_api.cu", "nf4ll_dequant.cu", "nf4ll_gemm.cu", "nf4ll_gemm2.cu", "nf4ll_lora.cu", "nf4ll_swiglu.cu", "nf4ll_stream.cu", "nf4ll_swap.cu", "nf4ll_norm.cu")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "--fmad=true", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "-shared"]
@@ -100,7 +100,8 @@ class LoraArgs(ctypes.Structure):
 
 class Segment(ctypes.Structure):
     """struct nf4ll_segment (include/nf4ll.h)."""
-    _fields_ = [("rows", ctypes.c_int64), ("lora", ctypes.POINTER(LoraArgs)), ("t_out", ctypes.c_void_p)]
+    _fields_ = [("rows", ctypes.c_int64), ("lora", ctypes.POINTER(LoraArgs)), ("t_out", ctypes.c_void_p),
+                ("t_ready", ctypes.c_int32)]
 
 
 _vp, _i64, _i32, _f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_float
@@ -127,6 +128,8 @@ SIGNATURES = {
     "nf4ll_test_expire_wait": (None, [ctypes.c_uint32]),
     "nf4ll_launch_count": (_i64, []),
     "nf4ll_kernel_events": (None, [_vp, _vp]),
+    "nf4ll_rms_forward": (_i32, [_vp, _vp, _vp, _vp, _f32, _i64, _i64, _vp, _i64, _vp, _LORA, _vp, _LORA, _vp, _vp]),
+    "nf4ll_rms_backward": (_i32, [_vp, _i64, _f32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _LORA, _vp, _LORA, _vp, _vp]),
     "nf4ll_swiglu_forward": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "nf4ll_swiglu_backward": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "nf4ll_read_status": (_i32, [_vp, _vp]),

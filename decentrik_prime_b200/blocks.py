@@ -47,16 +47,24 @@ class Projection:
     `_refresh_lora16`, solution/fast_qwen.py:686-692)."""
 
     def __init__(self, weight: linear.Nf4Weight, bias=None, lora=False, alpha=32.0, bucket=None, seed=0,
-                 b_std=0.01):
+                 b_std=0.01, lora_init=None):
+        """`lora_init` = (A fp32 [16,K], B fp32 [N,16], scale): the masters of an existing adapter (they are
+        used as they are, on the weight's device); otherwise `lora=True` draws seeded ones."""
         self.w, self.bias = weight, bias
-        self.has_lora = bool(lora)
+        self.has_lora = bool(lora) or lora_init is not None
         self.scale = alpha / linear.RANK
         dev = weight.device
         if self.has_lora:
-            gen = torch.Generator().manual_seed(seed)
-            bound = 1.0 / math.sqrt(weight.K)          # kaiming_uniform(a=sqrt(5)), PEFT's lora_A init
-            self.A = ((torch.rand(linear.RANK, weight.K, generator=gen) * 2 - 1) * bound).to(dev)
-            self.B = (torch.randn(weight.N, linear.RANK, generator=gen) * b_std).to(dev)
+            if lora_init is not None:
+                A, B, self.scale = lora_init
+                if tuple(A.shape) != (linear.RANK, weight.K) or tuple(B.shape) != (weight.N, linear.RANK):
+                    raise ValueError(f"LoRA factors {tuple(A.shape)}, {tuple(B.shape)} do not fit W[{weight.N},{weight.K}] at rank 16")
+                self.A, self.B = A.detach().to(dev, torch.float32), B.detach().to(dev, torch.float32)
+            else:
+                gen = torch.Generator().manual_seed(seed)
+                bound = 1.0 / math.sqrt(weight.K)          # kaiming_uniform(a=sqrt(5)), PEFT's lora_A init
+                self.A = ((torch.rand(linear.RANK, weight.K, generator=gen) * 2 - 1) * bound).to(dev)
+                self.B = (torch.randn(weight.N, linear.RANK, generator=gen) * b_std).to(dev)
             self.A16 = torch.empty_like(self.A, dtype=torch.float16)
             self.B16 = torch.empty_like(self.B, dtype=torch.float16)
             self.B16t = torch.empty(linear.RANK, weight.N, dtype=torch.float16, device=dev)

@@ -1308,8 +1308,10 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
       const nf4ll_lora* l = segments[i].lora;
       p.seg_begin[i] = at;
       if (l) {
-        if (int rc = lora_down_launch(act, ldact, l->mask, l->ld_mask, l->keep_scale, l->A, 1.0f, M, W->K, segments[i].t_out,
-                                      nullptr, 0, stream)) return rc;
+        // the rank-16 projection of this segment: computed here unless the producer of x already wrote it
+        if (!segments[i].t_ready)
+          if (int rc = lora_down_launch(act, ldact, l->mask, l->ld_mask, l->keep_scale, l->A, 1.0f, M, W->K, segments[i].t_out,
+                                        nullptr, 0, stream)) return rc;
         p.seg_left[i] = static_cast<const float*>(segments[i].t_out);
         p.seg_right[i] = static_cast<const __half*>(l->B) - at * 16;      // indexed by the fused output column
         p.seg_scale[i] = l->scale;

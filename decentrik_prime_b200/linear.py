@@ -171,7 +171,9 @@ def forward(w: Nf4Weight, x, bias=None, lora=None, mask=None, keep_scale=1.0, ou
 def forward_multi(w: Nf4Weight, x, segments, bias=None, out=None, workspace=None):
     """One launch for several projections that share x and are stacked row-wise in `w` (Q|K|V,
     gate|up; the reference's fused W_qkv GEMM, solution/fast_qwen.py:405-413, 947).
-    `segments`: one (rows, lora, mask, keep_scale) per projection, lora as in forward() or None.
+    `segments`: one (rows, lora, mask, keep_scale) per projection, lora as in forward() or None; a fifth element,
+    when given, is the projection's ready-made rank-16 product t fp32 [M,16] (k_norm.rms_forward wrote it while
+    producing x), which the call then reads instead of computing.
     Returns (y [M, sum rows], [t per segment or None])."""
     _check_act(x, w.K, "x")
     M = x.shape[0]
@@ -179,16 +181,22 @@ def forward_multi(w: Nf4Weight, x, segments, bias=None, out=None, workspace=None
     _check_act(y, w.N, "out")
     keep, ts = [], []
     arr = (_lib.Segment * len(segments))()
-    for i, (rows, lora, mask, keep_scale) in enumerate(segments):
+    for i, seg in enumerate(segments):
+        rows, lora, mask, keep_scale = seg[:4]
+        given = seg[4] if len(seg) > 4 else None
         if mask is not None and lora is None:
             raise ValueError("a dropout mask without a LoRA branch has no meaning")
+        if given is not None and (lora is None or given.dtype != torch.float32 or tuple(given.shape) != (M, RANK)
+                                  or not given.is_contiguous()):
+            raise ValueError("a ready-made rank-16 product must be contiguous fp32 [M, 16] and needs its LoRA branch")
         s, ref = _lora_struct(lora, mask, keep_scale)
-        t = torch.empty(M, RANK, dtype=torch.float32, device=x.device) if lora is not None else None
+        t = given if given is not None else (torch.empty(M, RANK, dtype=torch.float32, device=x.device) if lora is not None else None)
         keep.append(s)
         ts.append(t)
         arr[i].rows = int(rows)
         arr[i].lora = ctypes.pointer(s) if s is not None else None
         arr[i].t_out = None if t is None else t.data_ptr()
+        arr[i].t_ready = 1 if given is not None else 0
     h = _lib.lib()
     ws = _workspace(x.device, _workspace_need(M, w.N, w.K, 0)) if workspace is None else workspace
     _lib.check(h.nf4ll_forward_multi(ctypes.byref(w._c), x.data_ptr(), x.stride(0),
@@ -278,6 +286,19 @@ def lora_grads(dy, x, t, u, scale, mask=None, keep_scale=1.0, dA=None, dB=None, 
         _lib.check(h.nf4ll_lora_grads(*args, dA.data_ptr(), None, int(accumulate_a), stream))
         _lib.check(h.nf4ll_lora_grads(*args, None, dB.data_ptr(), int(accumulate_b), stream))
     return dA, dB
+
+
+def lora_u(dy, B16t, scale):
+    """u fp32 [M,16] = scale * dy . B, the rank-16 factor of the LoRA branch's backward (reference
+    solution/fast_qwen.py:1370, 1373 `daq`, `dav`), from the transposed fp16 shadow B16t [16, N]."""
+    M, N = dy.shape
+    _check_act(dy, N, "dy")
+    if B16t.dtype != torch.float16 or tuple(B16t.shape) != (RANK, N) or not B16t.is_contiguous():
+        raise ValueError("lora_B transposed shadow must be contiguous fp16 [16, N]")
+    u = torch.empty(M, RANK, dtype=torch.float32, device=dy.device)
+    _lib.check(_lib.lib().nf4ll_lora_down(dy.data_ptr(), dy.stride(0), None, 0, 1.0, B16t.data_ptr(), 1.0, RANK, M, N,
+                                          u.data_ptr(), None, _lib.current_stream(dy.device)))
+    return u.mul_(scale)
 
 
 class _Nf4LoraLinearFn(torch.autograd.Function):

@@ -35,22 +35,37 @@ def pack_lengths(batch, lo, hi, seed):
 
 
 class DecoderLayerProjections:
-    def __init__(self, hidden, inter, kv, seed, device, lora_on=("q_proj", "v_proj"), bucket=None, bias_qkv=True):
+    def __init__(self, hidden, inter, kv, seed, device, lora_on=("q_proj", "v_proj"), bucket=None, bias_qkv=True, parts=None):
+        """Seeded synthetic weights by default. `parts` (interop.layer_parts of a real model's decoder layer)
+        supplies them instead: {"layer": PackedLayer, "code2", "bias": {name: fp16}, "lora": {name: (A, B, scale)}}."""
         self.hidden, self.inter, self.kv = hidden, inter, kv
         shapes = {"q_proj": (hidden, hidden), "k_proj": (kv, hidden), "v_proj": (kv, hidden), "o_proj": (hidden, hidden),
                   "gate_proj": (inter, hidden), "up_proj": (inter, hidden), "down_proj": (hidden, inter)}
-        linears = {name: quantize.random_nf4_weight(*shapes[name], seed=seed * 16 + i, device=device)
-                   for i, name in enumerate(k_nf4.LAYER_WEIGHTS)}
-        self.layer, self.code2 = k_nf4.repack_layer(linears, torch.device(device))
+        if parts is None:
+            linears = {name: quantize.random_nf4_weight(*shapes[name], seed=seed * 16 + i, device=device)
+                       for i, name in enumerate(k_nf4.LAYER_WEIGHTS)}
+            self.layer, self.code2 = k_nf4.repack_layer(linears, torch.device(device))
+            given_bias, given_lora = None, None
+        else:
+            self.layer, self.code2 = parts["layer"], parts["code2"]
+            for name in k_nf4.LAYER_WEIGHTS:
+                if tuple(self.layer.segments[name][1:]) != shapes[name]:
+                    raise ValueError(f"{name}: {self.layer.segments[name][1:]} does not match the stack's shapes {shapes[name]}")
+            given_bias, given_lora = parts.get("bias", {}), parts.get("lora", {})
+            lora_on = tuple(given_lora)
+            bias_qkv = all(n in given_bias for n in ("q_proj", "k_proj", "v_proj"))
         self.proj = {}
         grad_lo = bucket._at if bucket is not None else 0
         gen = torch.Generator().manual_seed(seed * 16 + 9)
         for i, name in enumerate(k_nf4.LAYER_WEIGHTS):
             w = linear.Nf4Weight.from_layer(self.layer, name, self.code2)
             bias = None
-            if bias_qkv and name in ("q_proj", "k_proj", "v_proj"):      # Qwen2 has biases on q, k, v only
+            if given_bias is not None:
+                bias = given_bias.get(name)
+            elif bias_qkv and name in ("q_proj", "k_proj", "v_proj"):      # Qwen2 has biases on q, k, v only
                 bias = (torch.randn(shapes[name][0], generator=gen) * 0.1).half().to(device)
-            self.proj[name] = blocks.Projection(w, bias=bias, lora=name in lora_on, bucket=bucket, seed=seed * 16 + 10 + i)
+            self.proj[name] = blocks.Projection(w, bias=bias, lora=name in lora_on, bucket=bucket, seed=seed * 16 + 10 + i,
+                                                lora_init=None if given_lora is None else given_lora.get(name))
         # Q|K|V and gate|up lie row after row in the packed layer: one stacked matrix and one launch each
         self.w_qkv = linear.Nf4Weight.from_layer_group(self.layer, ("q_proj", "k_proj", "v_proj"), self.code2)
         self.w_gu = linear.Nf4Weight.from_layer_group(self.layer, ("gate_proj", "up_proj"), self.code2)
@@ -179,7 +194,15 @@ class DecoderLayerProjections:
 class ProjectionStack:
     """n_layers DecoderLayerProjections with one LoRA gradient bucket (all-reduced once per step under DP)."""
 
-    def __init__(self, hidden, inter, kv, n_layers, device, seed=0, lora_on=("q_proj", "v_proj"), distinct_layers=None):
+    def __init__(self, hidden, inter, kv, n_layers, device, seed=0, lora_on=("q_proj", "v_proj"), distinct_layers=None,
+                 layer_parts=None):
+        """`layer_parts`: one interop.layer_parts dict per layer of a real model (the weights are then not
+        synthetic, n_layers = len(layer_parts) and every layer must carry LoRA on the same projections)."""
+        if layer_parts is not None:
+            n_layers, distinct_layers = len(layer_parts), None
+            lora_on = tuple(layer_parts[0].get("lora", {}))
+            if any(tuple(p.get("lora", {})) != lora_on for p in layer_parts):
+                raise ValueError("every layer must carry LoRA on the same projections")
         self.hidden, self.inter, self.kv, self.n_layers, self.lora_on = hidden, inter, kv, n_layers, tuple(lora_on)
         per_layer = sum(blocks.lora_grad_numel(*{"q_proj": (hidden, hidden), "k_proj": (kv, hidden), "v_proj": (kv, hidden),
                                                  "o_proj": (hidden, hidden), "gate_proj": (inter, hidden),
@@ -189,7 +212,8 @@ class ProjectionStack:
         # budget of set-up time); each backward then overwrites the gradients of the layer object it runs on
         n_distinct = n_layers if distinct_layers is None else min(distinct_layers, n_layers)
         self.bucket = blocks.GradBucket(per_layer * n_distinct, device)
-        self._distinct = [DecoderLayerProjections(hidden, inter, kv, seed * 1000 + i, device, self.lora_on, self.bucket)
+        self._distinct = [DecoderLayerProjections(hidden, inter, kv, seed * 1000 + i, device, self.lora_on, self.bucket,
+                                                  parts=None if layer_parts is None else layer_parts[i])
                           for i in range(n_distinct)]
         self.layers = [self._distinct[i % n_distinct] for i in range(n_layers)]
         # saved activations live in the layer objects: a reused object cannot appear twice in one forward pass
@@ -228,3 +252,122 @@ class ProjectionStack:
         for i in reversed(range(self.n_layers)):
             d = backward(i, d, i > 0 or need_input_grad)
         return acts[-1], d
+
+
+class NormedDecoderLayer:
+    """The projections of one decoder layer between REAL fused residual + RMSNorm kernels, driven the way the
+    reference drives its layer loop (solution/fast_qwen.py:1017-1123 forward, 1232-1384 backward): an fp32 residual
+    stream, each norm adding the fp16 output of the GEMM before it (`delta`), norm 1 producing y16 AND the rank-16
+    LoRA products of q and v, one stacked launch for Q|K|V forward and ONE for its backward (the LoRA input
+    gradients are folded into norm 1's backward, as in solution/k_norm.py:64-71), one for gate|up each way.
+    Attention itself (RoPE, softmax) stays the stand-in of DecoderLayerProjections: it is not on this path.
+
+        forward(x32, delta16)  -> (x32', delta16')     with x_next = x32' + delta16'
+        backward(dres32, d16)  -> (dres32', d16')      gradients w.r.t. x_next in, w.r.t. this layer's input out
+    """
+
+    def __init__(self, base: DecoderLayerProjections, eps=1e-6, norm_weights=None, seed=0):
+        from . import k_norm
+        self.k_norm = k_norm
+        self.base, self.eps = base, eps
+        dev = base.layer.flat.device
+        if norm_weights is None:
+            gen = torch.Generator().manual_seed(seed * 16 + 15)
+            norm_weights = tuple((torch.rand(base.hidden, generator=gen) + 0.5).to(dev) for _ in range(2))
+        self.w_in, self.w_post = (w.to(dev, torch.float32).contiguous() for w in norm_weights[:2])
+        P = base.proj
+        if not (P["q_proj"].has_lora and P["v_proj"].has_lora) or any(P[n].has_lora for n in ("k_proj", "o_proj", "gate_proj", "up_proj", "down_proj")):
+            raise ValueError("the normed layer implements the task's adapter: LoRA on q_proj and v_proj only")
+        if not base.fused_groups:
+            raise ValueError("projection widths must be multiples of 128")
+        self._saved = None
+
+    def forward(self, x32, delta16, masks, keep_scale):
+        b, kn, P = self.base, self.k_norm, self.base.proj
+        M, H, KV = x32.shape[0], b.hidden, b.kv
+        dev = x32.device
+        f32 = dict(dtype=torch.float32, device=dev)
+        y1 = torch.empty(M, H, dtype=torch.float16, device=dev)
+        x1 = torch.empty(M, H, **f32) if delta16 is not None else x32
+        rstd1, tq, tv = torch.empty(M, **f32), torch.empty(M, 16, **f32), torch.empty(M, 16, **f32)
+        mq, mv = masks.get("q_proj"), masks.get("v_proj")
+        kn.rms_forward(x32, self.w_in, y1, rstd1, self.eps, delta=delta16, xout=x1 if delta16 is not None else None,
+                       aq=P["q_proj"].A16, av=P["v_proj"].A16, tq=tq, tv=tv, mq=mq, mv=mv, keep_scale=keep_scale)
+        qkv = torch.empty(M, H + 2 * KV, dtype=torch.float16, device=dev)
+        linear.forward_multi(b.w_qkv, y1, [(H, P["q_proj"].lora, mq, keep_scale, tq), (KV, None, None, 1.0),
+                                           (KV, P["v_proj"].lora, mv, keep_scale, tv)], bias=b.bias_qkv, out=qkv)
+        a = qkv[:, :H].clone()                                 # attention stand-in (see DecoderLayerProjections)
+        a[:, :KV] += qkv[:, H:H + KV]
+        a[:, KV:2 * KV] += qkv[:, H + KV:]
+        o, _ = linear.forward(P["o_proj"].w, a)
+        y2 = torch.empty(M, H, dtype=torch.float16, device=dev)
+        x2, rstd2 = torch.empty(M, H, **f32), torch.empty(M, **f32)
+        kn.rms_forward(x1, self.w_post, y2, rstd2, self.eps, delta=o, xout=x2)
+        g, u, h, _, _ = linear.forward_gate_up(b.w_gu, y2)
+        dn, _ = linear.forward(P["down_proj"].w, h)
+        self._saved = (x1, rstd1, y1, tq, tv, mq, mv, keep_scale, a, o, rstd2, g, u, h)
+        return x2, dn
+
+    def backward(self, dres, d16, need_dx=True):
+        """dres fp32 / d16 fp16: gradient w.r.t. x_next = x2 + dn (the fp16 copy feeds the GEMM, as the reference's
+        autocast copy does). Returns the same pair for this layer's input, or (None, None) when need_dx is False
+        (the first layer: only its LoRA gradients are wanted, solution/fast_qwen.py:1363-1364)."""
+        b, kn, P = self.base, self.k_norm, self.base.proj
+        x1, rstd1, y1, tq, tv, mq, mv, ks, a, o, rstd2, g, u, h = self._saved
+        H, KV, M = b.hidden, b.kv, dres.shape[0]
+        dev = dres.device
+        if b._grad_slice is not None:
+            b._grad_slice.zero_()
+        dh, _ = linear.backward_dx(P["down_proj"].w, d16)
+        linear.swiglu_backward(g, u, dh, inplace=True)
+        dy2, _ = linear.backward_dx(b.w_gu, g._base)           # [dg | du] . W_gu in one launch
+        dres2 = torch.empty_like(dres)
+        do16 = torch.empty(M, H, dtype=torch.float16, device=dev)
+        # norm 2's input is x1 + o: recomputed inside the kernel from the two saved tensors
+        kn.rms_backward(dy2, 1.0, x1, self.w_post, rstd2, dres2, dres=dres, out16=do16, delta=o)
+        da, _ = linear.backward_dx(P["o_proj"].w, do16)
+        dqkv = torch.empty(M, H + 2 * KV, dtype=torch.float16, device=dev)
+        dqkv[:, :H] = da
+        dqkv[:, H:H + KV] = da[:, :KV]
+        dqkv[:, H + KV:] = da[:, KV:2 * KV]
+        pq, pv = P["q_proj"], P["v_proj"]
+        uq = linear.lora_u(dqkv[:, :H], pq.B16t, pq.scale)
+        uv = linear.lora_u(dqkv[:, H + KV:], pv.B16t, pv.scale)
+        linear.lora_grads(dqkv[:, :H], y1, tq, uq, pq.scale, mask=mq, keep_scale=ks, dA=pq.dA, dB=pq.dB, accumulate=True)
+        linear.lora_grads(dqkv[:, H + KV:], y1, tv, uv, pv.scale, mask=mv, keep_scale=ks, dA=pv.dA, dB=pv.dB, accumulate=True)
+        self._saved = None
+        if not need_dx:
+            return None, None
+        dy1, _ = linear.backward_dx(b.w_qkv, dqkv)             # base term of q, k and v in one launch, no LoRA branch
+        out = torch.empty_like(dres)
+        out16 = torch.empty(M, H, dtype=torch.float16, device=dev)
+        kn.rms_backward(dy1, 1.0, x1, self.w_in, rstd1, out, dres=dres2, uq=uq, uv=uv, aq=pq.A16, av=pv.A16, mq=mq, mv=mv,
+                        keep_scale=ks, out16=out16)
+        return out, out16
+
+
+class NormedStack:
+    """n_layers NormedDecoderLayers over one LoRA gradient bucket: `run_step` is the whole forward and the
+    hand-written backward of the decoder stack (embedding, attention proper and the LM head are outside the path)."""
+
+    def __init__(self, hidden, inter, kv, n_layers, device, seed=0, eps=1e-6, layer_parts=None):
+        self.stack = ProjectionStack(hidden, inter, kv, n_layers, device, seed=seed, layer_parts=layer_parts)
+        norms = [None] * self.stack.n_layers if layer_parts is None else [p.get("norm") for p in layer_parts]
+        self.layers = [NormedDecoderLayer(l, eps if nw is None else nw[2], nw, seed=seed * 1000 + i)
+                       for i, (l, nw) in enumerate(zip(self.stack.layers, norms))]
+        self.bucket = self.stack.bucket
+
+    def flops(self, M):
+        return self.stack.flops(M)
+
+    def run_step(self, x32, dres, masks_per_layer, keep_scale):
+        """x32 fp32 [M, hidden]: the embedded tokens; dres fp32: the gradient of the loss w.r.t. the stack's output.
+        Returns (output fp32 = residual stream after the last layer, gradient w.r.t. layer 1's input or None)."""
+        x, delta = x32, None
+        for layer, masks in zip(self.layers, masks_per_layer):
+            x, delta = layer.forward(x, delta, masks, keep_scale)
+        out = x + delta.float()
+        d, d16 = dres, dres.half()
+        for i in reversed(range(len(self.layers))):
+            d, d16 = self.layers[i].backward(d, d16, need_dx=i > 0)
+        return out, d

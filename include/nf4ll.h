@@ -127,6 +127,8 @@ typedef struct {
   int64_t rows;             /* output columns (= weight rows) of this projection */
   const nf4ll_lora* lora;   /* its LoRA branch, or NULL */
   void* t_out;              /* fp32 [M,r] = drop(x) . A^T of this projection; required with lora */
+  int32_t t_ready;          /* non-zero: t_out already holds that product (nf4ll_rms_forward wrote it while
+                               producing x): the call reads it instead of computing it */
 } nf4ll_segment;
 int nf4ll_forward_multi(const nf4ll_mat* W, const void* x, int64_t ldx, const void* bias,
                         const nf4ll_segment* segments, int32_t n_segments, int64_t M, void* y, int64_t ldy,
@@ -190,6 +192,33 @@ int nf4ll_lora_grads(const void* dy, int64_t lddy, const void* x, int64_t ldx, c
                      int64_t ld_mask, float keep_scale, const void* t32, const void* u32,
                      float scale, int32_t r, int64_t M, int64_t N, int64_t K,
                      void* dA, void* dB, int32_t accumulate, void* stream);
+
+/* Fused residual add + RMSNorm that PRODUCES the inputs of the projections which follow it:
+ *   xs = x (+ delta16);  rstd = rsqrt(mean(xs^2) + eps);  y = w * (xs * rstd);  y16 = fp16(y)
+ *   t_i = fp16(keep_i ? y * keep_scale_i : 0) . A_i^T      for up to two LoRA branches (q and v), fp32 [M,16]
+ * Replaces the reference's rms_fwd_kernel (solution/k_norm.py:29-53; call sites solution/fast_qwen.py:1021-1027)
+ * and the LoRA-A GEMMs on its dropped-out outputs xq / xv (fast_qwen.py:943-944): those [M,D] copies are never
+ * written; hand t_i to nf4ll_forward_multi through nf4ll_segment.t_out with t_ready = 1.
+ * x fp32 [M,D] (the residual stream), delta16 optional fp16 [M,D] added first, xout optional fp32 [M,D]
+ * receiving xs (may be x itself), w fp32 [D], y16 optional fp16 [M,ldy], rstd fp32 [M].
+ * lora_a / lora_b: NULL or a branch of which A [16,D], mask, ld_mask and keep_scale are read (mask 8-byte
+ * aligned, ld_mask a multiple of 8); t_a / t_b receive the products. D a multiple of 8, at most 4096. */
+int nf4ll_rms_forward(const float* x, const void* delta16, float* xout, const float* w, float eps, int64_t M,
+                      int64_t D, void* y16, int64_t ldy, float* rstd, const nf4ll_lora* lora_a, void* t_a,
+                      const nf4ll_lora* lora_b, void* t_b, void* stream);
+
+/* Backward of that norm with the LoRA branches' input gradients folded in:
+ *   dy = fp16 grad * gscale + sum_i keep_i * keep_scale_i * (u_i . A_i),   u_i fp32 [M,16] = scale_i * d(out_i) . B_i
+ *   dx = rstd * (w*dy - xhat * mean(w*dy*xhat)),  xhat = xs * rstd;   out = dx (+ dres);  out16 = fp16(out)
+ * Replaces rms_bwd_kernel (solution/k_norm.py:56-87) and the GEMMs lqx = daq . A_q, lvx = dav . A_v that feed it
+ * (solution/fast_qwen.py:1376-1380): the rank-16 factors are expanded per element inside the kernel, so the
+ * projections' backward-dX may run without its LoRA branch (one launch for the stacked Q|K|V matrix).
+ * dy16 fp16 [M,lddy]; x, delta16 as in the forward (xs is recomputed); dres optional fp32 [M,D], may alias out;
+ * out fp32 [M,D]; out16 optional fp16 [M,D]. u_a / u_b: the products nf4ll_lora_down gives for lora_B transposed. */
+int nf4ll_rms_backward(const void* dy16, int64_t lddy, float gscale, const float* x, const void* delta16,
+                       const float* w, const float* rstd, const float* dres, float* out, void* out16, int64_t M,
+                       int64_t D, const nf4ll_lora* lora_a, const void* u_a, const nf4ll_lora* lora_b,
+                       const void* u_b, void* stream);
 
 /* SiLU-gated product between the up and down projections, fp32 math on fp16 matrices [M,I]:
  *   h = fp16(silu(g) * u);   backward: du = dh * silu(g), dg = (dh * u) * sig * (1 + g * (1 - sig)).

@@ -88,3 +88,144 @@ def test_stack_flops_per_token():
     assert base_15b == 187_170_816            # 187.17 MFLOP per token per layer
     base_7b = 4 * (3584 * 3584 * 2 + 512 * 3584 * 2 + 18944 * 3584 * 3)
     assert base_7b == 932_184_064             # 932.18 MFLOP per token per layer
+
+
+def test_stack_from_a_quantised_peft_model_and_adapter_save(tmp_path):
+    """interop.model_parts on a bitsandbytes/PEFT-shaped module tree -> ProjectionStack(layer_parts=...) runs the
+    real weights and LoRA factors (one layer against the oracle), and the trained factors leave as a PEFT adapter."""
+    from decentrik_prime_b200 import interop
+    from tests.test_interop import H, KV, I, fake_model
+    dev = torch.device("cuda")
+    parts = interop.model_parts(fake_model(2), dev)
+    st = stack.ProjectionStack(H, I, KV, 0, dev, layer_parts=parts)
+    assert st.n_layers == 2 and st.lora_on == ("q_proj", "v_proj")
+    M = 150
+    gen = torch.Generator().manual_seed(4)
+    x = torch.randn(M, H, generator=gen).half()
+    dy = (torch.randn(M, H, generator=gen) * 0.5).half()
+    ks = 1.0 / float(torch.tensor(0.95, dtype=torch.float32))
+    masks = [{n: (torch.rand(M, H, generator=gen) >= 0.05).to(torch.uint8) for n in ("q_proj", "v_proj")} for _ in range(2)]
+    layer = st.layers[0]
+    out = layer.forward(x.to(dev), {n: m.to(dev) for n, m in masks[0].items()}, ks)
+    dx = layer.backward(dy.to(dev), need_dx=True)
+    linear.check_status()
+    ref_out, ref_dx, ref_grads = oracle_layer(layer, x, dy, masks[0], ks, True)
+    err, rel = nf4_oracle.errors(out, ref_out.float())
+    assert rel <= 2e-3, (err, rel)
+    err, rel = nf4_oracle.errors(dx, ref_dx.float())
+    assert rel <= 3e-3, (err, rel)
+    for n in ("q_proj", "v_proj"):
+        for got, ref in ((layer.proj[n].dA, ref_grads[n][0]), (layer.proj[n].dB, ref_grads[n][1])):
+            err, rel = nf4_oracle.errors(got, ref)
+            assert rel <= 5e-3, (n, err, rel)
+    interop.save_adapter(tmp_path / "adapter", interop.stack_adapter(st))
+    header = interop.adapter_header(tmp_path / "adapter")
+    assert len(header) == 8 and header["base_model.model.model.layers.1.self_attn.q_proj.lora_A.weight"] == ["F32", [16, H]]
+
+
+def _normed_oracle_forward(nl, x32, delta16, masks, ks):
+    """CPU statement of NormedDecoderLayer.forward: norm_oracle for the norms, fp64 products rounded to fp16 where
+    the device stores fp16."""
+    import numpy as np
+    from oracle import norm_oracle
+    b = nl.base
+    H, KV = b.hidden, b.kv
+    W = {n: nf4_oracle.dequant_weight(b.layer, n, b.code2).double() for n in k_nf4.LAYER_WEIGHTS}
+    P = b.proj
+    n1 = norm_oracle.rms_forward_ref(x32.numpy(), nl.w_in.cpu().numpy(), nl.eps, delta=None if delta16 is None else delta16.numpy(),
+                                     mq=masks["q_proj"].numpy(), mv=masks["v_proj"].numpy(), keep_scale=ks)
+    y1 = torch.from_numpy(n1["y16"])
+    cols = []
+    t = {}
+    for n, key in (("q_proj", "xq16"), ("k_proj", None), ("v_proj", "xv16")):
+        y = y1.double() @ W[n].t() + P[n].bias.cpu().double()
+        if key:
+            t[n] = torch.from_numpy(n1[key]).double() @ P[n].A16.cpu().double().t()
+            y = y + P[n].scale * (t[n] @ P[n].B16.cpu().double().t())
+        cols.append(y.half())
+    q, k, v = cols
+    a = q.clone(); a[:, :KV] += k; a[:, KV:2 * KV] += v
+    o = (a.double() @ W["o_proj"].t()).half()
+    x1 = torch.from_numpy(n1["xout"])
+    n2 = norm_oracle.rms_forward_ref(x1.numpy(), nl.w_post.cpu().numpy(), nl.eps, delta=o.numpy())
+    y2 = torch.from_numpy(n2["y16"])
+    g = (y2.double() @ W["gate_proj"].t()).half()
+    u = (y2.double() @ W["up_proj"].t()).half()
+    h = (F.silu(g.float()) * u.float()).half()
+    dn = (h.double() @ W["down_proj"].t()).half()
+    saved = dict(W=W, x1=x1, y1=y1, t=t, a=a, o=o, rstd1=n1["rstd"], rstd2=n2["rstd"], g=g, u=u, h=h, masks=masks, ks=ks)
+    return torch.from_numpy(n2["xout"]), dn, saved
+
+
+def _normed_oracle_backward(nl, s, dres, d16, need_dx):
+    from oracle import norm_oracle
+    b, P, W = nl.base, nl.base.proj, s["W"]
+    H, KV = b.hidden, b.kv
+    dh = (d16.double() @ W["down_proj"]).half()
+    gf, sig = s["g"].float(), torch.sigmoid(s["g"].float())
+    du = (dh.float() * gf * sig).half()
+    dg = ((dh.float() * s["u"].float()) * sig * (1 + gf * (1 - sig))).half()
+    dy2 = (dg.double() @ W["gate_proj"] + du.double() @ W["up_proj"]).half()
+    dres2, do16 = norm_oracle.rms_backward_ref(dy2.numpy(), 1.0, s["x1"].numpy(), nl.w_post.cpu().numpy(), s["rstd2"],
+                                               delta=s["o"].numpy(), dres=dres.numpy())
+    da = (torch.from_numpy(do16).double() @ W["o_proj"]).half()
+    dq, dk, dv = da, da[:, :KV], da[:, KV:2 * KV]
+    grads, lx = {}, {}
+    for n, dyn in (("q_proj", dq), ("v_proj", dv)):
+        p = P[n]
+        u = p.scale * (dyn.double() @ p.B16.cpu().double())
+        xd = nf4_oracle.drop_ref(s["y1"], s["masks"][n], s["ks"]).double()
+        grads[n] = (u.t() @ xd, p.scale * (dyn.double().t() @ s["t"][n]))
+        lx[n] = (u @ p.A16.cpu().double()).numpy()
+    if not need_dx:
+        return None, None, grads
+    dy1 = (dq.double() @ W["q_proj"] + dk.double() @ W["k_proj"] + dv.double() @ W["v_proj"]).half()
+    out, out16 = norm_oracle.rms_backward_ref(dy1.numpy(), 1.0, s["x1"].numpy(), nl.w_in.cpu().numpy(), s["rstd1"], dres=dres2,
+                                              lq=lx["q_proj"], lv=lx["v_proj"], mq=s["masks"]["q_proj"].numpy(),
+                                              mv=s["masks"]["v_proj"].numpy(), keep_scale=s["ks"])
+    return torch.from_numpy(out), torch.from_numpy(out16), grads
+
+
+def test_normed_stack_matches_oracle():
+    """Two decoder layers with the real fused residual + RMSNorm kernels either side of the projections: forward,
+    hand-written backward (stacked Q|K|V and gate|up backward launches, LoRA input gradients folded into the norm
+    backward) and LoRA gradients against the CPU oracle of the same computation."""
+    dev = torch.device("cuda")
+    H, I, KV, M = 256, 512, 128, 150
+    ns = stack.NormedStack(H, I, KV, 2, dev, seed=9)
+    gen = torch.Generator().manual_seed(21)
+    x32 = torch.randn(M, H, generator=gen)
+    dres = torch.randn(M, H, generator=gen) * 0.5
+    ks = 1.0 / float(torch.tensor(0.95, dtype=torch.float32))
+    masks = [{n: (torch.rand(M, H, generator=gen) >= 0.05).to(torch.uint8) for n in ("q_proj", "v_proj")} for _ in range(2)]
+    out, d = ns.run_step(x32.to(dev), dres.to(dev), [{n: m.to(dev) for n, m in ms.items()} for ms in masks], ks)
+    linear.check_status()
+    x, delta, saved = x32, None, []
+    for nl, ms in zip(ns.layers, masks):
+        x, delta, s = _normed_oracle_forward(nl, x, delta, ms, ks)
+        saved.append(s)
+    err, rel = nf4_oracle.errors(out, x + delta.float())
+    assert rel <= 2e-3, (err, rel)
+    g_d, g_16 = dres, dres.half()
+    ref_grads = [None, None]
+    for i in (1, 0):
+        g_d, g_16, ref_grads[i] = _normed_oracle_backward(ns.layers[i], saved[i], g_d, g_16, need_dx=i > 0)
+    assert d is None and g_d is None          # the first layer's d(input) is not computed
+    for i in range(2):
+        for n in ("q_proj", "v_proj"):
+            p = ns.layers[i].base.proj[n]
+            for got, ref in ((p.dA, ref_grads[i][n][0]), (p.dB, ref_grads[i][n][1])):
+                err, rel = nf4_oracle.errors(got, ref)
+                assert rel <= 5e-3, (i, n, err, rel)
+    # the gradient that reaches layer 0 from layer 1, checked through layer 1 alone
+    nl = ns.layers[1]
+    x_in, delta_in = (saved[0]["x1"] * 0 + _normed_oracle_forward(ns.layers[0], x32, None, masks[0], ks)[0],
+                      _normed_oracle_forward(ns.layers[0], x32, None, masks[0], ks)[1])
+    nl.forward(x_in.to(dev), delta_in.to(dev), {n: m.to(dev) for n, m in masks[1].items()}, ks)
+    got, got16 = nl.backward(dres.to(dev), dres.half().to(dev), need_dx=True)
+    linear.check_status()
+    want, want16, _ = _normed_oracle_backward(nl, saved[1], dres, dres.half(), True)
+    err, rel = nf4_oracle.errors(got, want)
+    assert rel <= 3e-3, (err, rel)
+    err, rel = nf4_oracle.errors(got16, want16.float())
+    assert rel <= 3e-3, (err, rel)

@@ -2,8 +2,10 @@
 (tests/golden/make_golden.py ran solution/k_nf4.py:nf4_layer_dequant_kernel under dev/tl_emu.py)."""
 
 import hashlib
+import os
 
 import numpy as np
+import pytest
 import torch
 
 from oracle import nf4_oracle
@@ -68,3 +70,34 @@ def test_quantiser_round_trip_is_close():
     back = nf4_oracle.dequant_weight(layer, "w", code2)
     rel = ((back.float() - w.float()).norm() / w.float().norm()).item()
     assert rel < 0.12, rel
+
+
+# ------------------------------------------------------------------------------------------------
+# RMSNorm producer / backward oracle against the reference's own kernels (run under its emulator)
+# ------------------------------------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def norm_golden():
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "norm_golden.npz"))
+
+
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_norm_oracle_matches_reference_kernels(norm_golden, tag):
+    from oracle import norm_oracle
+    g = {k[2:]: norm_golden[k] for k in norm_golden.files if k.startswith(tag + "_")}
+    ks, eps = float(g["ks"]), float(g["eps"])
+    fwd = norm_oracle.rms_forward_ref(g["x"], g["w"], eps, delta=g["delta"], mq=g["mq"], mv=g["mv"], keep_scale=ks)
+    assert np.array_equal(fwd["xout"], g["xout"])
+    np.testing.assert_allclose(fwd["rstd"], g["rstd"], rtol=3e-7, atol=0)
+    # fp16 outputs: identical up to a last-place flip where the fp32 row sum was added up in another order
+    for name, ref in (("y16", g["y"]), ("xq16", g["xq"]), ("xv16", g["xv"])):
+        diff = np.abs(fwd[name].astype(np.float64) - ref.astype(np.float64))
+        assert (diff <= np.spacing(np.abs(ref)).astype(np.float64)).all(), name
+        assert (diff > 0).mean() < 1e-2, name
+    plain = norm_oracle.rms_forward_ref(g["x"], g["w"], eps)
+    np.testing.assert_allclose(plain["rstd"], g["rstd_nodelta"], rtol=3e-7, atol=0)
+    out, out16 = norm_oracle.rms_backward_ref(g["dy16"], float(g["gscale"][0]), g["x"], g["w"], g["rstd"], delta=g["delta"],
+                                              dres=g["dres"], lq=g["lq"], lv=g["lv"], mq=g["mq"], mv=g["mv"], keep_scale=ks)
+    np.testing.assert_allclose(out, g["bwd_out"], rtol=2e-5, atol=2e-6)
+    assert np.abs(out16.astype(np.float64) - g["bwd_out16"].astype(np.float64)).max() <= 4e-3
+    out, out16 = norm_oracle.rms_backward_ref(g["dy16"], float(g["gscale"][0]), g["xout"], g["w"], g["rstd"])
+    np.testing.assert_allclose(out, g["bwd_plain"], rtol=2e-5, atol=2e-6)
