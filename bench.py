@@ -220,6 +220,7 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        _limit_nccl_ctas()
         dist.init_process_group("nccl", device_id=dev)
     h = _lib.lib()
     M = M_ROWS
@@ -456,6 +457,7 @@ def run_ours(args):
                         "note": "copy_only = the same two copies per step on the same streams with no compute: the host-side "
                                 "ceiling of this loop at this N"},
                 "gpu_launches": (launches_per_step[0] or 0) * args.steps, "gpu_launches_per_step": launches_per_step[0],
+                "nccl_max_ctas": os.environ.get("NCCL_MAX_CTAS") if world > 1 else None,
                 "clocks": clocks}
         line.update(extra)
         if world == 1 and not args.no_stream:
@@ -482,6 +484,16 @@ def run_ours(args):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def _limit_nccl_ctas():
+    """The gradient all-reduce runs on a side stream under the next step's compute. Three of a step's five
+    tensor-core launches are cooperative split-K grids of 144 CTAs (one per SM, 148 SMs): they start only when
+    their whole grid can be resident, i.e. when at most 4 SMs are busy elsewhere. NCCL's default of up to 32 CTAs
+    for a collective would make each of them wait for the all-reduce to finish; four CTAs move the 2 MB bucket
+    slice of a step in far less than a step. Set before the communicator is created; a value from the environment wins."""
+    os.environ.setdefault("NCCL_MAX_CTAS", "4")
+    os.environ.setdefault("NCCL_MIN_CTAS", "1")
 
 
 def config0_numbers(dev):
@@ -629,6 +641,7 @@ def run_stack(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        _limit_nccl_ctas()
         dist.init_process_group("nccl", device_id=dev)
     res = stack_numbers(args.workload, dev, world, rank, args)
     if rank == 0:

@@ -188,23 +188,34 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Every wait on an mbarrier is bounded: after kSpinLimit failed polls (each poll itself suspends
-// for a hardware-chosen interval) the waiter gives up, and the kernel reports it through the
-// status word instead of hanging the GPU. `abort_flag` (shared memory) makes all other waiters of
+// Every wait on an mbarrier is bounded twice over: after kSpinLimit failed polls (each poll itself
+// suspends for a hardware-chosen interval) or after kWaitLimitNs of wall time, whichever comes first,
+// the waiter gives up, and the kernel reports it through the status word instead of hanging the GPU. `abort_flag` (shared memory) makes all other waiters of
 // the CTA give up quickly too.
 // The first polls use the non-blocking test_wait: try_wait costs a few hundred cycles even when the
 // phase is already complete, which is the common case on the MMA issuer's and the decoders'
 // critical paths; try_wait (which lets the hardware park the thread) only takes over for long waits.
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr uint32_t kFastPolls = 32;
+constexpr uint64_t kWaitLimitNs = 1000000000ull;      // and never longer than one second of wall time
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t i = 0; i < kFastPolls; ++i) {
     if (mbar_test_wait(bar, parity)) return true;
   }
+  const uint64_t t0 = global_timer_ns();
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 63u && *abort_flag) return false;
+    if ((i & 63u) == 63u) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) break;     // a failed poll can itself take microseconds
+    }
   }
   *abort_flag = 1;
   return false;

@@ -1197,7 +1197,7 @@ int swap_forward_launch(const nf4ll_mat* W, const void* x, int64_t ldx, const vo
 int64_t swap_workspace_bytes(int64_t N, int64_t K, int64_t M, int sms, int force_slices);
 constexpr int64_t kStreamMaxRows = 16;     // at or below this many token rows the forward is a weight-streaming pass
 constexpr int64_t kStreamCapRows = 64;     // the streaming kernel's own limit (reachable through the tuning hook)
-constexpr int64_t kSwapMaxRows = 128;      // limit of the swapped-operand kernel (weights as the MMA's M operand)
+constexpr int64_t kSwapMaxRows = 64;       // limit of the swapped-operand kernel (weights as the MMA's M operand)
 
 // Which kernel computes a forward of M rows: the 256 x 256 / 128-row tile kernels (kTiles), the register-level
 // weight-streaming kernel for decode-sized batches (kStream), or the swapped-operand tensor-core kernel for

@@ -119,36 +119,43 @@ rms_fwd_kernel(const float* __restrict__ x, const __half* __restrict__ delta, fl
     for (int j = 0; j < 4; ++j) { ca[i][j] = 0.f; cb[i][j] = 0.f; }
 #pragma unroll
   for (int c = 0; c < CPW; ++c) {
-    const int64_t k = (static_cast<int64_t>(c) * kNormWarps + warp) * 32 + t * 8;
-    if (k < D) {
+    const int64_t kc = (static_cast<int64_t>(c) * kNormWarps + warp) * 32;      // first column of the warp's chunk
+    const int64_t k = kc + t * 8;
+    // the MMAs below are warp-wide instructions: the whole warp takes part in a chunk that starts inside the
+    // row, and lanes whose eight columns lie past its end (D need not be a multiple of 32) contribute zeros
+    if (kc < D) {
+      const bool in = k < D;
       float wv[8];
-      load8_f32(w + k, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) wv[j] = 0.f;
+      if (in) load8_f32(w + k, wv);
       uint4 ra = make_uint4(0, 0, 0, 0), rb = ra, sa = ra, sb = ra;
-      if (ba.A) { ra = __ldg(reinterpret_cast<const uint4*>(ba.A + static_cast<int64_t>(g) * D + k));
-                  rb = __ldg(reinterpret_cast<const uint4*>(ba.A + static_cast<int64_t>(g + 8) * D + k)); }
-      if (bb.A) { sa = __ldg(reinterpret_cast<const uint4*>(bb.A + static_cast<int64_t>(g) * D + k));
-                  sb = __ldg(reinterpret_cast<const uint4*>(bb.A + static_cast<int64_t>(g + 8) * D + k)); }
+      if (ba.A && in) { ra = __ldg(reinterpret_cast<const uint4*>(ba.A + static_cast<int64_t>(g) * D + k));
+                        rb = __ldg(reinterpret_cast<const uint4*>(ba.A + static_cast<int64_t>(g + 8) * D + k)); }
+      if (bb.A && in) { sa = __ldg(reinterpret_cast<const uint4*>(bb.A + static_cast<int64_t>(g) * D + k));
+                        sb = __ldg(reinterpret_cast<const uint4*>(bb.A + static_cast<int64_t>(g + 8) * D + k)); }
 #pragma unroll
       for (int i = 0; i < RG; ++i) {
         const float r = s_rstd[g + 8 * i];
+        const bool live = in && ok[i];
         float y[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) y[j] = wv[j] * (xv[c][i][j] * r);
-        if (y16 && ok[i]) *reinterpret_cast<uint4*>(y16 + row[i] * ldy + k) = pack8(y);
+        if (y16 && live) *reinterpret_cast<uint4*>(y16 + row[i] * ldy + k) = pack8(y);
         if (ba.A) {
           float d[8];
-          const uint2 m = (ba.mask && ok[i]) ? __ldg(reinterpret_cast<const uint2*>(ba.mask + row[i] * ba.ld_mask + k)) : make_uint2(0, 0);
+          const uint2 m = (ba.mask && live) ? __ldg(reinterpret_cast<const uint2*>(ba.mask + row[i] * ba.ld_mask + k)) : make_uint2(0, 0);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) d[j] = ok[i] ? (ba.mask ? (keep_bit(m, j) ? y[j] * ba.keep_scale : 0.f) : y[j]) : 0.f;
+          for (int j = 0; j < 8; ++j) d[j] = live ? (ba.mask ? (keep_bit(m, j) ? y[j] * ba.keep_scale : 0.f) : y[j]) : 0.f;
           const uint4 q = pack8(d);
           mma16816(ca[i], ra.x, rb.x, ra.y, rb.y, q.x, q.y);
           mma16816(ca[i], ra.z, rb.z, ra.w, rb.w, q.z, q.w);
         }
         if (bb.A) {
           float d[8];
-          const uint2 m = (bb.mask && ok[i]) ? __ldg(reinterpret_cast<const uint2*>(bb.mask + row[i] * bb.ld_mask + k)) : make_uint2(0, 0);
+          const uint2 m = (bb.mask && live) ? __ldg(reinterpret_cast<const uint2*>(bb.mask + row[i] * bb.ld_mask + k)) : make_uint2(0, 0);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) d[j] = ok[i] ? (bb.mask ? (keep_bit(m, j) ? y[j] * bb.keep_scale : 0.f) : y[j]) : 0.f;
+          for (int j = 0; j < 8; ++j) d[j] = live ? (bb.mask ? (keep_bit(m, j) ? y[j] * bb.keep_scale : 0.f) : y[j]) : 0.f;
           const uint4 q = pack8(d);
           mma16816(cb[i], sa.x, sb.x, sa.y, sb.y, q.x, q.y);
           mma16816(cb[i], sa.z, sb.z, sa.w, sb.w, q.z, q.w);

@@ -1,29 +1,33 @@
-// Short-batch forward (17 .. 128 token rows) with the roles of the operands swapped: the WEIGHTS are the
-// 128-row M operand of tcgen05.mma and the token rows its N operand (16 .. 128 columns), so no MMA row is
-// padding and the kernel's cost is the stream of NF4 bytes, like the decode-sized kernel's. Replaces, for such
-// batches, the same reference call sites as the big-tile kernel (solution/fast_qwen.py:947, 1037, 1080-1112).
+// Short-batch forward (up to 64 token rows) with the roles of the operands swapped: the WEIGHTS are the 128-row
+// M operand of tcgen05.mma and the token rows its N operand (16, 32 or 64 columns), so no MMA row is padding and
+// the kernel's cost is the stream of NF4 bytes, like the decode-sized kernel's. Replaces, for such batches, the
+// same reference call sites as the big-tile kernel (solution/fast_qwen.py:947, 1037, 1080-1112).
 //
 //   y^T[128 weight rows, tokens] = W_tile[128, K-slice] . x^T          (fp32 in tensor memory)
 //
 // The dequantised weights never touch shared memory: a decode thread owns one weight row of the tile (= one
 // tensor-memory lane), turns the 32 bytes of codes of a quantisation block into 64 fp16 values with 32 loads
-// from a lane-replicated 256-entry table of half2 level pairs (one shift, one logic op and one conflict-free
-// 4-byte shared load per two weights), scales them by the block's absmax and writes them with ONE tcgen05.st
-// into the A-operand region of tensor memory; the MMA reads A from tensor memory and the token tile
-// (TMA, 128-byte swizzle) from shared memory. Codes arrive by TMA in boxes of 128 rows x 128 bytes (four
-// blocks per row: whole 128-byte lines per request), three boxes in flight per CTA.
+// from a lane-replicated 256-entry table of half2 level pairs (one byte permute, one multiply-add and one
+// conflict-free 4-byte shared load per two weights), scales them by the block's absmax and writes them with ONE
+// tcgen05.st into the A-operand region of tensor memory; the MMA reads A from tensor memory and the token tile
+// from shared memory.
 //
-// The scale is applied in fp16 (weight = fp16(fp16(NF4[c]) * fp16(absmax))), which differs from the
-// big-tile kernel's bit-exact fp16(NF4[c] * absmax) by a few 2^-11 relative roundings, inside the 1e-3
-// tolerance of the path.
+// One persistent CTA per SM. Codes arrive in coarse stages of four quantisation blocks: a TMA box of 128 rows x
+// 128 bytes (whole 128-byte lines) plus the blocks' absmax values, which two helper warps recover from the 8-bit
+// absmax codes (loaded several stages ahead) and leave in the stage as half2 pairs. EIGHT stages (128 KB of codes)
+// are in flight per SM: at a loaded DRAM latency of ~3 us that is what it takes to keep several TB/s moving.
+// Token tiles (TMA, 128-byte swizzle; they come out of L2) travel in a ring of their own. Sixteen decode warps form four teams (one warp per tensor-memory lane
+// quarter each); block b of the running count belongs to team b % 4 and to A sub-stage b % 8 of tensor memory.
 //
-// A CTA computes one unit = (tile of 128 weight rows) x (slice of the contraction). With more than one
-// slice the units of a tile leave their partial sums in a slab of the workspace and the last one to arrive
-// adds them up in slice order (a fixed order), adds bias and the LoRA term and stores fp16.
+// The scale is applied in fp16 (weight = fp16(fp16(NF4[c]) * fp16(absmax))), which differs from the big-tile
+// kernel's bit-exact fp16(NF4[c] * absmax) by a few 2^-11 relative roundings, inside the 1e-3 tolerance of the path.
 //
-// Warp roles: 0 TMA producer of codes, 1 tensor-memory allocation + MMA issue, 2 TMA producer of token
-// tiles, 3 idle, 4..11 decode (two teams on alternate blocks, one warp per tensor-memory lane quarter) and
-// then the epilogue. Every wait is bounded and reports through the status word.
+// A unit of work = (tile of 128 weight rows) x (slice of the contraction); CTA c takes units c, c + grid, ...
+// With more than one slice the units of a tile leave their partial sums in a slab of the workspace and the last
+// one to arrive adds them up in slice order (a fixed order), adds bias and the LoRA term and stores fp16.
+//
+// Warp roles: 0 TMA producer of codes, 1 tensor-memory allocation + MMA issue, 2-3 absmax helpers, 4..19 decode
+// and then the epilogue, 20 TMA producer of token tiles. Every wait is bounded and reports through the status word.
 #include "nf4ll_gemm_shared.cuh"
 
 namespace nf4ll {
@@ -42,26 +46,31 @@ struct SwapParams {
   float lora_scale;
   int slices;              // slices of the contraction
   int groups_per_slice;    // groups of four quantisation blocks per slice
+  int n_units;             // tiles * slices
   float* slab;             // [tiles][slices][NTOK][128] fp32 partial sums (slices > 1)
   int* counters;           // [tile]: arrivals (zero on entry)
   int32_t* status;
 };
 
-constexpr int kSwapThreads = 384;
-constexpr int kSwapCSt = 3;                  // coarse stages of codes (four blocks x 128 rows x 32 bytes each)
+constexpr int kSwapThreads = 672;            // code producer, MMA issuer, two absmax helper warps, 16 decode warps, token-tile producer
+constexpr int kSwapTeams = 4;
+constexpr int kSwapDecodeWarps = 4 * kSwapTeams;
+constexpr int kSwapCSt = 8;                  // coarse stages in flight: codes of four blocks (16 KB) + their absmax (2 KB)
+constexpr int kSwapASt = 8;                  // A sub-stages in tensor memory (32 columns each)
 constexpr int kSwapCodeBytes = 128 * 128;
 constexpr int kSwapTableBytes = 256 * 128;
 
 template <int NTOK>
 struct SwapCfg {
-  // sub-stages of the A operand in tensor memory (32 columns each) and of the token tiles in shared memory;
-  // three at 64 tokens so that two CTAs fit one SM's shared memory
-  static constexpr int kASt = NTOK == 64 ? 3 : 4;
   static constexpr int kXBytes = NTOK * 128;                       // one token tile: NTOK rows x 64 fp16
+  static constexpr int kXSt = NTOK == 64 ? 6 : 8;                  // token tiles in flight (they come from L2)
+  static constexpr int kAbsOff = kSwapCodeBytes;                   // absmax of the stage: [128 rows][4 blocks] half2 pairs
+  static constexpr int kStageBytes = kSwapCodeBytes + 128 * 16;
   static constexpr int kDCols = NTOK < 32 ? 32 : NTOK;             // accumulator columns
-  static constexpr int kTmemCols = 256;                            // accumulator + 4 x 32 A columns, as a power of two
-  static constexpr int kSmemBytes = 1024 + kSwapCSt * kSwapCodeBytes + kASt * kXBytes + kSwapTableBytes + 1024 + 256;
-  static_assert(kDCols + kASt * 32 <= kTmemCols, "tensor memory budget");
+  static constexpr int kTmemCols = 512;                            // accumulator + 8 x 32 A columns, as a power of two
+  static constexpr int kSmemBytes = 1024 + kSwapCSt * kStageBytes + kXSt * kXBytes + kSwapTableBytes + 1024 + 512;
+  static_assert(kDCols + kSwapASt * 32 <= kTmemCols, "tensor memory budget");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
 
 // D[tmem] (+)= A[tmem] . B[smem]: the A operand (128 rows x 16 fp16, two per 32-bit column) comes from tensor memory
@@ -105,54 +114,77 @@ __device__ __forceinline__ void swap_decode8(uint32_t w, uint32_t lane_base, uin
   }
 }
 
+// 32 lanes x 16 consecutive fp32 columns
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+
 template <int NTOK>
-__global__ void __launch_bounds__(kSwapThreads, NTOK <= 64 ? 2 : 1)
+__global__ void __launch_bounds__(kSwapThreads, 1)
 nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_nib, const SwapParams p) {
   using Cfg = SwapCfg<NTOK>;
-  constexpr int kSwapASt = Cfg::kASt;
   // x, the weights and code2 may be read at once (what precedes this kernel on the stream is the rank-16
   // projection kernel, itself started only after all earlier work had finished, or a memset, which orders this
   // kernel after everything before it); the first write to global memory waits for the predecessor.
   pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sNib = smem;                                         // [kSwapCSt][128 rows][128 B], 128-byte swizzle
-  uint8_t* sX = sNib + kSwapCSt * kSwapCodeBytes;               // [kSwapASt][NTOK rows][128 B], 128-byte swizzle
-  uint32_t* sTbl = reinterpret_cast<uint32_t*>(sX + kSwapASt * Cfg::kXBytes);
+  uint8_t* sStage = smem;                        // [kSwapCSt] { codes [128 rows][128 B] (128-byte swizzle) | absmax [128 rows][4] half2 }
+  uint8_t* sX = sStage + kSwapCSt * Cfg::kStageBytes;           // [kXSt] token tiles [NTOK rows][128 B], 128-byte swizzle
+  uint32_t* sTbl = reinterpret_cast<uint32_t*>(sX + Cfg::kXSt * Cfg::kXBytes);
   float* sCode2 = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sTbl) + kSwapTableBytes);
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sCode2) + 1024);
-  uint64_t* a_full = bars;                       // [kSwapASt] token tile landed + the team's four warps stored their A rows
-  uint64_t* a_empty = a_full + 4;                // [kSwapASt] the MMAs that read the sub-stage have completed
-  uint64_t* nib_full = a_empty + 4;              // [kSwapCSt] codes landed
-  uint64_t* nib_empty = nib_full + kSwapCSt;     // [kSwapCSt] all eight decode warps have read their blocks
-  uint64_t* acc_full = nib_empty + kSwapCSt;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* a_full = bars;                       // [kSwapASt] the team's four warps stored their rows of the A operand
+  uint64_t* a_empty = a_full + kSwapASt;         // [kSwapASt] the MMAs that read the sub-stage have completed
+  uint64_t* grp_full = a_empty + kSwapASt;       // [kSwapCSt] codes landed and absmax written
+  uint64_t* grp_empty = grp_full + kSwapCSt;     // [kSwapCSt] sixteen decode warps have read their codes
+  uint64_t* x_full = grp_empty + kSwapCSt;       // [kXSt] token tile landed
+  uint64_t* x_empty = x_full + 8;                // [kXSt] the MMAs that read the token tile have completed
+  uint64_t* acc_full = x_empty + 8;
+  uint64_t* acc_empty = acc_full + 1;            // the epilogue has read the accumulator (sixteen decode warps)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* last_flag = abort_flag + 1;
+  volatile int* stop_flag = abort_flag + 2;
   uint32_t* sLv = tmem_slot + 4;                 // 16 level bit patterns
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x / p.slices, sl = blockIdx.x - tile * p.slices;
-  const int64_t n0 = static_cast<int64_t>(tile) * 128;
   const int bpr = static_cast<int>(p.K / 64);
-  const int blk_begin = sl * p.groups_per_slice * 4;
-  int blk_end = blk_begin + p.groups_per_slice * 4;
-  if (blk_end > bpr) blk_end = bpr;
-  const int nblk = blk_end - blk_begin;              // > 0 by construction of the slices
   const Abort ab{abort_flag, p.status};
+  // unit u -> (tile, first block, number of blocks); every role walks the same sequence u = blockIdx.x, + gridDim.x, ...
+  auto unit_range = [&](int u, int& tile, int& sl, int& blk_begin, int& nblk) {
+    tile = u / p.slices;
+    sl = u - tile * p.slices;
+    blk_begin = sl * p.groups_per_slice * 4;
+    int blk_end = blk_begin + p.groups_per_slice * 4;
+    if (blk_end > bpr) blk_end = bpr;
+    nblk = blk_end - blk_begin;                 // > 0 by construction of the slices
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSwapASt; ++s) {
-      mbar_init(smem_u32(a_full + s), 1 + 4);
+      mbar_init(smem_u32(a_full + s), 4);
       mbar_init(smem_u32(a_empty + s), 1);
     }
     for (int s = 0; s < kSwapCSt; ++s) {
-      mbar_init(smem_u32(nib_full + s), 1);
-      mbar_init(smem_u32(nib_empty + s), 8);
+      mbar_init(smem_u32(grp_full + s), 1 + 2);        // TMA bytes + the two absmax helper warps
+      mbar_init(smem_u32(grp_empty + s), kSwapDecodeWarps);
+    }
+    for (int s = 0; s < Cfg::kXSt; ++s) {
+      mbar_init(smem_u32(x_full + s), 1);
+      mbar_init(smem_u32(x_empty + s), 1);
     }
     mbar_init(smem_u32(acc_full), 1);
+    mbar_init(smem_u32(acc_empty), kSwapDecodeWarps);
     *abort_flag = 0;
     *last_flag = 0;
+    *stop_flag = 0;
     mbar_fence_init();
   }
   if (threadIdx.x < 16) {
@@ -180,186 +212,296 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
   constexpr uint32_t kACol0 = Cfg::kDCols;
 
   if (warp == 0) {
-    // ----------------------------------------------------------------------------- codes
+    // ----------------------------------------------------------------------------- TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tmap_nib);
-      const int ngrp = (nblk + 3) / 4;
-      int issued = 0;
-      for (int gidx = 0; gidx < ngrp; ++gidx, ++issued) {
-        const int c = gidx % kSwapCSt;
-        if (!wait_or_abort(smem_u32(nib_empty + c), ((gidx / kSwapCSt) & 1) ^ 1, ab, 0x0502)) break;
-        mbar_arrive_expect_tx(smem_u32(nib_full + c), kSwapCodeBytes);
-        tma_load_2d(smem_u32(sNib + c * kSwapCodeBytes), &tmap_nib, (blk_begin + gidx * 4) * 32, static_cast<int>(n0),
-                    smem_u32(nib_full + c));
+      int cg = 0;                                   // coarse stages issued so far, over all units
+      bool ok = true;
+      for (int u = blockIdx.x; ok && u < p.n_units; u += gridDim.x) {
+        int tile, sl, blk_begin, nblk;
+        unit_range(u, tile, sl, blk_begin, nblk);
+        const int ngrp = (nblk + 3) / 4;
+        for (int gidx = 0; gidx < ngrp; ++gidx, ++cg) {
+          const int c = cg % kSwapCSt;
+          if (!wait_or_abort(smem_u32(grp_empty + c), ((cg / kSwapCSt) & 1) ^ 1, ab, 0x0502)) { ok = false; break; }
+          mbar_arrive_expect_tx(smem_u32(grp_full + c), kSwapCodeBytes);
+          tma_load_2d(smem_u32(sStage + c * Cfg::kStageBytes), &tmap_nib, (blk_begin + gidx * 4) * 32, tile * 128, smem_u32(grp_full + c));
+        }
       }
       if (*abort_flag) {
-        for (int gidx = (issued > kSwapCSt ? issued - kSwapCSt : 0); gidx < issued; ++gidx)
-          for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(smem_u32(nib_full + gidx % kSwapCSt), (gidx / kSwapCSt) & 1); ++spin) {}
+        // give copies still in flight a bounded chance to land before the CTA goes away
+        for (int k = (cg > kSwapCSt ? cg - kSwapCSt : 0); k < cg; ++k)
+          for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(smem_u32(grp_full + k % kSwapCSt), (k / kSwapCSt) & 1); ++spin) {}
       }
-    }
-  } else if (warp == 2) {
-    // ----------------------------------------------------------------------------- token tiles
-    if (lane == 0) {
-      tma_prefetch_desc(&tmap_x);
-      int issued = 0;
-      for (int i = 0; i < nblk; ++i, ++issued) {
-        const int sa = i % kSwapASt;
-        if (!wait_or_abort(smem_u32(a_empty + sa), ((i / kSwapASt) & 1) ^ 1, ab, 0x0501)) break;
-        mbar_arrive_expect_tx(smem_u32(a_full + sa), Cfg::kXBytes);
-        tma_load_2d(smem_u32(sX + sa * Cfg::kXBytes), &tmap_x, (blk_begin + i) * 64, 0, smem_u32(a_full + sa));
-      }
-      (void)issued;
     }
   } else if (warp == 1) {
     // ----------------------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_f16(128, NTOK, 0, 0);
       bool ok = true;
-      for (int i = 0; ok && i < nblk; ++i) {
-        const int sa = i % kSwapASt;
-        if (!wait_or_abort(smem_u32(a_full + sa), (i / kSwapASt) & 1, ab, 0x0503)) { ok = false; break; }
+      int bg = 0, ul = 0;
+      for (int u = blockIdx.x; ok && u < p.n_units; u += gridDim.x, ++ul) {
+        int tile, sl, blk_begin, nblk;
+        unit_range(u, tile, sl, blk_begin, nblk);
+        // the accumulator is free once the previous unit's epilogue has read it
+        if (!wait_or_abort(smem_u32(acc_empty), (ul & 1) ^ 1, ab, 0x0507)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t x_base = smem_u32(sX + sa * Cfg::kXBytes);
+        for (int i = 0; i < nblk; ++i, ++bg) {
+          const int sa = bg % kSwapASt, xs = bg % Cfg::kXSt;
+          if (!wait_or_abort(smem_u32(x_full + xs), (bg / Cfg::kXSt) & 1, ab, 0x0508)) { ok = false; break; }
+          if (!wait_or_abort(smem_u32(a_full + sa), (bg / kSwapASt) & 1, ab, 0x0503)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t x0 = smem_u32(sX + xs * Cfg::kXBytes);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          const uint64_t bdesc = make_smem_desc(x_base + kk * 32, 16, 1024, kSwizzle128B);
-          tc_mma_f16_ts(tmem_base, tmem_base + kACol0 + sa * 32 + kk * 8, bdesc, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t bdesc = make_smem_desc(x0 + kk * 32, 16, 1024, kSwizzle128B);
+            tc_mma_f16_ts(tmem_base, tmem_base + kACol0 + sa * 32 + kk * 8, bdesc, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(smem_u32(a_empty + sa));
+          tc_commit(smem_u32(x_empty + xs));
         }
-        tc_commit(smem_u32(a_empty + sa));
+        if (ok) tc_commit(smem_u32(acc_full));
       }
-      tc_commit(smem_u32(acc_full));
       if (!ok) {
-        for (int spin = 0; spin < (1 << 18) && !mbar_try_wait(smem_u32(acc_full), 0); ++spin) {}
+        // make sure nothing is still running on the tensor core before tensor memory is freed
+        tc_commit(smem_u32(acc_full));
+        for (int spin = 0; spin < (1 << 18) && !mbar_try_wait(smem_u32(acc_full), ul & 1); ++spin) {}
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp == 20) {
+    // ----------------------------------------------------------------------------- token tiles
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_x);
+      int bg = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; ok && u < p.n_units; u += gridDim.x) {
+        int tile, sl, blk_begin, nblk;
+        unit_range(u, tile, sl, blk_begin, nblk);
+        for (int i = 0; i < nblk; ++i, ++bg) {
+          const int xs = bg % Cfg::kXSt;
+          if (!wait_or_abort(smem_u32(x_empty + xs), ((bg / Cfg::kXSt) & 1) ^ 1, ab, 0x0501)) { ok = false; break; }
+          mbar_arrive_expect_tx(smem_u32(x_full + xs), Cfg::kXBytes);
+          tma_load_2d(smem_u32(sX + xs * Cfg::kXBytes), &tmap_x, (blk_begin + i) * 64, 0, smem_u32(x_full + xs));
+        }
+      }
+    }
+  } else if (warp < 4) {
+    // ----------------------------------------------------------------------------- absmax helpers
+    // thread h owns tile rows h and h + 64: absmax[b] = code2[qabs[b]] * scale2 + offset2 (rounded separately) of
+    // the stage's four blocks, rounded to fp16 and stored as (a, a) pairs. The four absmax codes of a group are
+    // one 32-bit word per row; the words of the next four groups are in flight while these four are processed.
+    const int h = threadIdx.x - 64;
+    int cg = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; ok && u < p.n_units; u += gridDim.x) {
+      int tile, sl, blk_begin, nblk;
+      unit_range(u, tile, sl, blk_begin, nblk);
+      const int ngrp = (nblk + 3) / 4;
+      int64_t qr[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        int64_t n = static_cast<int64_t>(tile) * 128 + h + 64 * e;
+        if (n >= p.N) n = p.N - 1;                 // tail rows: any valid row; their output is never stored
+        qr[e] = n * bpr + blk_begin;
+      }
+      auto load_word = [&](int e, int grp) -> uint32_t {
+        // absmax codes of blocks 4 grp .. 4 grp + 3 of row e (bytes past the slice's last block read as 0)
+        if (grp >= ngrp) return 0u;
+        const uint8_t* src = p.qabs + qr[e] + grp * 4;
+        const int nb = (nblk - grp * 4 < 4) ? nblk - grp * 4 : 4;
+        if (nb == 4 && (reinterpret_cast<uintptr_t>(src) & 3) == 0) return __ldg(reinterpret_cast<const uint32_t*>(src));
+        uint32_t w = 0;
+        for (int j = 0; j < nb; ++j) w |= static_cast<uint32_t>(__ldg(src + j)) << (8 * j);
+        return w;
+      };
+      uint32_t cur[4][2], nxt[4][2];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) cur[i][e] = load_word(e, i);
+      for (int g0 = 0; ok && g0 < ngrp; g0 += 4) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) nxt[i][e] = load_word(e, g0 + 4 + i);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int grp = g0 + i;
+          if (grp >= ngrp) break;
+          const int c = cg % kSwapCSt;
+          if (!wait_or_abort(smem_u32(grp_empty + c), ((cg / kSwapCSt) & 1) ^ 1, ab, 0x0509)) { ok = false; break; }
+          uint8_t* dst = sStage + c * Cfg::kStageBytes + Cfg::kAbsOff;
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int64_t b = qr[e] + grp * 4;
+            uint32_t out[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int64_t bj = b + j;
+              const float am = block_absmax(sCode2[(cur[i][e] >> (8 * j)) & 0xffu], __ldg(p.scale2 + (bj >> 8)), __ldg(p.offset2 + (bj >> 8)));
+              const __half2 a2 = __float2half2_rn(am);
+              out[j] = *reinterpret_cast<const uint32_t*>(&a2);
+            }
+            *reinterpret_cast<uint4*>(dst + (h + 64 * e) * 16) = make_uint4(out[0], out[1], out[2], out[3]);
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(grp_full + c));
+          ++cg;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) cur[i][e] = nxt[i][e];
+      }
+    }
+  } else {
     // ----------------------------------------------------------------------------- decode, then epilogue
     const int q = warp & 3;                       // tensor-memory lane quarter
-    const int team = (warp - 4) >> 2;             // blocks of this parity
+    const int team = (warp - 4) >> 2;             // blocks b of the running count with b % 4 == team
     const int r = q * 32 + lane;                  // weight row inside the tile = tensor-memory lane
-    const int64_t n = n0 + r;
-    const bool row_ok = n < p.N;
-    const int64_t qrow = (row_ok ? n : p.N - 1) * bpr + blk_begin;
     const uint32_t lane_base = smem_u32(sTbl) + lane * 4;
-    const uint32_t nib_row = smem_u32(sNib) + r * 128;
+    const uint32_t row_off = r * 128;
     const int key = r & 7;
     const uint32_t tA = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + kACol0;
-    bool ok = true;
-
-    auto absmax_of = [&](int i) -> float {
-      const int64_t b = qrow + i;
-      return block_absmax(sCode2[__ldg(p.qabs + b)], __ldg(p.scale2 + (b >> 8)), __ldg(p.offset2 + (b >> 8)));
-    };
-    float am_next = (team < nblk) ? absmax_of(team) : 0.f;
-    for (int i = team; ok && i < nblk; i += 2) {
-      const int gidx = i >> 2, j = i & 3, c = gidx % kSwapCSt;
-      const float am = am_next;
-      if (i + 2 < nblk) am_next = absmax_of(i + 2);                     // travels during this block's decode
-      if (!wait_or_abort(smem_u32(nib_full + c), (gidx / kSwapCSt) & 1, ab, 0x0504)) { ok = false; break; }
-      const uint32_t src = nib_row + c * kSwapCodeBytes;
-      const uint4 c0 = lds128(src + (((2 * j) ^ key) << 4));
-      const uint4 c1 = lds128(src + (((2 * j + 1) ^ key) << 4));
-      if (j >= 2 || i + 2 >= nblk) {               // this warp's last block of the coarse stage
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(nib_empty + c));
-      }
-      const int sa = i % kSwapASt;
-      if (!wait_or_abort(smem_u32(a_empty + sa), ((i / kSwapASt) & 1) ^ 1, ab, 0x0505)) { ok = false; break; }
-      const __half2 a2 = __float2half2_rn(am);
-      const uint32_t am2 = *reinterpret_cast<const uint32_t*>(&a2);
-      uint32_t v[32];
-      swap_decode8(c0.x, lane_base, am2, v + 0);  swap_decode8(c0.y, lane_base, am2, v + 4);
-      swap_decode8(c0.z, lane_base, am2, v + 8);  swap_decode8(c0.w, lane_base, am2, v + 12);
-      swap_decode8(c1.x, lane_base, am2, v + 16); swap_decode8(c1.y, lane_base, am2, v + 20);
-      swap_decode8(c1.z, lane_base, am2, v + 24); swap_decode8(c1.w, lane_base, am2, v + 28);
-      __syncwarp();
-      tmem_st32(tA + sa * 32, v);
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(a_full + sa));
-    }
-    // a warp that left the loop early (failed wait) still owes nothing: every other waiter sees the abort flag
-
-    // --- epilogue: lane = weight row, columns = tokens
-    if (ok) ok = wait_or_abort(smem_u32(acc_full), 0, ab, 0x0506);
-    pdl_wait();                                 // T and the cleared counters come from the kernel before this one
-    constexpr int kChunks = Cfg::kDCols / 32;
     const bool direct = p.slices == 1;
-    float bias = 0.f, bs[16];
-    auto load_row_terms = [&]() {
-      if (p.bias && row_ok) bias = __half2float(p.bias[n]);
-      if (p.t32 && row_ok) {
-        float tmp[8];
-        const uint4* bp = reinterpret_cast<const uint4*>(p.lora_b + n * 16);
-        unpack8(__ldg(bp), tmp);
-#pragma unroll
-        for (int jj = 0; jj < 8; ++jj) bs[jj] = tmp[jj] * p.lora_scale;
-        unpack8(__ldg(bp + 1), tmp);
-#pragma unroll
-        for (int jj = 0; jj < 8; ++jj) bs[8 + jj] = tmp[jj] * p.lora_scale;
-      }
-    };
-    auto finish = [&](int tok, float v) {
-      // bias, LoRA term, one rounding; 32 lanes store 32 consecutive output columns of one token row
-      if (p.t32) {
-        const float4* tr = reinterpret_cast<const float4*>(p.t32 + static_cast<int64_t>(tok) * 16);
-        float l = 0.f;
-#pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-          const float4 tv = __ldcg(tr + j4);
-          l = fmaf(tv.x, bs[4 * j4], l); l = fmaf(tv.y, bs[4 * j4 + 1], l);
-          l = fmaf(tv.z, bs[4 * j4 + 2], l); l = fmaf(tv.w, bs[4 * j4 + 3], l);
+    bool ok = true;
+    int bg = 0, cg = 0, ul = 0;
+
+    for (int u = blockIdx.x; u < p.n_units; u += gridDim.x, ++ul) {
+      int tile, sl, blk_begin, nblk;
+      unit_range(u, tile, sl, blk_begin, nblk);
+      const int64_t n = static_cast<int64_t>(tile) * 128 + r;
+      const bool row_ok = n < p.N;
+      const int ngrp = (nblk + 3) / 4;
+      for (int grp = 0; grp < ngrp; ++grp, ++cg) {
+        const int c = cg % kSwapCSt;
+        const int nb = (nblk - grp * 4 < 4) ? nblk - grp * 4 : 4;
+        // this warp's block of the group (at most one: four consecutive blocks, four teams)
+        const int j = (team - (bg + grp * 4)) & 3;
+        const bool mine = j < nb;
+        if (ok && !wait_or_abort(smem_u32(grp_full + c), (cg / kSwapCSt) & 1, ab, 0x0504)) ok = false;
+        if (ok && mine) {
+          const int gi = bg + grp * 4 + j;
+          const uint32_t src = smem_u32(sStage + c * Cfg::kStageBytes) + row_off;
+          const uint4 c0 = lds128(src + (((2 * j) ^ key) << 4));
+          const uint4 c1 = lds128(src + (((2 * j + 1) ^ key) << 4));
+          const uint32_t am2 = lds_u32s(smem_u32(sStage + c * Cfg::kStageBytes) + Cfg::kAbsOff + r * 16 + j * 4);
+          const int sa = gi % kSwapASt;
+          if (!wait_or_abort(smem_u32(a_empty + sa), ((gi / kSwapASt) & 1) ^ 1, ab, 0x0505)) ok = false;
+          if (ok) {
+            uint32_t v[32];
+            swap_decode8(c0.x, lane_base, am2, v + 0);  swap_decode8(c0.y, lane_base, am2, v + 4);
+            swap_decode8(c0.z, lane_base, am2, v + 8);  swap_decode8(c0.w, lane_base, am2, v + 12);
+            swap_decode8(c1.x, lane_base, am2, v + 16); swap_decode8(c1.y, lane_base, am2, v + 20);
+            swap_decode8(c1.z, lane_base, am2, v + 24); swap_decode8(c1.w, lane_base, am2, v + 28);
+            __syncwarp();
+            tmem_st32(tA + sa * 32, v);
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(a_full + sa));
+          }
         }
-        v += l;
-      }
-      p.y[static_cast<int64_t>(tok) * p.ldy + n] = __float2half_rn(v + bias);
-    };
-    if (ok) {
-      tc_fence_after();
-      if (direct) load_row_terms();
-      for (int ch = team; ch < kChunks; ch += 2) {
-        uint32_t v[32];
+        // every decode warp hands the coarse stage back exactly once, after its last read of it
         __syncwarp();
-        tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ch * 32, v);
-        tmem_ld_wait();
-        if (direct) {
-          if (row_ok) {
+        if (ok && lane == 0) mbar_arrive(smem_u32(grp_empty + c));
+      }
+      bg += nblk;
+
+      // --- epilogue of the unit: lane = weight row, columns = tokens; team t takes token columns 16 t .. 16 t + 15
+      if (ok) ok = wait_or_abort(smem_u32(acc_full), ul & 1, ab, 0x0506);
+      pdl_wait();                                 // T and the cleared counters come from the kernel before this one
+      float bias = 0.f, bs[16];
+      auto load_row_terms = [&]() {
+        if (p.bias && row_ok) bias = __half2float(p.bias[n]);
+        if (p.t32 && row_ok) {
+          float tmp[8];
+          const uint4* bp = reinterpret_cast<const uint4*>(p.lora_b + n * 16);
+          unpack8(__ldg(bp), tmp);
 #pragma unroll
-            for (int jt = 0; jt < 32; ++jt) {
-              const int tok = ch * 32 + jt;
-              if (tok < p.M) finish(tok, __uint_as_float(v[jt]));
+          for (int jj = 0; jj < 8; ++jj) bs[jj] = tmp[jj] * p.lora_scale;
+          unpack8(__ldg(bp + 1), tmp);
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj) bs[8 + jj] = tmp[jj] * p.lora_scale;
+        }
+      };
+      auto finish = [&](int tok, float v) {
+        // bias, LoRA term, one rounding; 32 lanes store 32 consecutive output columns of one token row
+        if (p.t32) {
+          const float4* tr = reinterpret_cast<const float4*>(p.t32 + static_cast<int64_t>(tok) * 16);
+          float l = 0.f;
+#pragma unroll
+          for (int j4 = 0; j4 < 4; ++j4) {
+            const float4 tv = __ldcg(tr + j4);
+            l = fmaf(tv.x, bs[4 * j4], l); l = fmaf(tv.y, bs[4 * j4 + 1], l);
+            l = fmaf(tv.z, bs[4 * j4 + 2], l); l = fmaf(tv.w, bs[4 * j4 + 3], l);
+          }
+          v += l;
+        }
+        p.y[static_cast<int64_t>(tok) * p.ldy + n] = __float2half_rn(v + bias);
+      };
+      const bool has_cols = team * 16 < NTOK;
+      if (ok) {
+        tc_fence_after();
+        uint32_t v[16];
+        if (has_cols) {
+          if (direct) load_row_terms();
+          __syncwarp();
+          tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + team * 16, v);
+          tmem_ld_wait();
+        }
+        // the accumulator is in registers: the next unit's MMAs may overwrite it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(acc_empty));
+        if (has_cols) {
+          if (direct) {
+            if (row_ok) {
+#pragma unroll
+              for (int jt = 0; jt < 16; ++jt) {
+                const int tok = team * 16 + jt;
+                if (tok < p.M) finish(tok, __uint_as_float(v[jt]));
+              }
+            }
+          } else {
+            float* mine = p.slab + ((static_cast<int64_t>(tile) * p.slices + sl) * NTOK) * 128 + r;
+#pragma unroll
+            for (int jt = 0; jt < 16; ++jt) {
+              const int tok = team * 16 + jt;
+              if (tok < p.M) mine[static_cast<int64_t>(tok) * 128] = __uint_as_float(v[jt]);
             }
           }
-        } else {
-          float* mine = p.slab + ((static_cast<int64_t>(tile) * p.slices + sl) * NTOK) * 128 + r;
-#pragma unroll
-          for (int jt = 0; jt < 32; ++jt) {
-            const int tok = ch * 32 + jt;
-            if (tok < p.M) mine[static_cast<int64_t>(tok) * 128] = __uint_as_float(v[jt]);
+        }
+      } else {
+        // a failed wait: still release the MMA issuer, which may be waiting for the accumulator to be read
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(acc_empty));
+      }
+      if (!direct) {
+        // the unit of a tile that arrives last adds the partial sums up in slice order
+        __threadfence();
+        named_barrier(1, kSwapDecodeWarps * 32);
+        if (threadIdx.x == 128) {
+          const int prev = atomicAdd(p.counters + tile, 1);
+          *last_flag = (prev == p.slices - 1) ? 1 : 0;
+          *stop_flag = *abort_flag;               // sampled once per unit, so that all decode warps leave together
+          __threadfence();
+        }
+        named_barrier(1, kSwapDecodeWarps * 32);
+        if (*last_flag && !*stop_flag) {
+          load_row_terms();
+          const float* all = p.slab + (static_cast<int64_t>(tile) * p.slices * NTOK) * 128 + r;
+          const int tok_end = static_cast<int>(p.M < NTOK ? p.M : NTOK);
+          for (int tok = team; tok < tok_end; tok += kSwapTeams) {
+            float v = 0.f;
+            for (int s2 = 0; s2 < p.slices; ++s2) v += __ldcg(all + (static_cast<int64_t>(s2) * NTOK + tok) * 128);
+            if (row_ok) finish(tok, v);
           }
         }
-      }
-    }
-    if (!direct) {
-      // the unit of a tile that arrives last adds the partial sums up in slice order
-      __threadfence();
-      named_barrier(1, 256);
-      if (threadIdx.x == 128) {
-        const int prev = atomicAdd(p.counters + tile, 1);
-        if (prev == p.slices - 1) *last_flag = 1;
-        __threadfence();
-      }
-      named_barrier(1, 256);
-      if (*last_flag && !*abort_flag) {
-        load_row_terms();
-        const float* all = p.slab + (static_cast<int64_t>(tile) * p.slices * NTOK) * 128 + r;
-        const int tok_end = static_cast<int>(p.M < NTOK ? p.M : NTOK);
-        for (int tok = team; tok < tok_end; tok += 2) {
-          float v = 0.f;
-          for (int s2 = 0; s2 < p.slices; ++s2) v += __ldcg(all + (static_cast<int64_t>(s2) * NTOK + tok) * 128);
-          if (row_ok) finish(tok, v);
-        }
+        named_barrier(1, kSwapDecodeWarps * 32);  // last_flag is rewritten by the next unit
+        if (*stop_flag) break;
+      } else if (*abort_flag) {
+        break;                                    // no barriers between the decode warps in this mode: each may leave on its own
       }
     }
   }
@@ -407,29 +549,37 @@ static int swap_encode(CUtensorMap* map, CUtensorMapDataType type, const void* b
   return NF4LL_OK;
 }
 
-static int swap_ntok(int64_t M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
+static int swap_ntok(int64_t M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 64); }
 
-// Slices of the contraction for W[N,K]: enough units (tiles x slices) for a few CTAs per SM, in whole groups of
-// four quantisation blocks, at least two groups per slice.
-void swap_plan(int64_t N, int64_t K, int sms, int force_slices, int* slices, int* groups_per_slice) {
+// Slices of the contraction for W[N,K] at `ntok` token columns. The persistent grid has one CTA per SM: the
+// slice count is the one that minimises rounds x (work of a unit + a fixed cost per unit)
+// + the traffic of the partial-sum slab, in whole groups of four quantisation blocks.
+void swap_plan(int64_t N, int64_t K, int ntok, int sms, int force_slices, int* slices, int* groups_per_slice) {
   const int groups = static_cast<int>((K / 64 + 3) / 4);
   const int64_t tiles = (N + 127) / 128;
-  int s = 1;
-  const int64_t want = static_cast<int64_t>(sms) * 4;
-  if (tiles < want) s = static_cast<int>((want + tiles - 1) / tiles);
-  int max_s = groups / 2;
-  if (max_s < 1) max_s = 1;
-  if (s > max_s) s = max_s;
-  if (force_slices > 0) s = force_slices;
-  if (s > groups) s = groups;
-  const int per = (groups + s - 1) / s;
+  const int64_t grid = sms;
+  int best = 1;
+  double best_cost = 1e30;
+  for (int s = 1; s <= groups && s <= 32; ++s) {
+    const int per = (groups + s - 1) / s;
+    if ((groups + per - 1) / per != s) continue;            // not a distinct split
+    const int64_t units = tiles * s;
+    const int64_t rounds = (units + grid - 1) / grid;
+    // in units of "one group of four blocks of one tile": a unit costs its groups plus about one group of fixed
+    // overhead (pipeline fill, epilogue); a slab element costs 8 bytes of traffic against 2114 bytes per tile-group
+    const double slab = s > 1 ? static_cast<double>(units) * ntok * 128 * 8 / (128.0 * 256 * 0.516) / static_cast<double>(grid) : 0.0;
+    const double cost = static_cast<double>(rounds) * (per + 1.0) + slab;
+    if (cost < best_cost) { best_cost = cost; best = s; }
+  }
+  if (force_slices > 0) best = force_slices > groups ? groups : force_slices;
+  const int per = (groups + best - 1) / best;
   *slices = (groups + per - 1) / per;
   *groups_per_slice = per;
 }
 
 int64_t swap_workspace_bytes(int64_t N, int64_t K, int64_t M, int sms, int force_slices) {
   int s = 1, per = 0;
-  swap_plan(N, K, sms, force_slices, &s, &per);
+  swap_plan(N, K, swap_ntok(M), sms, force_slices, &s, &per);
   const int64_t tiles = (N + 127) / 128;
   const int64_t counters = (tiles * 4 + 255) / 256 * 256;
   const int64_t slab = s > 1 ? tiles * s * swap_ntok(M) * 128 * 4 : 0;
@@ -461,24 +611,26 @@ int swap_forward_launch(const nf4ll_mat* W, const void* x, int64_t ldx, const vo
   p.bias = static_cast<const __half*>(bias);
   p.t32 = t32; p.lora_b = static_cast<const __half*>(lora_b); p.lora_scale = lora_scale;
   p.status = status;
-  swap_plan(W->N, W->K, sms, force_slices, &p.slices, &p.groups_per_slice);
+  const int ntok = swap_ntok(M);
+  swap_plan(W->N, W->K, ntok, sms, force_slices, &p.slices, &p.groups_per_slice);
   const int64_t tiles = (W->N + 127) / 128;
+  p.n_units = static_cast<int>(tiles * p.slices);
   const int64_t counter_bytes = (tiles * 4 + 255) / 256 * 256;
   p.counters = static_cast<int*>(scratch);
   p.slab = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + counter_bytes);
   if (p.slices > 1 && !counters_zeroed) NF4LL_CUDA(cudaMemsetAsync(p.counters, 0, tiles * 4, stream));
-  const int ntok = swap_ntok(M);
   CUtensorMap mx, mn;
   if (int rc = swap_encode(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x, static_cast<uint64_t>(W->K), static_cast<uint64_t>(M),
                            static_cast<uint64_t>(ldx) * 2, 64, static_cast<uint32_t>(ntok), "token tile")) return rc;
   if (int rc = swap_encode(&mn, CU_TENSOR_MAP_DATA_TYPE_UINT8, W->nib, static_cast<uint64_t>(W->K / 2), static_cast<uint64_t>(W->N),
                            static_cast<uint64_t>(W->K / 2), 128, 128, "codes")) return rc;
-  const unsigned grid = static_cast<unsigned>(tiles * p.slices);
+  int64_t ctas = sms;
+  if (ctas > p.n_units) ctas = p.n_units;
+  const unsigned grid = static_cast<unsigned>(ctas);
   switch (ntok) {
     case 16: return swap_launch_cfg<16>(mx, mn, p, grid, stream);
     case 32: return swap_launch_cfg<32>(mx, mn, p, grid, stream);
-    case 64: return swap_launch_cfg<64>(mx, mn, p, grid, stream);
-    default: return swap_launch_cfg<128>(mx, mn, p, grid, stream);
+    default: return swap_launch_cfg<64>(mx, mn, p, grid, stream);
   }
 }
 

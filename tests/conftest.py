@@ -10,6 +10,10 @@ if ROOT not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA GPU (B200, sm_100a); run with -m gpu")
+    # the CPU oracles are small: a few threads are plenty, and on a host whose cores are shared with other jobs a
+    # thread per visible core makes every CPU tensor operation crawl
+    import torch
+    torch.set_num_threads(max(1, min(torch.get_num_threads(), 8)))
 
 
 def pytest_collection_modifyitems(config, items):
