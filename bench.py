@@ -231,6 +231,11 @@ def run_ours(args):
     bucket = blocks.GradBucket(N_WEIGHT_SETS * blocks.MlpBlock.grad_numel(HIDDEN, INTER), dev)
     layers = [blocks.MlpBlock(HIDDEN, INTER, seed=100 + i, device=dev, lora=True, bucket=bucket) for i in range(N_WEIGHT_SETS)]
     per_layer = blocks.MlpBlock.grad_numel(HIDDEN, INTER)
+    if not args.no_grad_stream:
+        # the dA/dB kernels of a backward run on a side stream beside the dX GEMMs (forked and joined inside the step)
+        grad_stream = torch.cuda.Stream(dev)
+        for blk in layers:
+            blk.use_grad_stream(grad_stream)
     gen = torch.Generator().manual_seed(1234 + rank)       # every rank has its own rows
     # x and dy of a step lie back to back in one pinned buffer: one host-to-device copy per step
     host_in = [torch.randn(2, M, HIDDEN, generator=gen).half().pin_memory() for _ in range(N_INPUT_SETS)]
@@ -435,6 +440,7 @@ def run_ours(args):
                 "launch": ("cuda graphs: one captured step per weight set, replayed; every ninth timed step "
                            "of the value loop issued eagerly with event hooks") if not args.no_graphs
                 else "eager: every launch issued from python",
+                "grad_stream": not args.no_grad_stream,
                 "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                              "frac": (achieved / peak) if achieved else None,
                              "peak_source": pk["source"] + (" burst bf16 (timed region under 1 s)" if burst
@@ -763,6 +769,7 @@ def main():
     ap.add_argument("--no-stream", action="store_true", help="skip the small-batch weight-stream numbers")
     ap.add_argument("--no-extras", action="store_true", help="skip benchmark configurations 0, 2 and 3")
     ap.add_argument("--no-graphs", action="store_true", help="issue every step from Python instead of replaying CUDA graphs")
+    ap.add_argument("--no-grad-stream", action="store_true", help="issue the LoRA gradient kernels on the step's own stream instead of a side stream")
     ap.add_argument("--profile-leg", default="step", choices=("step", "stream"),
                     help="which leg cudaProfilerStart/Stop brackets (for `ncu --profile-from-start off`): the timed "
                          "steps, or the small-batch weight-stream measurements")

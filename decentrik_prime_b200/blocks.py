@@ -99,8 +99,12 @@ class Projection:
             self._saved = (x, mask if self.has_lora else None, keep_scale, t)
         return y
 
-    def backward(self, dy, out=None, accumulate=False, need_dx=True, accumulate_grads=False):
-        """dx (optionally accumulated into `out`) and, with LoRA, dA/dB into this projection's views."""
+    def backward(self, dy, out=None, accumulate=False, need_dx=True, accumulate_grads=False, grad_stream=None, pending=None):
+        """dx (optionally accumulated into `out`) and, with LoRA, dA/dB into this projection's views.
+        `grad_stream`: issue the dA/dB kernel there (after everything queued so far on the current stream), so
+        that it runs beside the GEMMs that follow: nothing downstream of it in the backward reads dA/dB. The
+        caller joins the stream again before the gradients are used and keeps `pending` (the tensors the side
+        kernel reads) alive until then."""
         x, mask, keep_scale, t = self._saved
         dx = None
         u = None
@@ -116,8 +120,16 @@ class Projection:
                                                   _lib.current_stream(dy.device)))
             u.mul_(self.scale)
         if self.has_lora:
-            linear.lora_grads(dy, x, t, u, self.scale, mask=mask, keep_scale=keep_scale, dA=self.dA, dB=self.dB,
-                              accumulate=accumulate_grads)
+            if grad_stream is None:
+                linear.lora_grads(dy, x, t, u, self.scale, mask=mask, keep_scale=keep_scale, dA=self.dA, dB=self.dB,
+                                  accumulate=accumulate_grads)
+            else:
+                grad_stream.wait_stream(torch.cuda.current_stream(dy.device))
+                with torch.cuda.stream(grad_stream):
+                    linear.lora_grads(dy, x, t, u, self.scale, mask=mask, keep_scale=keep_scale, dA=self.dA, dB=self.dB,
+                                      accumulate=accumulate_grads)
+                if pending is not None:
+                    pending.extend((dy, x, t, u, mask))
         self._saved = None
         return dx
 
@@ -159,6 +171,15 @@ class MlpBlock:
         # with a bucket the block's gradients are one contiguous slice: cleared by one fill per backward
         self._grad_slice = bucket.flat[grad_lo:bucket._at] if (bucket is not None and lora) else None
         self._saved = None
+        self.grad_stream = None
+        self._pending = []
+
+    def use_grad_stream(self, stream=None):
+        """Run the three dA/dB kernels of a backward on a side stream, beside the dX GEMMs (they are bound by
+        HBM latency, the GEMMs by the tensor and shared-memory pipes); `backward` joins the stream before it
+        returns. Works eagerly and under CUDA-graph capture (the fork and the join are captured as edges)."""
+        self.grad_stream = stream if stream is not None else torch.cuda.Stream(self.gate.w.device)
+        return self
 
     @staticmethod
     def grad_numel(hidden, inter):
@@ -190,7 +211,8 @@ class MlpBlock:
         if self._grad_slice is not None and not accumulate_grads:
             self._grad_slice.zero_()
             accumulate_grads = True
-        dh = self.down.backward(dy, accumulate_grads=accumulate_grads)
+        gs, pend = self.grad_stream, self._pending
+        dh = self.down.backward(dy, accumulate_grads=accumulate_grads, grad_stream=gs, pending=pend)
         if self.fused_glue:
             dg, du = linear.swiglu_backward(g, u, dh, inplace=True)
         else:
@@ -199,10 +221,14 @@ class MlpBlock:
             dhf = dh.float()
             du = (dhf * gf * sig).half()
             dg = (dhf * u.float() * sig * (1.0 + gf * (1.0 - sig))).half()
-        dx = self.gate.backward(dg, out=out, need_dx=need_dx, accumulate_grads=accumulate_grads)
+        dx = self.gate.backward(dg, out=out, need_dx=need_dx, accumulate_grads=accumulate_grads, grad_stream=gs, pending=pend)
         # d(input) of gate and up are summed into one buffer: the second launch adds its fp32 result to the
         # fp16 values the first one stored and rounds again (two roundings, like the reference's fp16 add,
         # solution/fast_qwen.py:1320-1323)
-        dx = self.up.backward(du, out=dx, accumulate=need_dx, need_dx=need_dx, accumulate_grads=accumulate_grads)
+        dx = self.up.backward(du, out=dx, accumulate=need_dx, need_dx=need_dx, accumulate_grads=accumulate_grads,
+                              grad_stream=gs, pending=pend)
+        if gs is not None:
+            torch.cuda.current_stream(dy.device).wait_stream(gs)
+            pend.clear()
         self._saved = None
         return dx

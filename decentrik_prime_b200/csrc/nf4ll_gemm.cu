@@ -1198,17 +1198,21 @@ int64_t swap_workspace_bytes(int64_t N, int64_t K, int64_t M, int sms, int force
 constexpr int64_t kStreamMaxRows = 16;     // at or below this many token rows the forward is a weight-streaming pass
 constexpr int64_t kStreamCapRows = 64;     // the streaming kernel's own limit (reachable through the tuning hook)
 constexpr int64_t kSwapMaxRows = 64;       // limit of the swapped-operand kernel (weights as the MMA's M operand)
+constexpr int64_t kSwapMinRows = 33;       // measured on B200: from here up, and for weights of at least
+constexpr int64_t kSwapMinWeights = int64_t(1) << 26;      // this many elements, it beats the 128-row tiles (by 4-13 %)
 
 // Which kernel computes a forward of M rows: the 256 x 256 / 128-row tile kernels (kTiles), the register-level
 // weight-streaming kernel for decode-sized batches (kStream), or the swapped-operand tensor-core kernel for
-// short batches (kSwap). Bits 1 and 2 of the tuning flags force kStream / kSwap up to that kernel's limit.
+// short batches of 33 to 64 rows against a large weight (kSwap). Bits 1 and 2 of the tuning flags force kStream /
+// kSwap up to that kernel's limit.
 enum : int { kTiles = 0, kStream = 1, kSwap = 2 };
-static int forward_kind(int mode, int64_t M, bool stacked, const Tune& tune) {
+static int forward_kind(int mode, int64_t M, int64_t N, int64_t K, bool stacked, const Tune& tune) {
   if (mode != kFwd || stacked) return kTiles;
   if (tune.flags & 2) return M <= kStreamCapRows ? kStream : kTiles;
   if (tune.flags & 4) return M <= kSwapMaxRows ? kSwap : kTiles;
   if (tune.any()) return kTiles;
   if (M <= kStreamMaxRows) return kStream;
+  if (M >= kSwapMinRows && M <= kSwapMaxRows && N * K >= kSwapMinWeights) return kSwap;
   return kTiles;
 }
 
@@ -1255,7 +1259,7 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
   Tune tune = g_tune;
   if (segments && (narrow_tiles || tune.bn == 512)) tune.bn = narrow_tiles ? 128 : 256;
   Plan pl = make_plan(mode, M, NO, KC, lora ? lora->r : 0, sms, tune);
-  const int kind = forward_kind(mode, M, segments != nullptr, tune);
+  const int kind = forward_kind(mode, M, W->N, W->K, segments != nullptr, tune);
   const int force_slices = (tune.flags & 6) ? tune.splits : 0;
   const int64_t need = kind != kTiles ? pl.left_bytes + pl.bt_bytes + small_batch_scratch(kind, W->N, W->K, M, sms, force_slices)
                                       : pl.total();

@@ -12,12 +12,22 @@
 // tcgen05.st into the A-operand region of tensor memory; the MMA reads A from tensor memory and the token tile
 // from shared memory.
 //
-// One persistent CTA per SM. Codes arrive in coarse stages of four quantisation blocks: a TMA box of 128 rows x
-// 128 bytes (whole 128-byte lines) plus the blocks' absmax values, which two helper warps recover from the 8-bit
-// absmax codes (loaded several stages ahead) and leave in the stage as half2 pairs. EIGHT stages (128 KB of codes)
-// are in flight per SM: at a loaded DRAM latency of ~3 us that is what it takes to keep several TB/s moving.
-// Token tiles (TMA, 128-byte swizzle; they come out of L2) travel in a ring of their own. Sixteen decode warps form four teams (one warp per tensor-memory lane
-// quarter each); block b of the running count belongs to team b % 4 and to A sub-stage b % 8 of tensor memory.
+// One persistent CTA per SM. Codes arrive in coarse stages of four quantisation blocks (one "group", K = 256): a
+// TMA box of 128 rows x 128 bytes (whole 128-byte lines) plus the 8-bit absmax codes of those blocks (4 bytes
+// per row, copied by the producer warp's 32 lanes with cp.async so that they travel with the codes and cost no
+// thread a DRAM round trip). Five to eight stages are in flight per SM. Token tiles (TMA, 128-byte swizzle; they
+// come out of L2) travel in a ring of their own, one group (four tiles) per slot.
+//
+// Sixteen decode warps form four teams (one warp per tensor-memory lane quarter each). A team takes a HALF group
+// (two blocks, K = 128, 64 columns of A operand) at a time, the half groups going round the teams, so that four
+// half groups are being decoded at once and each team's chain of latencies (wait, shared loads, table loads,
+// tcgen05.st, fence, arrive) overlaps the others'. Tensor memory holds three groups of A operand.
+// The MMA issuer is ONE thread, and what it does per group is kept to one wait, up to sixteen MMAs whose
+// descriptors differ by immediates, and one commit: a group's A operand and its token tiles share one "full"
+// barrier (eight warp arrivals + the TMA bytes) and one "empty" barrier (the commit), three groups deep.
+// Measured on B200: an MMA of 128 x N x 16 takes about 64 clocks for every N <= 128 (72 with A in tensor memory)
+// and a commit costs the issuing thread about as much as two MMAs, so sixteen MMAs per group bound the kernel at
+// about 28 weights per clock per SM.
 //
 // The scale is applied in fp16 (weight = fp16(fp16(NF4[c]) * fp16(absmax))), which differs from the big-tile
 // kernel's bit-exact fp16(NF4[c] * absmax) by a few 2^-11 relative roundings, inside the 1e-3 tolerance of the path.
@@ -26,8 +36,9 @@
 // With more than one slice the units of a tile leave their partial sums in a slab of the workspace and the last
 // one to arrive adds them up in slice order (a fixed order), adds bias and the LoRA term and stores fp16.
 //
-// Warp roles: 0 TMA producer of codes, 1 tensor-memory allocation + MMA issue, 2-3 absmax helpers, 4..19 decode
-// and then the epilogue, 20 TMA producer of token tiles. Every wait is bounded and reports through the status word.
+// Warp roles: 0 producer of codes (TMA) and absmax codes (cp.async), 1 tensor-memory allocation + MMA issue,
+// 2 TMA producer of token tiles, 3..18 decode and then the epilogue. Every wait is bounded and reports through
+// the status word.
 #include "nf4ll_gemm_shared.cuh"
 
 namespace nf4ll {
@@ -52,26 +63,43 @@ struct SwapParams {
   int32_t* status;
 };
 
-constexpr int kSwapThreads = 672;            // code producer, MMA issuer, two absmax helper warps, 16 decode warps, token-tile producer
+constexpr int kSwapThreads = 608;            // code producer, MMA issuer, token-tile producer, 16 decode warps
 constexpr int kSwapTeams = 4;
 constexpr int kSwapDecodeWarps = 4 * kSwapTeams;
-constexpr int kSwapCSt = 8;                  // coarse stages in flight: codes of four blocks (16 KB) + their absmax (2 KB)
-constexpr int kSwapASt = 8;                  // A sub-stages in tensor memory (32 columns each)
+constexpr int kSwapFirstDecodeWarp = 3;
+constexpr int kSwapAGrp = 3;                 // groups of A operand in tensor memory (128 columns each) = groups of token tiles in flight
 constexpr int kSwapCodeBytes = 128 * 128;
 constexpr int kSwapTableBytes = 256 * 128;
 
 template <int NTOK>
 struct SwapCfg {
   static constexpr int kXBytes = NTOK * 128;                       // one token tile: NTOK rows x 64 fp16
-  static constexpr int kXSt = NTOK == 64 ? 6 : 8;                  // token tiles in flight (they come from L2)
-  static constexpr int kAbsOff = kSwapCodeBytes;                   // absmax of the stage: [128 rows][4 blocks] half2 pairs
-  static constexpr int kStageBytes = kSwapCodeBytes + 128 * 16;
-  static constexpr int kDCols = NTOK < 32 ? 32 : NTOK;             // accumulator columns
-  static constexpr int kTmemCols = 512;                            // accumulator + 8 x 32 A columns, as a power of two
-  static constexpr int kSmemBytes = 1024 + kSwapCSt * kStageBytes + kXSt * kXBytes + kSwapTableBytes + 1024 + 512;
-  static_assert(kDCols + kSwapASt * 32 <= kTmemCols, "tensor memory budget");
+  static constexpr int kXGBytes = 4 * kXBytes;                     // the four token tiles of a group
+  static constexpr int kXG = kSwapAGrp;                            // groups of token tiles in flight (they come from L2)
+  static constexpr int kCSt = NTOK == 64 ? 5 : (NTOK == 32 ? 6 : 8);   // coarse stages in flight: codes of four blocks (16 KB) + their absmax codes
+  static constexpr int kAbsOff = kSwapCodeBytes;                   // absmax codes of the stage: [128 rows][4 blocks] bytes
+  static constexpr int kStageBytes = kSwapCodeBytes + 1024;        // kept a multiple of 1024 for the swizzled codes
+  static constexpr int kDCols = 64;                                // accumulator columns reserved
+  static constexpr int kTmemCols = 512;                            // accumulator + 3 x 128 A columns, as a power of two
+  static constexpr int kSmemBytes = 1024 + kCSt * kStageBytes + kXG * kXGBytes + kSwapTableBytes + 1024 + 512;
+  static_assert(kDCols + kSwapAGrp * 128 <= kTmemCols, "tensor memory budget");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
+
+// 4-byte asynchronous copy global -> shared, and the arrive that fires on `bar` once all copies this
+// thread has issued so far have landed (it counts as one of the barrier's expected arrivals)
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+// a wait for the one thread that issues the MMAs: polls without the slow path's bookkeeping until the limit
+__device__ __forceinline__ bool swap_wait(uint32_t bar, uint32_t parity, const Abort& ab, int code) {
+  for (uint32_t i = 0; i < 4096u; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return wait_or_abort(bar, parity, ab, code);
+}
 
 // D[tmem] (+)= A[tmem] . B[smem]: the A operand (128 rows x 16 fp16, two per 32-bit column) comes from tensor memory
 __device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
@@ -135,18 +163,17 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
   pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sStage = smem;                        // [kSwapCSt] { codes [128 rows][128 B] (128-byte swizzle) | absmax [128 rows][4] half2 }
-  uint8_t* sX = sStage + kSwapCSt * Cfg::kStageBytes;           // [kXSt] token tiles [NTOK rows][128 B], 128-byte swizzle
-  uint32_t* sTbl = reinterpret_cast<uint32_t*>(sX + Cfg::kXSt * Cfg::kXBytes);
+  constexpr int kCSt = Cfg::kCSt;
+  uint8_t* sStage = smem;                        // [kCSt] { codes [128 rows][128 B] (128-byte swizzle) | absmax codes [128 rows][4] }
+  uint8_t* sX = sStage + kCSt * Cfg::kStageBytes;               // [kXG][4] token tiles [NTOK rows][128 B], 128-byte swizzle
+  uint32_t* sTbl = reinterpret_cast<uint32_t*>(sX + Cfg::kXG * Cfg::kXGBytes);
   float* sCode2 = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sTbl) + kSwapTableBytes);
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sCode2) + 1024);
-  uint64_t* a_full = bars;                       // [kSwapASt] the team's four warps stored their rows of the A operand
-  uint64_t* a_empty = a_full + kSwapASt;         // [kSwapASt] the MMAs that read the sub-stage have completed
-  uint64_t* grp_full = a_empty + kSwapASt;       // [kSwapCSt] codes landed and absmax written
-  uint64_t* grp_empty = grp_full + kSwapCSt;     // [kSwapCSt] sixteen decode warps have read their codes
-  uint64_t* x_full = grp_empty + kSwapCSt;       // [kXSt] token tile landed
-  uint64_t* x_empty = x_full + 8;                // [kXSt] the MMAs that read the token tile have completed
-  uint64_t* acc_full = x_empty + 8;
+  uint64_t* a_full = bars;                       // [kSwapAGrp] eight decode warps stored the group's A operand and its token tiles landed
+  uint64_t* a_empty = a_full + 8;                // [kSwapAGrp] the MMAs that read the group (A operand and token tiles) have completed
+  uint64_t* grp_full = a_empty + 8;              // [kCSt] codes and absmax codes landed
+  uint64_t* grp_empty = grp_full + 8;            // [kCSt] the eight decode warps of the group's two half groups have read it
+  uint64_t* acc_full = grp_empty + 8;
   uint64_t* acc_empty = acc_full + 1;            // the epilogue has read the accumulator (sixteen decode warps)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -168,17 +195,13 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
   };
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kSwapASt; ++s) {
-      mbar_init(smem_u32(a_full + s), 4);
+    for (int s = 0; s < kSwapAGrp; ++s) {
+      mbar_init(smem_u32(a_full + s), 8 + 1);          // the warps of the group's two half groups + the token tiles' TMA bytes
       mbar_init(smem_u32(a_empty + s), 1);
     }
-    for (int s = 0; s < kSwapCSt; ++s) {
-      mbar_init(smem_u32(grp_full + s), 1 + 2);        // TMA bytes + the two absmax helper warps
-      mbar_init(smem_u32(grp_empty + s), kSwapDecodeWarps);
-    }
-    for (int s = 0; s < Cfg::kXSt; ++s) {
-      mbar_init(smem_u32(x_full + s), 1);
-      mbar_init(smem_u32(x_empty + s), 1);
+    for (int s = 0; s < kCSt; ++s) {
+      mbar_init(smem_u32(grp_full + s), 1 + 32);       // TMA bytes + the producer warp's 32 lanes (their absmax-code copies)
+      mbar_init(smem_u32(grp_empty + s), 8);
     }
     mbar_init(smem_u32(acc_full), 1);
     mbar_init(smem_u32(acc_empty), kSwapDecodeWarps);
@@ -212,53 +235,87 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
   constexpr uint32_t kACol0 = Cfg::kDCols;
 
   if (warp == 0) {
-    // ----------------------------------------------------------------------------- TMA producer
-    if (lane == 0) {
-      tma_prefetch_desc(&tmap_nib);
-      int cg = 0;                                   // coarse stages issued so far, over all units
-      bool ok = true;
-      for (int u = blockIdx.x; ok && u < p.n_units; u += gridDim.x) {
-        int tile, sl, blk_begin, nblk;
-        unit_range(u, tile, sl, blk_begin, nblk);
-        const int ngrp = (nblk + 3) / 4;
-        for (int gidx = 0; gidx < ngrp; ++gidx, ++cg) {
-          const int c = cg % kSwapCSt;
-          if (!wait_or_abort(smem_u32(grp_empty + c), ((cg / kSwapCSt) & 1) ^ 1, ab, 0x0502)) { ok = false; break; }
+    // ----------------------------------------------------------------------------- producer of codes and absmax codes
+    // All 32 lanes walk the groups together: lane 0 issues the TMA box of the codes, every lane copies the
+    // 4 absmax codes (one 32-bit word) of tile rows lane, lane + 32, lane + 64, lane + 96. A group's word of a row
+    // is 4-byte aligned when the row length in blocks is a multiple of four; otherwise, and for a last group of
+    // fewer than four blocks (its word would run past the row, for the last row past the array), the bytes are
+    // fetched one by one.
+    if (lane == 0) tma_prefetch_desc(&tmap_nib);
+    const bool words_ok = (bpr & 3) == 0;
+    int cg = 0;                                   // coarse stages issued so far, over all units
+    bool ok = true;
+    for (int u = blockIdx.x; ok && u < p.n_units; u += gridDim.x) {
+      int tile, sl, blk_begin, nblk;
+      unit_range(u, tile, sl, blk_begin, nblk);
+      const int ngrp = (nblk + 3) / 4;
+      int64_t qrow[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        int64_t n = static_cast<int64_t>(tile) * 128 + lane + 32 * e;
+        if (n >= p.N) n = p.N - 1;                 // tail rows: any valid row; their output is never stored
+        qrow[e] = n * bpr + blk_begin;
+      }
+      for (int gidx = 0; gidx < ngrp; ++gidx, ++cg) {
+        const int c = cg % kCSt;
+        if (!wait_or_abort(smem_u32(grp_empty + c), ((cg / kCSt) & 1) ^ 1, ab, 0x0502)) { ok = false; break; }
+        const uint32_t stage = smem_u32(sStage + c * Cfg::kStageBytes);
+        const int nb = (nblk - gidx * 4 < 4) ? nblk - gidx * 4 : 4;
+        if (lane == 0) {
           mbar_arrive_expect_tx(smem_u32(grp_full + c), kSwapCodeBytes);
-          tma_load_2d(smem_u32(sStage + c * Cfg::kStageBytes), &tmap_nib, (blk_begin + gidx * 4) * 32, tile * 128, smem_u32(grp_full + c));
+          tma_load_2d(stage, &tmap_nib, (blk_begin + gidx * 4) * 32, tile * 128, smem_u32(grp_full + c));
+        }
+        if (words_ok && nb == 4) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) cp_async4(stage + Cfg::kAbsOff + (lane + 32 * e) * 4, p.qabs + qrow[e] + gidx * 4);
+          cp_async_arrive(smem_u32(grp_full + c));
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            uint32_t w = 0;
+            for (int j = 0; j < nb; ++j) w |= static_cast<uint32_t>(__ldg(p.qabs + qrow[e] + gidx * 4 + j)) << (8 * j);
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(stage + Cfg::kAbsOff + (lane + 32 * e) * 4), "r"(w) : "memory");
+          }
+          mbar_arrive(smem_u32(grp_full + c));
         }
       }
-      if (*abort_flag) {
-        // give copies still in flight a bounded chance to land before the CTA goes away
-        for (int k = (cg > kSwapCSt ? cg - kSwapCSt : 0); k < cg; ++k)
-          for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(smem_u32(grp_full + k % kSwapCSt), (k / kSwapCSt) & 1); ++spin) {}
-      }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    if (lane == 0 && *abort_flag) {
+      // give copies still in flight a bounded chance to land before the CTA goes away
+      for (int k = (cg > kCSt ? cg - kCSt : 0); k < cg; ++k)
+        for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(smem_u32(grp_full + k % kCSt), (k / kCSt) & 1); ++spin) {}
     }
   } else if (warp == 1) {
     // ----------------------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_f16(128, NTOK, 0, 0);
       bool ok = true;
-      int bg = 0, ul = 0;
+      int cg = 0, ul = 0;
       for (int u = blockIdx.x; ok && u < p.n_units; u += gridDim.x, ++ul) {
         int tile, sl, blk_begin, nblk;
         unit_range(u, tile, sl, blk_begin, nblk);
         // the accumulator is free once the previous unit's epilogue has read it
         if (!wait_or_abort(smem_u32(acc_empty), (ul & 1) ^ 1, ab, 0x0507)) { ok = false; break; }
         tc_fence_after();
-        for (int i = 0; i < nblk; ++i, ++bg) {
-          const int sa = bg % kSwapASt, xs = bg % Cfg::kXSt;
-          if (!wait_or_abort(smem_u32(x_full + xs), (bg / Cfg::kXSt) & 1, ab, 0x0508)) { ok = false; break; }
-          if (!wait_or_abort(smem_u32(a_full + sa), (bg / kSwapASt) & 1, ab, 0x0503)) { ok = false; break; }
+        const int ngrp = (nblk + 3) / 4;
+        for (int grp = 0; grp < ngrp; ++grp, ++cg) {
+          const int gs = cg % kSwapAGrp;
+          const int nb = (nblk - grp * 4 < 4) ? nblk - grp * 4 : 4;
+          if (!swap_wait(smem_u32(a_full + gs), (cg / kSwapAGrp) & 1, ab, 0x0503)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t x0 = smem_u32(sX + xs * Cfg::kXBytes);
+          const uint64_t xdesc = make_smem_desc(smem_u32(sX + gs * Cfg::kXGBytes), 16, 1024, kSwizzle128B);
+          const uint32_t a0 = tmem_base + kACol0 + gs * 128;
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t bdesc = make_smem_desc(x0 + kk * 32, 16, 1024, kSwizzle128B);
-            tc_mma_f16_ts(tmem_base, tmem_base + kACol0 + sa * 32 + kk * 8, bdesc, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+          for (int j = 0; j < 4; ++j) {
+            if (j < nb) {
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk)
+                tc_mma_f16_ts(tmem_base, a0 + j * 32 + kk * 8, xdesc + ((j * Cfg::kXBytes + kk * 32) >> 4), idesc,
+                              (j == 0 && kk == 0) ? (grp > 0 ? 1u : 0u) : 1u);
+            }
           }
-          tc_commit(smem_u32(a_empty + sa));
-          tc_commit(smem_u32(x_empty + xs));
+          tc_commit(smem_u32(a_empty + gs));
         }
         if (ok) tc_commit(smem_u32(acc_full));
       }
@@ -268,96 +325,30 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
         for (int spin = 0; spin < (1 << 18) && !mbar_try_wait(smem_u32(acc_full), ul & 1); ++spin) {}
       }
     }
-  } else if (warp == 20) {
+  } else if (warp == 2) {
     // ----------------------------------------------------------------------------- token tiles
     if (lane == 0) {
       tma_prefetch_desc(&tmap_x);
-      int bg = 0;
+      int cg = 0;
       bool ok = true;
       for (int u = blockIdx.x; ok && u < p.n_units; u += gridDim.x) {
         int tile, sl, blk_begin, nblk;
         unit_range(u, tile, sl, blk_begin, nblk);
-        for (int i = 0; i < nblk; ++i, ++bg) {
-          const int xs = bg % Cfg::kXSt;
-          if (!wait_or_abort(smem_u32(x_empty + xs), ((bg / Cfg::kXSt) & 1) ^ 1, ab, 0x0501)) { ok = false; break; }
-          mbar_arrive_expect_tx(smem_u32(x_full + xs), Cfg::kXBytes);
-          tma_load_2d(smem_u32(sX + xs * Cfg::kXBytes), &tmap_x, (blk_begin + i) * 64, 0, smem_u32(x_full + xs));
+        const int ngrp = (nblk + 3) / 4;
+        for (int grp = 0; grp < ngrp; ++grp, ++cg) {
+          const int xg = cg % Cfg::kXG;
+          const int nb = (nblk - grp * 4 < 4) ? nblk - grp * 4 : 4;
+          if (!wait_or_abort(smem_u32(a_empty + xg), ((cg / Cfg::kXG) & 1) ^ 1, ab, 0x0501)) { ok = false; break; }
+          mbar_arrive_expect_tx(smem_u32(a_full + xg), nb * Cfg::kXBytes);
+          for (int j = 0; j < nb; ++j)
+            tma_load_2d(smem_u32(sX + xg * Cfg::kXGBytes + j * Cfg::kXBytes), &tmap_x, (blk_begin + grp * 4 + j) * 64, 0, smem_u32(a_full + xg));
         }
-      }
-    }
-  } else if (warp < 4) {
-    // ----------------------------------------------------------------------------- absmax helpers
-    // thread h owns tile rows h and h + 64: absmax[b] = code2[qabs[b]] * scale2 + offset2 (rounded separately) of
-    // the stage's four blocks, rounded to fp16 and stored as (a, a) pairs. The four absmax codes of a group are
-    // one 32-bit word per row; the words of the next four groups are in flight while these four are processed.
-    const int h = threadIdx.x - 64;
-    int cg = 0;
-    bool ok = true;
-    for (int u = blockIdx.x; ok && u < p.n_units; u += gridDim.x) {
-      int tile, sl, blk_begin, nblk;
-      unit_range(u, tile, sl, blk_begin, nblk);
-      const int ngrp = (nblk + 3) / 4;
-      int64_t qr[2];
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        int64_t n = static_cast<int64_t>(tile) * 128 + h + 64 * e;
-        if (n >= p.N) n = p.N - 1;                 // tail rows: any valid row; their output is never stored
-        qr[e] = n * bpr + blk_begin;
-      }
-      auto load_word = [&](int e, int grp) -> uint32_t {
-        // absmax codes of blocks 4 grp .. 4 grp + 3 of row e (bytes past the slice's last block read as 0)
-        if (grp >= ngrp) return 0u;
-        const uint8_t* src = p.qabs + qr[e] + grp * 4;
-        const int nb = (nblk - grp * 4 < 4) ? nblk - grp * 4 : 4;
-        if (nb == 4 && (reinterpret_cast<uintptr_t>(src) & 3) == 0) return __ldg(reinterpret_cast<const uint32_t*>(src));
-        uint32_t w = 0;
-        for (int j = 0; j < nb; ++j) w |= static_cast<uint32_t>(__ldg(src + j)) << (8 * j);
-        return w;
-      };
-      uint32_t cur[4][2], nxt[4][2];
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int e = 0; e < 2; ++e) cur[i][e] = load_word(e, i);
-      for (int g0 = 0; ok && g0 < ngrp; g0 += 4) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-          for (int e = 0; e < 2; ++e) nxt[i][e] = load_word(e, g0 + 4 + i);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int grp = g0 + i;
-          if (grp >= ngrp) break;
-          const int c = cg % kSwapCSt;
-          if (!wait_or_abort(smem_u32(grp_empty + c), ((cg / kSwapCSt) & 1) ^ 1, ab, 0x0509)) { ok = false; break; }
-          uint8_t* dst = sStage + c * Cfg::kStageBytes + Cfg::kAbsOff;
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int64_t b = qr[e] + grp * 4;
-            uint32_t out[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int64_t bj = b + j;
-              const float am = block_absmax(sCode2[(cur[i][e] >> (8 * j)) & 0xffu], __ldg(p.scale2 + (bj >> 8)), __ldg(p.offset2 + (bj >> 8)));
-              const __half2 a2 = __float2half2_rn(am);
-              out[j] = *reinterpret_cast<const uint32_t*>(&a2);
-            }
-            *reinterpret_cast<uint4*>(dst + (h + 64 * e) * 16) = make_uint4(out[0], out[1], out[2], out[3]);
-          }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(grp_full + c));
-          ++cg;
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-          for (int e = 0; e < 2; ++e) cur[i][e] = nxt[i][e];
       }
     }
   } else {
     // ----------------------------------------------------------------------------- decode, then epilogue
     const int q = warp & 3;                       // tensor-memory lane quarter
-    const int team = (warp - 4) >> 2;             // blocks b of the running count with b % 4 == team
+    const int team = (warp - kSwapFirstDecodeWarp) >> 2;
     const int r = q * 32 + lane;                  // weight row inside the tile = tensor-memory lane
     const uint32_t lane_base = smem_u32(sTbl) + lane * 4;
     const uint32_t row_off = r * 128;
@@ -365,48 +356,84 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
     const uint32_t tA = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + kACol0;
     const bool direct = p.slices == 1;
     bool ok = true;
-    int bg = 0, cg = 0, ul = 0;
+    int cg = 0, hc = 0, ul = 0;
+    int64_t s_idx = -1;                           // index of the scale2 / offset2 pair held in registers
+    float s2 = 0.f, o2 = 0.f;
 
     for (int u = blockIdx.x; u < p.n_units; u += gridDim.x, ++ul) {
       int tile, sl, blk_begin, nblk;
       unit_range(u, tile, sl, blk_begin, nblk);
       const int64_t n = static_cast<int64_t>(tile) * 128 + r;
       const bool row_ok = n < p.N;
-      const int ngrp = (nblk + 3) / 4;
-      for (int grp = 0; grp < ngrp; ++grp, ++cg) {
-        const int c = cg % kSwapCSt;
-        const int nb = (nblk - grp * 4 < 4) ? nblk - grp * 4 : 4;
-        // this warp's block of the group (at most one: four consecutive blocks, four teams)
-        const int j = (team - (bg + grp * 4)) & 3;
-        const bool mine = j < nb;
-        if (ok && !wait_or_abort(smem_u32(grp_full + c), (cg / kSwapCSt) & 1, ab, 0x0504)) ok = false;
-        if (ok && mine) {
-          const int gi = bg + grp * 4 + j;
-          const uint32_t src = smem_u32(sStage + c * Cfg::kStageBytes) + row_off;
-          const uint4 c0 = lds128(src + (((2 * j) ^ key) << 4));
-          const uint4 c1 = lds128(src + (((2 * j + 1) ^ key) << 4));
-          const uint32_t am2 = lds_u32s(smem_u32(sStage + c * Cfg::kStageBytes) + Cfg::kAbsOff + r * 16 + j * 4);
-          const int sa = gi % kSwapASt;
-          if (!wait_or_abort(smem_u32(a_empty + sa), ((gi / kSwapASt) & 1) ^ 1, ab, 0x0505)) ok = false;
-          if (ok) {
-            uint32_t v[32];
-            swap_decode8(c0.x, lane_base, am2, v + 0);  swap_decode8(c0.y, lane_base, am2, v + 4);
-            swap_decode8(c0.z, lane_base, am2, v + 8);  swap_decode8(c0.w, lane_base, am2, v + 12);
-            swap_decode8(c1.x, lane_base, am2, v + 16); swap_decode8(c1.y, lane_base, am2, v + 20);
-            swap_decode8(c1.z, lane_base, am2, v + 24); swap_decode8(c1.w, lane_base, am2, v + 28);
-            __syncwarp();
-            tmem_st32(tA + sa * 32, v);
-            tmem_st_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(a_full + sa));
+      const int64_t qrow = (row_ok ? n : p.N - 1) * bpr + blk_begin;     // block index of the row's first block of the slice
+      const int nhalf = (nblk + 1) / 2;
+      // the unit's half groups go round the teams: this team takes those whose running count is team (mod 4)
+      int first = (team - hc) & 3;
+      for (int hu = first; hu < nhalf; hu += kSwapTeams) {
+        const int c = (cg + (hu >> 1)) % kCSt, half = hu & 1;
+        const int gcount = cg + (hu >> 1), gs = gcount % kSwapAGrp;           // running count and slot of the half group's group
+        const int nb2 = (nblk - hu * 2 < 2) ? 1 : 2;           // blocks in this half group
+        if (ok && !wait_or_abort(smem_u32(grp_full + c), ((cg + (hu >> 1)) / kCSt) & 1, ab, 0x0504)) ok = false;
+        uint4 c0 = make_uint4(0, 0, 0, 0), c1 = c0, c2 = c0, c3 = c0;
+        uint32_t qa = 0;
+        if (ok) {
+          const uint32_t stage = smem_u32(sStage + c * Cfg::kStageBytes);
+          const uint32_t src = stage + row_off;
+          c0 = lds128(src + (((4 * half) ^ key) << 4));
+          c1 = lds128(src + (((4 * half + 1) ^ key) << 4));
+          if (nb2 == 2) {
+            c2 = lds128(src + (((4 * half + 2) ^ key) << 4));
+            c3 = lds128(src + (((4 * half + 3) ^ key) << 4));
           }
+          asm volatile("ld.shared.u16 %0, [%1];" : "=r"(qa) : "r"(stage + Cfg::kAbsOff + r * 4 + half * 2) : "memory");
         }
-        // every decode warp hands the coarse stage back exactly once, after its last read of it
+        // the stage goes back as soon as this warp's codes are in registers: eight warps read a stage, or four
+        // (arriving twice) when the unit's last group has one half group only
         __syncwarp();
-        if (ok && lane == 0) mbar_arrive(smem_u32(grp_empty + c));
+        if (ok && lane == 0) {
+          mbar_arrive(smem_u32(grp_empty + c));
+          if (half == 0 && nblk - (hu >> 1) * 4 <= 2) mbar_arrive(smem_u32(grp_empty + c));
+        }
+        // the group's columns of tensor memory are free once the MMAs of three groups ago have completed
+        const bool lone = half == 0 && nblk - (hu >> 1) * 4 <= 2;              // the unit's last group has this half group only
+        if (ok && !wait_or_abort(smem_u32(a_empty + gs), ((gcount / kSwapAGrp) & 1) ^ 1, ab, 0x0505)) ok = false;
+        if (ok) {
+          // absmax = code2[qabs] * scale2 + offset2, rounded separately (the scale pair changes every 256 blocks)
+          const int64_t b0 = qrow + hu * 2;
+          uint32_t am2[2];
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int64_t si = (b0 + j) >> 8;
+            if (si != s_idx) { s_idx = si; s2 = __ldg(p.scale2 + si); o2 = __ldg(p.offset2 + si); }
+            const __half2 a2 = __float2half2_rn(block_absmax(sCode2[(qa >> (8 * j)) & 0xffu], s2, o2));
+            am2[j] = *reinterpret_cast<const uint32_t*>(&a2);
+          }
+          uint32_t v[32];
+          swap_decode8(c0.x, lane_base, am2[0], v + 0);  swap_decode8(c0.y, lane_base, am2[0], v + 4);
+          swap_decode8(c0.z, lane_base, am2[0], v + 8);  swap_decode8(c0.w, lane_base, am2[0], v + 12);
+          swap_decode8(c1.x, lane_base, am2[0], v + 16); swap_decode8(c1.y, lane_base, am2[0], v + 20);
+          swap_decode8(c1.z, lane_base, am2[0], v + 24); swap_decode8(c1.w, lane_base, am2[0], v + 28);
+          __syncwarp();
+          tmem_st32(tA + gs * 128 + half * 64, v);
+          if (nb2 == 2) {
+            swap_decode8(c2.x, lane_base, am2[1], v + 0);  swap_decode8(c2.y, lane_base, am2[1], v + 4);
+            swap_decode8(c2.z, lane_base, am2[1], v + 8);  swap_decode8(c2.w, lane_base, am2[1], v + 12);
+            swap_decode8(c3.x, lane_base, am2[1], v + 16); swap_decode8(c3.y, lane_base, am2[1], v + 20);
+            swap_decode8(c3.z, lane_base, am2[1], v + 24); swap_decode8(c3.w, lane_base, am2[1], v + 28);
+            __syncwarp();
+            tmem_st32(tA + gs * 128 + half * 64 + 32, v);
+          }
+          tmem_st_wait();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (ok && lane == 0) {
+          mbar_arrive(smem_u32(a_full + gs));
+          if (lone) mbar_arrive(smem_u32(a_full + gs));
+        }
       }
-      bg += nblk;
+      hc += nhalf;
+      cg += (nblk + 3) / 4;
 
       // --- epilogue of the unit: lane = weight row, columns = tokens; team t takes token columns 16 t .. 16 t + 15
       if (ok) ok = wait_or_abort(smem_u32(acc_full), ul & 1, ab, 0x0506);
@@ -481,7 +508,7 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
         // the unit of a tile that arrives last adds the partial sums up in slice order
         __threadfence();
         named_barrier(1, kSwapDecodeWarps * 32);
-        if (threadIdx.x == 128) {
+        if (threadIdx.x == kSwapFirstDecodeWarp * 32) {
           const int prev = atomicAdd(p.counters + tile, 1);
           *last_flag = (prev == p.slices - 1) ? 1 : 0;
           *stop_flag = *abort_flag;               // sampled once per unit, so that all decode warps leave together

@@ -240,7 +240,10 @@ int nf4ll_read_status(const int32_t* status, void* stream);
  * for the calling thread's next nf4ll_forward / nf4ll_backward_dx calls; zeros restore the built-in
  * heuristic. flags bit 0: never use the cooperative split reduction (the splits of a tile then leave the
  * sum to whichever of them finishes last), e.g. under a profiler that replays kernels one at a time.
- * Size the workspace of such calls with nf4ll_workspace_bytes_tuned. */
+ * flags bit 1: run a forward of at most 64 rows on the register-level weight-streaming kernel (default: up to
+ * 16 rows); flags bit 2: run a forward of at most 64 rows on the swapped-operand tensor-core kernel (default:
+ * 33 to 64 rows against weights of at least 2^26 elements). With bit 1 or 2, `splits` forces that kernel's
+ * number of slices of the contraction. Size the workspace of such calls with nf4ll_workspace_bytes_tuned. */
 void nf4ll_tune_override(int32_t bm_tiles, int32_t bn, int32_t splits, int32_t flags);
 
 /* Measurement hook; no counterpart in the reference. The calling thread's NEXT nf4ll_forward /

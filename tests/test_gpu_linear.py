@@ -303,6 +303,45 @@ def test_block_step_replays_from_a_cuda_graph():
     assert rel <= 1e-5, (err, rel)
 
 
+def test_block_gradients_on_a_side_stream_match_the_single_stream_step():
+    """The dA/dB kernels issued on a side stream (forked after the dX launch of their projection, joined at
+    the end of the backward) give what the single-stream step gives, eagerly and from a captured graph."""
+    from decentrik_prime_b200 import blocks
+    dev = torch.device("cuda")
+    bucket = blocks.GradBucket(blocks.MlpBlock.grad_numel(1536, 1024), dev)
+    blk = blocks.MlpBlock(1536, 1024, seed=23, device=dev, bucket=bucket)
+    gen = torch.Generator().manual_seed(4)
+    M = 1024
+    x = torch.randn(M, 1536, generator=gen).half().cuda()
+    dy = torch.randn(M, 1536, generator=gen).half().cuda()
+    masks = [(torch.rand(M, k, generator=gen) >= 0.05).to(torch.uint8).cuda() for k in (1536, 1536, 1024)]
+    ks = 1.0 / 0.95
+    y0 = blk.forward(x, masks, ks)
+    dx0 = blk.backward(dy).clone()
+    g0 = bucket.flat.clone()
+    blk.use_grad_stream()
+    for _ in range(2):
+        blk.forward(x, masks, ks)
+        dx1 = blk.backward(dy)
+    torch.cuda.synchronize()
+    assert torch.equal(dx1, dx0)
+    err, rel = nf4_oracle.errors(bucket.flat, g0.double())
+    assert rel <= 1e-5, (err, rel)
+    side = torch.cuda.Stream(dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            blk.forward(x, masks, ks)
+            dx2 = blk.backward(dy)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    linear.check_status()
+    assert torch.equal(dx2, dx0)
+    err, rel = nf4_oracle.errors(bucket.flat, g0.double())
+    assert rel <= 1e-5, (err, rel)
+
+
 def test_split_contraction_is_stable_under_back_to_back_launches():
     """The split-contraction path (partial sums through scratch, the splits of a tile share the final
     reduction) must give the same bits on every launch: 100 forwards queued back to back without host

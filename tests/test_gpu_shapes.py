@@ -70,6 +70,49 @@ def test_small_batch_forward_variants(N, K, M):
             assert_close("t", t, ref["t"])
 
 
+@pytest.mark.parametrize("N,K", [(256, 256), (192, 256), (256, 384), (640, 1024), (4096, 512), (256, 320), (512, 2112)])
+@pytest.mark.parametrize("M", [1, 16, 17, 33, 64])
+def test_swapped_operand_kernel_variants(N, K, M):
+    """The swapped-operand tensor-core kernel (weights as the MMA's 128-row operand, 16 / 32 / 64 token columns),
+    forced through the tuning hook: one and several slices of the contraction, tiles with fewer than 128 weight
+    rows (N = 192), last groups of one and two quantisation blocks (K = 320, 2112, 384),
+    row lengths that are not a multiple of four blocks (K = 384, 320: absmax codes fetched byte by byte)."""
+    pr = make_problem(N, K, M, seed=3000 + N + K + M, lora=True, dropout=0.05, bias=True)
+    ref = nf4_oracle.lora_linear_o1(oracle_weight(pr), pr.x, None, pr.bias, pr.A16, pr.B16, pr.scale, pr.mask, pr.keep_scale)
+    d = to_device(pr)
+    ws = torch.empty(64 << 20, dtype=torch.uint8, device="cuda")
+    for slices in (0, 1, 2, 3):
+        with linear.tune_override(splits=slices, flags=4):
+            y, t = linear.forward(d.w, d.x, bias=d.bias, lora=d.lora, mask=d.mask, keep_scale=d.keep_scale, workspace=ws, want_t=True)
+        linear.check_status()
+        assert_close(f"y slices={slices}", y, ref["y"])
+        assert_close("t", t, ref["t"])
+    # no LoRA, no bias: the epilogue's plain path
+    pr = make_problem(N, K, M, seed=3100 + N + K + M, lora=False, dropout=0.0)
+    ref = nf4_oracle.lora_linear_o1(oracle_weight(pr), pr.x, None, None, None, None, 1.0, None, 1.0)
+    d = to_device(pr)
+    with linear.tune_override(flags=4):
+        y, _ = linear.forward(d.w, d.x, workspace=ws)
+    linear.check_status()
+    assert_close("y plain", y, ref["y"])
+
+
+@pytest.mark.parametrize("M", [17, 32, 33, 64])
+def test_streaming_kernel_forced_up_to_64_rows(M):
+    """The register-level weight-streaming kernel with four and eight token tiles (17..64 rows), which the
+    default dispatch never picks: forced through the tuning hook."""
+    for N, K in ((256, 256), (256, 384)):
+        pr = make_problem(N, K, M, seed=3200 + N + K + M, lora=True, dropout=0.05, bias=True)
+        ref = nf4_oracle.lora_linear_o1(oracle_weight(pr), pr.x, None, pr.bias, pr.A16, pr.B16, pr.scale, pr.mask, pr.keep_scale)
+        d = to_device(pr)
+        ws = torch.empty(64 << 20, dtype=torch.uint8, device="cuda")
+        for slices in (0, 2):
+            with linear.tune_override(splits=slices, flags=2):
+                y, _ = linear.forward(d.w, d.x, bias=d.bias, lora=d.lora, mask=d.mask, keep_scale=d.keep_scale, workspace=ws)
+            linear.check_status()
+            assert_close(f"y slices={slices}", y, ref["y"])
+
+
 CONFIG4_SHAPES = {"q/o": (5120, 5120), "gate/up": (27648, 5120), "down": (5120, 27648)}
 
 
