@@ -469,7 +469,7 @@ def run_ours(args):
         if world == 1 and not args.no_stream:
             if args.profile_leg == "stream":
                 torch.cuda.profiler.start()
-            cases = weight_stream_numbers(dev, pk["hbm_gbs"])
+            cases = weight_stream_numbers(dev, pk["hbm_gbs"], args.stream_case)
             if args.profile_leg == "stream":
                 torch.cuda.profiler.stop()
             line["weight_stream"] = {"unit": "GB/s of NF4 bytes", "peak_gbs": pk["hbm_gbs"], "peak_source": pk["source"],
@@ -660,20 +660,25 @@ def run_stack(args):
         dist.destroy_process_group()
 
 
-def weight_stream_numbers(dev, peak_gbs):
+def weight_stream_numbers(dev, peak_gbs, only=None):
     """Secondary metric of the path: NF4 bytes streamed per second by the forward at decode-sized
     batches (benchmark configuration 4: Qwen2.5-32B shapes, LoRA r=16 fused, M in {1, 8, 64}). Distinct weight
     copies larger than L2 (126 MB) rotate inside one CUDA graph so that every launch reads its NF4
-    bytes from HBM; the figure is algorithmic bytes (0.516 B per weight) over the median replay time."""
+    bytes from HBM; the figure is algorithmic bytes (0.516 B per weight) over the median replay time.
+    `only` = "<shape prefix>:<M>" (e.g. "gate:64") restricts the leg to one case, for a profiler capture."""
     import statistics
     import torch
     from decentrik_prime_b200 import blocks, linear
     out = []
     for name, n, k, copies in (("q/o 5120x5120", 5120, 5120, 20), ("gate/up 27648x5120", 27648, 5120, 4),
                                ("down 5120x27648", 5120, 27648, 4)):
+        if only and not name.startswith(only.split(":")[0]):
+            continue
         ps = [blocks.make_projection(n, k, seed=900 + i, device=dev, lora=True) for i in range(copies)]
         nbytes = ps[0].w.nbytes
         for M in (1, 8, 64):
+            if only and int(only.split(":")[1]) != M:
+                continue
             x = torch.randn(M, k, device=dev).half()
             ys = [torch.empty(M, n, device=dev, dtype=torch.float16) for _ in ps]
             side = torch.cuda.Stream(dev)
@@ -773,6 +778,8 @@ def main():
     ap.add_argument("--profile-leg", default="step", choices=("step", "stream"),
                     help="which leg cudaProfilerStart/Stop brackets (for `ncu --profile-from-start off`): the timed "
                          "steps, or the small-batch weight-stream measurements")
+    ap.add_argument("--stream-case", default=None,
+                    help='run one case of the weight-stream leg only, "<shape prefix>:<M>", e.g. "gate:64" (profiler captures)')
     ap.add_argument("--workload", default="mlp", choices=("mlp", "stack1.5b", "stack7b"),
                     help="mlp = the default bench line (benchmark configuration 1); stack* = configs 2 / 3")
     args = ap.parse_args()
