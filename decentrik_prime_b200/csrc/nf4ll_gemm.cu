@@ -1198,21 +1198,26 @@ int64_t swap_workspace_bytes(int64_t N, int64_t K, int64_t M, int sms, int force
 constexpr int64_t kStreamMaxRows = 16;     // at or below this many token rows the forward is a weight-streaming pass
 constexpr int64_t kStreamCapRows = 64;     // the streaming kernel's own limit (reachable through the tuning hook)
 constexpr int64_t kSwapMaxRows = 64;       // limit of the swapped-operand kernel (weights as the MMA's M operand)
-constexpr int64_t kSwapMinRows = 33;       // measured on B200: from here up, and for weights of at least
-constexpr int64_t kSwapMinWeights = int64_t(1) << 26;      // this many elements, it beats the 128-row tiles (by 4-13 %)
+// measured on B200 against the streaming kernel (two token tiles) and the 128-row tiles: the swapped-operand kernel
+// wins from 9 rows up on weights of at least 2^24 elements, and up to 64 rows on weights of at least 2^26
+constexpr int64_t kSwapMinRows = 9;
+constexpr int64_t kSwapMidRows = 32;
+constexpr int64_t kSwapMinWeights = int64_t(1) << 24;
+constexpr int64_t kSwapBigWeights = int64_t(1) << 26;
 
 // Which kernel computes a forward of M rows: the 256 x 256 / 128-row tile kernels (kTiles), the register-level
 // weight-streaming kernel for decode-sized batches (kStream), or the swapped-operand tensor-core kernel for
-// short batches of 33 to 64 rows against a large weight (kSwap). Bits 1 and 2 of the tuning flags force kStream /
+// short batches of 9 to 64 rows against a large weight (kSwap). Bits 1 and 2 of the tuning flags force kStream /
 // kSwap up to that kernel's limit.
 enum : int { kTiles = 0, kStream = 1, kSwap = 2 };
 static int forward_kind(int mode, int64_t M, int64_t N, int64_t K, bool stacked, const Tune& tune) {
   if (mode != kFwd || stacked) return kTiles;
   if (tune.flags & 2) return M <= kStreamCapRows ? kStream : kTiles;
-  if (tune.flags & 4) return M <= kSwapMaxRows ? kSwap : kTiles;
+  const bool swap_ok = M <= kSwapMaxRows && N * (K / 64) < (int64_t(1) << 31);      // the kernel indexes quantisation blocks with 32 bits
+  if (tune.flags & 4) return swap_ok ? kSwap : kTiles;
   if (tune.any()) return kTiles;
+  if (swap_ok && M >= kSwapMinRows && N * K >= (M <= kSwapMidRows ? kSwapMinWeights : kSwapBigWeights)) return kSwap;
   if (M <= kStreamMaxRows) return kStream;
-  if (M >= kSwapMinRows && M <= kSwapMaxRows && N * K >= kSwapMinWeights) return kSwap;
   return kTiles;
 }
 

@@ -22,12 +22,16 @@
 // (two blocks, K = 128, 64 columns of A operand) at a time, the half groups going round the teams, so that four
 // half groups are being decoded at once and each team's chain of latencies (wait, shared loads, table loads,
 // tcgen05.st, fence, arrive) overlaps the others'. Tensor memory holds three groups of A operand.
-// The MMA issuer is ONE thread, and what it does per group is kept to one wait, up to sixteen MMAs whose
-// descriptors differ by immediates, and one commit: a group's A operand and its token tiles share one "full"
-// barrier (eight warp arrivals + the TMA bytes) and one "empty" barrier (the commit), three groups deep.
-// Measured on B200: an MMA of 128 x N x 16 takes about 64 clocks for every N <= 128 (72 with A in tensor memory)
-// and a commit costs the issuing thread about as much as two MMAs, so sixteen MMAs per group bound the kernel at
-// about 28 weights per clock per SM.
+// What an MMA-issuing thread does per group is kept to one wait, up to sixteen MMAs whose descriptors differ by
+// immediates, and one commit: a group's A operand and its token tiles share one "full" barrier (eight warp
+// arrivals + the TMA bytes) and one "empty" barrier (the commit), three groups deep. Measured on B200: ONE thread
+// issues an MMA of 128 x N x 16 (N <= 128, A in tensor memory) every 70-90 clocks whatever N is, while the tensor
+// pipe is busy for a fraction of that; the rate adds up over issuing threads (2 threads: 48 clocks per MMA, 4: 24).
+// So TWO threads issue, one the MMAs of the first two blocks of every group, the other those of the last two,
+// each into an accumulator of its own; the epilogue adds the two.
+// Barrier discipline: an mbarrier wait names a phase by its parity only, so every waiter must meet every phase of a
+// barrier in order. Even groups (decoded by teams 0-1) and odd groups (teams 2-3) therefore use barriers of their own: the "full" / "empty" pair of a group is indexed by its running count modulo 6 (slot x parity), while
+// the storage it guards (tensor-memory columns, token tiles) is indexed modulo 3.
 //
 // The scale is applied in fp16 (weight = fp16(fp16(NF4[c]) * fp16(absmax))), which differs from the big-tile
 // kernel's bit-exact fp16(NF4[c] * absmax) by a few 2^-11 relative roundings, inside the 1e-3 tolerance of the path.
@@ -36,8 +40,8 @@
 // With more than one slice the units of a tile leave their partial sums in a slab of the workspace and the last
 // one to arrive adds them up in slice order (a fixed order), adds bias and the LoRA term and stores fp16.
 //
-// Warp roles: 0 producer of codes (TMA) and absmax codes (cp.async), 1 tensor-memory allocation + MMA issue,
-// 2 TMA producer of token tiles, 3..18 decode and then the epilogue. Every wait is bounded and reports through
+// Warp roles: 0 producer of codes (TMA) and absmax codes (cp.async), 1 tensor-memory allocation + MMA issue (first
+// half of every group), 2 TMA producer of token tiles, 3..18 decode and then the epilogue, 19 MMA issue (second half). Every wait is bounded and reports through
 // the status word.
 #include "nf4ll_gemm_shared.cuh"
 
@@ -63,7 +67,9 @@ struct SwapParams {
   int32_t* status;
 };
 
-constexpr int kSwapThreads = 608;            // code producer, MMA issuer, token-tile producer, 16 decode warps
+constexpr int kSwapThreads = 640;            // code producer, MMA issuer, token-tile producer, 16 decode warps, second MMA issuer
+constexpr int kSwapIssuers = 2;              // MMA-issuing threads, each with its own accumulator
+constexpr int kSwapIssuerWarp1 = 19;
 constexpr int kSwapTeams = 4;
 constexpr int kSwapDecodeWarps = 4 * kSwapTeams;
 constexpr int kSwapFirstDecodeWarp = 3;
@@ -76,11 +82,13 @@ struct SwapCfg {
   static constexpr int kXBytes = NTOK * 128;                       // one token tile: NTOK rows x 64 fp16
   static constexpr int kXGBytes = 4 * kXBytes;                     // the four token tiles of a group
   static constexpr int kXG = kSwapAGrp;                            // groups of token tiles in flight (they come from L2)
-  static constexpr int kCSt = NTOK == 64 ? 5 : (NTOK == 32 ? 6 : 8);   // coarse stages in flight: codes of four blocks (16 KB) + their absmax codes
+  // coarse stages in flight: codes of four blocks (16 KB) + their absmax codes. An EVEN number: a team reads the
+  // groups of one parity only, and must meet every phase of a stage's barrier (a parity wait cannot skip one)
+  static constexpr int kCSt = NTOK == 64 ? 4 : (NTOK == 32 ? 6 : 8);
   static constexpr int kAbsOff = kSwapCodeBytes;                   // absmax codes of the stage: [128 rows][4 blocks] bytes
   static constexpr int kStageBytes = kSwapCodeBytes + 1024;        // kept a multiple of 1024 for the swizzled codes
-  static constexpr int kDCols = 64;                                // accumulator columns reserved
-  static constexpr int kTmemCols = 512;                            // accumulator + 3 x 128 A columns, as a power of two
+  static constexpr int kDCols = 64 * kSwapIssuers;                 // accumulator columns reserved: 64 per issuing thread
+  static constexpr int kTmemCols = 512;                            // 2 accumulators + 3 x 128 A columns
   static constexpr int kSmemBytes = 1024 + kCSt * kStageBytes + kXG * kXGBytes + kSwapTableBytes + 1024 + 512;
   static_assert(kDCols + kSwapAGrp * 128 <= kTmemCols, "tensor memory budget");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
@@ -94,7 +102,7 @@ __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
 __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
-// a wait for the one thread that issues the MMAs: polls without the slow path's bookkeeping until the limit
+// a wait for the threads on the kernel's critical path: polls without the slow path's bookkeeping until the limit
 __device__ __forceinline__ bool swap_wait(uint32_t bar, uint32_t parity, const Abort& ab, int code) {
   for (uint32_t i = 0; i < 4096u; ++i)
     if (mbar_try_wait(bar, parity)) return true;
@@ -142,6 +150,17 @@ __device__ __forceinline__ void swap_decode8(uint32_t w, uint32_t lane_base, uin
   }
 }
 
+// 32 lanes x 16 consecutive 32-bit columns, registers -> tensor memory
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+
 // 32 lanes x 16 consecutive fp32 columns
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
   asm volatile(
@@ -173,7 +192,8 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
   uint64_t* a_empty = a_full + 8;                // [kSwapAGrp] the MMAs that read the group (A operand and token tiles) have completed
   uint64_t* grp_full = a_empty + 8;              // [kCSt] codes and absmax codes landed
   uint64_t* grp_empty = grp_full + 8;            // [kCSt] the eight decode warps of the group's two half groups have read it
-  uint64_t* acc_full = grp_empty + 8;
+  uint64_t* drain = grp_empty + 8;               // [kSwapIssuers] used only when a wait has failed: the issuer's MMAs have all completed
+  uint64_t* acc_full = drain + 2;
   uint64_t* acc_empty = acc_full + 1;            // the epilogue has read the accumulator (sixteen decode warps)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -195,15 +215,16 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
   };
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kSwapAGrp; ++s) {
+    for (int s = 0; s < 2 * kSwapAGrp; ++s) {
       mbar_init(smem_u32(a_full + s), 8 + 1);          // the warps of the group's two half groups + the token tiles' TMA bytes
-      mbar_init(smem_u32(a_empty + s), 1);
+      mbar_init(smem_u32(a_empty + s), kSwapIssuers);  // one commit per issuing thread
     }
+    for (int s = 0; s < kSwapIssuers; ++s) mbar_init(smem_u32(drain + s), 1);
     for (int s = 0; s < kCSt; ++s) {
       mbar_init(smem_u32(grp_full + s), 1 + 32);       // TMA bytes + the producer warp's 32 lanes (their absmax-code copies)
       mbar_init(smem_u32(grp_empty + s), 8);
     }
-    mbar_init(smem_u32(acc_full), 1);
+    mbar_init(smem_u32(acc_full), kSwapIssuers);
     mbar_init(smem_u32(acc_empty), kSwapDecodeWarps);
     *abort_flag = 0;
     *last_flag = 0;
@@ -286,10 +307,13 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
       for (int k = (cg > kCSt ? cg - kCSt : 0); k < cg; ++k)
         for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(smem_u32(grp_full + k % kCSt), (k / kCSt) & 1); ++spin) {}
     }
-  } else if (warp == 1) {
-    // ----------------------------------------------------------------------------- MMA issuer
+  } else if (warp == 1 || warp == kSwapIssuerWarp1) {
+    // ----------------------------------------------------------------------------- MMA issuers
+    // issuer mi takes blocks 2 mi and 2 mi + 1 of every group and accumulates them in its own columns
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_f16(128, NTOK, 0, 0);
+      const int mi = warp == 1 ? 0 : 1;
+      const uint32_t d_tmem = tmem_base + mi * 64;
       bool ok = true;
       int cg = 0, ul = 0;
       for (int u = blockIdx.x; ok && u < p.n_units; u += gridDim.x, ++ul) {
@@ -299,30 +323,34 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
         if (!wait_or_abort(smem_u32(acc_empty), (ul & 1) ^ 1, ab, 0x0507)) { ok = false; break; }
         tc_fence_after();
         const int ngrp = (nblk + 3) / 4;
+        bool first = true;                         // this issuer's first MMA of the unit overwrites its accumulator
         for (int grp = 0; grp < ngrp; ++grp, ++cg) {
           const int gs = cg % kSwapAGrp;
           const int nb = (nblk - grp * 4 < 4) ? nblk - grp * 4 : 4;
-          if (!swap_wait(smem_u32(a_full + gs), (cg / kSwapAGrp) & 1, ab, 0x0503)) { ok = false; break; }
+          const int gb = cg % (2 * kSwapAGrp);        // the group's barrier pair
+          if (!swap_wait(smem_u32(a_full + gb), (cg / (2 * kSwapAGrp)) & 1, ab, 0x0503)) { ok = false; break; }
           tc_fence_after();
           const uint64_t xdesc = make_smem_desc(smem_u32(sX + gs * Cfg::kXGBytes), 16, 1024, kSwizzle128B);
           const uint32_t a0 = tmem_base + kACol0 + gs * 128;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int jj = 0; jj < 2; ++jj) {
+            const int j = 2 * mi + jj;
             if (j < nb) {
 #pragma unroll
               for (int kk = 0; kk < 4; ++kk)
-                tc_mma_f16_ts(tmem_base, a0 + j * 32 + kk * 8, xdesc + ((j * Cfg::kXBytes + kk * 32) >> 4), idesc,
-                              (j == 0 && kk == 0) ? (grp > 0 ? 1u : 0u) : 1u);
+                tc_mma_f16_ts(d_tmem, a0 + j * 32 + kk * 8, xdesc + ((j * Cfg::kXBytes + kk * 32) >> 4), idesc,
+                              (jj == 0 && kk == 0) ? (first ? 0u : 1u) : 1u);
             }
           }
-          tc_commit(smem_u32(a_empty + gs));
+          if (2 * mi < nb) first = false;
+          tc_commit(smem_u32(a_empty + gb));
         }
         if (ok) tc_commit(smem_u32(acc_full));
       }
       if (!ok) {
-        // make sure nothing is still running on the tensor core before tensor memory is freed
-        tc_commit(smem_u32(acc_full));
-        for (int spin = 0; spin < (1 << 18) && !mbar_try_wait(smem_u32(acc_full), ul & 1); ++spin) {}
+        // make sure none of this thread's MMAs is still running before tensor memory is freed
+        tc_commit(smem_u32(drain + mi));
+        for (int spin = 0; spin < (1 << 18) && !mbar_try_wait(smem_u32(drain + mi), 0); ++spin) {}
       }
     }
   } else if (warp == 2) {
@@ -338,10 +366,12 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
         for (int grp = 0; grp < ngrp; ++grp, ++cg) {
           const int xg = cg % Cfg::kXG;
           const int nb = (nblk - grp * 4 < 4) ? nblk - grp * 4 : 4;
-          if (!wait_or_abort(smem_u32(a_empty + xg), ((cg / Cfg::kXG) & 1) ^ 1, ab, 0x0501)) { ok = false; break; }
-          mbar_arrive_expect_tx(smem_u32(a_full + xg), nb * Cfg::kXBytes);
+          const int gb = cg % (2 * kSwapAGrp);
+          if (cg >= kSwapAGrp &&
+              !wait_or_abort(smem_u32(a_empty + (cg - kSwapAGrp) % (2 * kSwapAGrp)), ((cg - kSwapAGrp) / (2 * kSwapAGrp)) & 1, ab, 0x0501)) { ok = false; break; }
+          mbar_arrive_expect_tx(smem_u32(a_full + gb), nb * Cfg::kXBytes);
           for (int j = 0; j < nb; ++j)
-            tma_load_2d(smem_u32(sX + xg * Cfg::kXGBytes + j * Cfg::kXBytes), &tmap_x, (blk_begin + grp * 4 + j) * 64, 0, smem_u32(a_full + xg));
+            tma_load_2d(smem_u32(sX + xg * Cfg::kXGBytes + j * Cfg::kXBytes), &tmap_x, (blk_begin + grp * 4 + j) * 64, 0, smem_u32(a_full + gb));
         }
       }
     }
@@ -356,8 +386,8 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
     const uint32_t tA = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + kACol0;
     const bool direct = p.slices == 1;
     bool ok = true;
-    int cg = 0, hc = 0, ul = 0;
-    int64_t s_idx = -1;                           // index of the scale2 / offset2 pair held in registers
+    int cg = 0, ul = 0;
+    int s_idx = -1;                               // index of the scale2 / offset2 pair held in registers
     float s2 = 0.f, o2 = 0.f;
 
     for (int u = blockIdx.x; u < p.n_units; u += gridDim.x, ++ul) {
@@ -365,15 +395,21 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
       unit_range(u, tile, sl, blk_begin, nblk);
       const int64_t n = static_cast<int64_t>(tile) * 128 + r;
       const bool row_ok = n < p.N;
-      const int64_t qrow = (row_ok ? n : p.N - 1) * bpr + blk_begin;     // block index of the row's first block of the slice
-      const int nhalf = (nblk + 1) / 2;
-      // the unit's half groups go round the teams: this team takes those whose running count is team (mod 4)
-      int first = (team - hc) & 3;
-      for (int hu = first; hu < nhalf; hu += kSwapTeams) {
-        const int c = (cg + (hu >> 1)) % kCSt, half = hu & 1;
-        const int gcount = cg + (hu >> 1), gs = gcount % kSwapAGrp;           // running count and slot of the half group's group
-        const int nb2 = (nblk - hu * 2 < 2) ? 1 : 2;           // blocks in this half group
-        if (ok && !wait_or_abort(smem_u32(grp_full + c), ((cg + (hu >> 1)) / kCSt) & 1, ab, 0x0504)) ok = false;
+      const int qrow = static_cast<int>((row_ok ? n : p.N - 1) * bpr) + blk_begin;   // block index of the row's first block of the slice (< 2^31: checked on the host)
+      const int ngrp_unit = (nblk + 3) / 4;
+      // teams 0, 1 take the first and the second half of the groups whose running count is even, teams 2, 3 those of
+      // the odd ones: a team meets every phase of the barriers it waits on (a unit's last group may lack its second
+      // half; the epilogue that follows orders everything of the unit before the team's next wait)
+      const int half = team & 1;
+      for (int grp = 0; grp < ngrp_unit; ++grp) {
+        const int gcount = cg + grp;                           // running count of the group
+        if ((gcount & 1) != (team >> 1)) continue;
+        const int nb = (nblk - grp * 4 < 4) ? nblk - grp * 4 : 4;
+        if (half * 2 >= nb) continue;
+        const int hu = grp * 2 + half;                         // half group of the unit
+        const int c = gcount % kCSt, gs = gcount % kSwapAGrp;
+        const int nb2 = (nb - half * 2 < 2) ? 1 : 2;           // blocks in this half group
+        if (ok && !swap_wait(smem_u32(grp_full + c), (gcount / kCSt) & 1, ab, 0x0504)) ok = false;
         uint4 c0 = make_uint4(0, 0, 0, 0), c1 = c0, c2 = c0, c3 = c0;
         uint32_t qa = 0;
         if (ok) {
@@ -392,48 +428,55 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
         __syncwarp();
         if (ok && lane == 0) {
           mbar_arrive(smem_u32(grp_empty + c));
-          if (half == 0 && nblk - (hu >> 1) * 4 <= 2) mbar_arrive(smem_u32(grp_empty + c));
+          if (nb <= 2) mbar_arrive(smem_u32(grp_empty + c));
         }
         // the group's columns of tensor memory are free once the MMAs of three groups ago have completed
-        const bool lone = half == 0 && nblk - (hu >> 1) * 4 <= 2;              // the unit's last group has this half group only
-        if (ok && !wait_or_abort(smem_u32(a_empty + gs), ((gcount / kSwapAGrp) & 1) ^ 1, ab, 0x0505)) ok = false;
+        const bool lone = nb <= 2;                 // the unit's last group has this half group only
+        const int gb = gcount % (2 * kSwapAGrp);
+        if (ok && gcount >= kSwapAGrp &&
+            !swap_wait(smem_u32(a_empty + (gcount - kSwapAGrp) % (2 * kSwapAGrp)), ((gcount - kSwapAGrp) / (2 * kSwapAGrp)) & 1, ab, 0x0505)) ok = false;
         if (ok) {
           // absmax = code2[qabs] * scale2 + offset2, rounded separately (the scale pair changes every 256 blocks)
-          const int64_t b0 = qrow + hu * 2;
+          const int b0 = qrow + hu * 2;
           uint32_t am2[2];
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
-            const int64_t si = (b0 + j) >> 8;
+            const int si = (b0 + j) >> 8;
             if (si != s_idx) { s_idx = si; s2 = __ldg(p.scale2 + si); o2 = __ldg(p.offset2 + si); }
             const __half2 a2 = __float2half2_rn(block_absmax(sCode2[(qa >> (8 * j)) & 0xffu], s2, o2));
             am2[j] = *reinterpret_cast<const uint32_t*>(&a2);
           }
-          uint32_t v[32];
+          // sixteen columns (32 weights) at a time: the thread holds its four words of codes and one batch of results
+          uint32_t v[16];
+          const uint32_t dst = tA + gs * 128 + half * 64;
           swap_decode8(c0.x, lane_base, am2[0], v + 0);  swap_decode8(c0.y, lane_base, am2[0], v + 4);
           swap_decode8(c0.z, lane_base, am2[0], v + 8);  swap_decode8(c0.w, lane_base, am2[0], v + 12);
-          swap_decode8(c1.x, lane_base, am2[0], v + 16); swap_decode8(c1.y, lane_base, am2[0], v + 20);
-          swap_decode8(c1.z, lane_base, am2[0], v + 24); swap_decode8(c1.w, lane_base, am2[0], v + 28);
           __syncwarp();
-          tmem_st32(tA + gs * 128 + half * 64, v);
+          tmem_st16(dst, v);
+          swap_decode8(c1.x, lane_base, am2[0], v + 0);  swap_decode8(c1.y, lane_base, am2[0], v + 4);
+          swap_decode8(c1.z, lane_base, am2[0], v + 8);  swap_decode8(c1.w, lane_base, am2[0], v + 12);
+          __syncwarp();
+          tmem_st16(dst + 16, v);
           if (nb2 == 2) {
             swap_decode8(c2.x, lane_base, am2[1], v + 0);  swap_decode8(c2.y, lane_base, am2[1], v + 4);
             swap_decode8(c2.z, lane_base, am2[1], v + 8);  swap_decode8(c2.w, lane_base, am2[1], v + 12);
-            swap_decode8(c3.x, lane_base, am2[1], v + 16); swap_decode8(c3.y, lane_base, am2[1], v + 20);
-            swap_decode8(c3.z, lane_base, am2[1], v + 24); swap_decode8(c3.w, lane_base, am2[1], v + 28);
             __syncwarp();
-            tmem_st32(tA + gs * 128 + half * 64 + 32, v);
+            tmem_st16(dst + 32, v);
+            swap_decode8(c3.x, lane_base, am2[1], v + 0);  swap_decode8(c3.y, lane_base, am2[1], v + 4);
+            swap_decode8(c3.z, lane_base, am2[1], v + 8);  swap_decode8(c3.w, lane_base, am2[1], v + 12);
+            __syncwarp();
+            tmem_st16(dst + 48, v);
           }
           tmem_st_wait();
         }
         tc_fence_before();
         __syncwarp();
         if (ok && lane == 0) {
-          mbar_arrive(smem_u32(a_full + gs));
-          if (lone) mbar_arrive(smem_u32(a_full + gs));
+          mbar_arrive(smem_u32(a_full + gb));
+          if (lone) mbar_arrive(smem_u32(a_full + gb));
         }
       }
-      hc += nhalf;
-      cg += (nblk + 3) / 4;
+      cg += ngrp_unit;
 
       // --- epilogue of the unit: lane = weight row, columns = tokens; team t takes token columns 16 t .. 16 t + 15
       if (ok) ok = wait_or_abort(smem_u32(acc_full), ul & 1, ab, 0x0506);
@@ -474,8 +517,15 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
         if (has_cols) {
           if (direct) load_row_terms();
           __syncwarp();
-          tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + team * 16, v);
+          // the accumulators of the two issuing threads (the second one unused by a unit of one or two blocks)
+          const bool used0 = true, used1 = nblk > 2;
+          uint32_t w[16];
+          if (used0) tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + team * 16, v);
+          if (used1) tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + 64 + team * 16, w);
           tmem_ld_wait();
+#pragma unroll
+          for (int jt = 0; jt < 16; ++jt)
+            v[jt] = __float_as_uint((used0 ? __uint_as_float(v[jt]) : 0.f) + (used1 ? __uint_as_float(w[jt]) : 0.f));
         }
         // the accumulator is in registers: the next unit's MMAs may overwrite it
         tc_fence_before();
@@ -592,10 +642,11 @@ void swap_plan(int64_t N, int64_t K, int ntok, int sms, int force_slices, int* s
     if ((groups + per - 1) / per != s) continue;            // not a distinct split
     const int64_t units = tiles * s;
     const int64_t rounds = (units + grid - 1) / grid;
-    // in units of "one group of four blocks of one tile": a unit costs its groups plus about one group of fixed
-    // overhead (pipeline fill, epilogue); a slab element costs 8 bytes of traffic against 2114 bytes per tile-group
-    const double slab = s > 1 ? static_cast<double>(units) * ntok * 128 * 8 / (128.0 * 256 * 0.516) / static_cast<double>(grid) : 0.0;
-    const double cost = static_cast<double>(rounds) * (per + 1.0) + slab;
+    // in units of "one group of four blocks of one tile": a unit costs its groups plus about four groups of fixed
+    // overhead (pipeline fill and drain, epilogue: measured); a slab element costs 8 bytes of traffic against 16.9 KB
+    // per tile-group, weighted twice (the exchange is latency-bound, not bandwidth-bound)
+    const double slab = s > 1 ? 2.0 * static_cast<double>(units) * ntok * 128 * 8 / (128.0 * 256 * 0.516) / static_cast<double>(grid) : 0.0;
+    const double cost = static_cast<double>(rounds) * (per + 4.0) + slab;
     if (cost < best_cost) { best_cost = cost; best = s; }
   }
   if (force_slices > 0) best = force_slices > groups ? groups : force_slices;

@@ -242,7 +242,7 @@ int nf4ll_read_status(const int32_t* status, void* stream);
  * sum to whichever of them finishes last), e.g. under a profiler that replays kernels one at a time.
  * flags bit 1: run a forward of at most 64 rows on the register-level weight-streaming kernel (default: up to
  * 16 rows); flags bit 2: run a forward of at most 64 rows on the swapped-operand tensor-core kernel (default:
- * 33 to 64 rows against weights of at least 2^26 elements). With bit 1 or 2, `splits` forces that kernel's
+ * 9 to 32 rows against weights of at least 2^24 elements, 33 to 64 rows against at least 2^26). With bit 1 or 2, `splits` forces that kernel's
  * number of slices of the contraction. Size the workspace of such calls with nf4ll_workspace_bytes_tuned. */
 void nf4ll_tune_override(int32_t bm_tiles, int32_t bn, int32_t splits, int32_t flags);
 
