@@ -44,7 +44,10 @@ N_WEIGHT_SETS, N_INPUT_SETS = 8, 4
 # measurement of this run); reported with that label
 NCU_DRAM_BYTES_PER_LAUNCH = 53.0e6
 CPU_BUDGET_S = 100.0
-ROOFLINE_EVERY = 9      # timed steps whose tensor-core launches are bracketed by events: every ninth (9 and the 8 weight sets are coprime)
+# timed steps whose tensor-core launches are bracketed by events: every 49th (49 and the 8 weight sets are coprime). Such a
+# step is issued from Python instead of replayed from its graph, which costs host time (0.5 ms here, 2 ms on a slow
+# host core): rare enough that the timed region stays GPU-bound wherever it runs
+ROOFLINE_EVERY = 49
 
 
 def block_flops(M):
@@ -437,7 +440,7 @@ def run_ours(args):
                 "vs_baseline": None, "dtype": "f16", "data": "synthetic",
                 "config": block_config(world),
                 "tokens_per_s": world * M * args.steps / (ms * 1e-3),
-                "launch": ("cuda graphs: one captured step per weight set, replayed; every ninth timed step "
+                "launch": ("cuda graphs: one captured step per weight set, replayed; every 49th timed step "
                            "of the value loop issued eagerly with event hooks") if not args.no_graphs
                 else "eager: every launch issued from python",
                 "grad_stream": not args.no_grad_stream,
