@@ -139,6 +139,27 @@ def test_config4_weight_stream_shapes(which):
         assert float(y.float().abs().max()) < 50.0
 
 
+@pytest.mark.parametrize("N,K", [(18944, 3584), (3584, 18944), (3584, 3584)])
+def test_short_batches_on_7b_shapes(N, K):
+    """Every batch size class of the default dispatch (streaming kernel, swapped-operand kernel with 16 / 32 / 64
+    token columns, 128-row tiles) at the Qwen2.5-7B shapes, whose rows are 56 and 296 quantisation blocks long
+    (14 and 74 groups of four): M in {1, 8, 9, 16, 24, 33, 64, 65} with LoRA, dropout and bias; y on sampled output
+    columns for every token, t in full."""
+    pr = make_problem(N, K, 65, seed=4500 + N % 89, lora=True, dropout=0.05, bias=True, device="cuda")
+    gen = torch.Generator().manual_seed(N * 3 + K)
+    cols = sorted(set([0, 1, 127, 128, N - 128, N - 1] + torch.randint(0, N, (58,), generator=gen).tolist()))
+    w_rows = oracle_rows(pr.layer, "w", pr.code2, cols)
+    d = to_device(pr)
+    for M in (1, 8, 9, 16, 24, 33, 64, 65):
+        ref = nf4_oracle.lora_linear_o1(w_rows, pr.x[:M], None, pr.bias[cols], pr.A16, pr.B16[cols], pr.scale, pr.mask[:M], pr.keep_scale)
+        y, t = linear.forward(d.w, d.x[:M].contiguous(), bias=d.bias, lora=d.lora, mask=d.mask[:M].contiguous(),
+                              keep_scale=d.keep_scale, want_t=True)
+        linear.check_status()
+        assert_close(f"M={M} y", y[:, cols], ref["y"])
+        assert_close(f"M={M} t", t, ref["t"])
+        assert torch.isfinite(y).all()
+
+
 # ----------------------------------------------------------------------------------------------
 # training shapes: configuration 3 (Qwen2.5-7B) and configuration 1 (Qwen2.5-1.5B MLP), M = 2048
 # ----------------------------------------------------------------------------------------------
