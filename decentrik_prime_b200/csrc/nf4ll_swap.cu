@@ -84,7 +84,8 @@ struct SwapCfg {
   static constexpr int kXG = kSwapAGrp;                            // groups of token tiles in flight (they come from L2)
   // coarse stages in flight: codes of four blocks (16 KB) + their absmax codes. An EVEN number: a team reads the
   // groups of one parity only, and must meet every phase of a stage's barrier (a parity wait cannot skip one)
-  static constexpr int kCSt = NTOK == 64 ? 4 : (NTOK == 32 ? 6 : 8);
+  // (a power of two, so that the stage and its phase are a mask and a shift of the running count)
+  static constexpr int kCSt = NTOK == 64 ? 4 : 8;
   static constexpr int kAbsOff = kSwapCodeBytes;                   // absmax codes of the stage: [128 rows][4 blocks] bytes
   static constexpr int kStageBytes = kSwapCodeBytes + 1024;        // kept a multiple of 1024 for the swizzled codes
   static constexpr int kDCols = 64 * kSwapIssuers;                 // accumulator columns reserved: 64 per issuing thread
@@ -401,13 +402,17 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
       // the odd ones: a team meets every phase of the barriers it waits on (a unit's last group may lack its second
       // half; the epilogue that follows orders everything of the unit before the team's next wait)
       const int half = team & 1;
-      for (int grp = 0; grp < ngrp_unit; ++grp) {
+      // first group of the unit with this team's parity; its running count split as 6 k6 + gb (gb = barrier pair, gb % 3 =
+      // slot of tensor memory), kept up to date by additions inside the loop
+      int grp = ((team >> 1) ^ cg) & 1;
+      int k6 = (cg + grp) / (2 * kSwapAGrp), gb = (cg + grp) - k6 * (2 * kSwapAGrp);
+      for (; grp < ngrp_unit; grp += 2, gb += 2) {
+        if (gb >= 2 * kSwapAGrp) { gb -= 2 * kSwapAGrp; ++k6; }
         const int gcount = cg + grp;                           // running count of the group
-        if ((gcount & 1) != (team >> 1)) continue;
         const int nb = (nblk - grp * 4 < 4) ? nblk - grp * 4 : 4;
         if (half * 2 >= nb) continue;
         const int hu = grp * 2 + half;                         // half group of the unit
-        const int c = gcount % kCSt, gs = gcount % kSwapAGrp;
+        const int c = gcount & (kCSt - 1), gs = gb >= kSwapAGrp ? gb - kSwapAGrp : gb;
         const int nb2 = (nb - half * 2 < 2) ? 1 : 2;           // blocks in this half group
         if (ok && !swap_wait(smem_u32(grp_full + c), (gcount / kCSt) & 1, ab, 0x0504)) ok = false;
         uint4 c0 = make_uint4(0, 0, 0, 0), c1 = c0, c2 = c0, c3 = c0;
@@ -430,15 +435,10 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
           mbar_arrive(smem_u32(grp_empty + c));
           if (nb <= 2) mbar_arrive(smem_u32(grp_empty + c));
         }
-        // the group's columns of tensor memory are free once the MMAs of three groups ago have completed
-        const bool lone = nb <= 2;                 // the unit's last group has this half group only
-        const int gb = gcount % (2 * kSwapAGrp);
-        if (ok && gcount >= kSwapAGrp &&
-            !swap_wait(smem_u32(a_empty + (gcount - kSwapAGrp) % (2 * kSwapAGrp)), ((gcount - kSwapAGrp) / (2 * kSwapAGrp)) & 1, ab, 0x0505)) ok = false;
+        // absmax = code2[qabs] * scale2 + offset2, rounded separately (the scale pair changes every 256 blocks)
+        uint32_t am2[2] = {0u, 0u};
         if (ok) {
-          // absmax = code2[qabs] * scale2 + offset2, rounded separately (the scale pair changes every 256 blocks)
           const int b0 = qrow + hu * 2;
-          uint32_t am2[2];
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
             const int si = (b0 + j) >> 8;
@@ -446,6 +446,16 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
             const __half2 a2 = __float2half2_rn(block_absmax(sCode2[(qa >> (8 * j)) & 0xffu], s2, o2));
             am2[j] = *reinterpret_cast<const uint32_t*>(&a2);
           }
+        }
+        // the group's columns of tensor memory are free once the MMAs of three groups ago have completed: that group's
+        // barrier pair is (gb + 3) mod 6, its phase k6 or k6 - 1
+        const bool lone = nb <= 2;                 // the unit's last group has this half group only
+        if (ok && gcount >= kSwapAGrp) {
+          const int pb = gb >= kSwapAGrp ? gb - kSwapAGrp : gb + kSwapAGrp;
+          const int pk = gb >= kSwapAGrp ? k6 : k6 - 1;
+          if (!swap_wait(smem_u32(a_empty + pb), pk & 1, ab, 0x0505)) ok = false;
+        }
+        if (ok) {
           // sixteen columns (32 weights) at a time: the thread holds its four words of codes and one batch of results
           uint32_t v[16];
           const uint32_t dst = tA + gs * 128 + half * 64;
@@ -455,16 +465,13 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
           tmem_st16(dst, v);
           swap_decode8(c1.x, lane_base, am2[0], v + 0);  swap_decode8(c1.y, lane_base, am2[0], v + 4);
           swap_decode8(c1.z, lane_base, am2[0], v + 8);  swap_decode8(c1.w, lane_base, am2[0], v + 12);
-          __syncwarp();
           tmem_st16(dst + 16, v);
           if (nb2 == 2) {
             swap_decode8(c2.x, lane_base, am2[1], v + 0);  swap_decode8(c2.y, lane_base, am2[1], v + 4);
             swap_decode8(c2.z, lane_base, am2[1], v + 8);  swap_decode8(c2.w, lane_base, am2[1], v + 12);
-            __syncwarp();
             tmem_st16(dst + 32, v);
             swap_decode8(c3.x, lane_base, am2[1], v + 0);  swap_decode8(c3.y, lane_base, am2[1], v + 4);
             swap_decode8(c3.z, lane_base, am2[1], v + 8);  swap_decode8(c3.w, lane_base, am2[1], v + 12);
-            __syncwarp();
             tmem_st16(dst + 48, v);
           }
           tmem_st_wait();
