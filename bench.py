@@ -234,6 +234,8 @@ def run_ours(args):
     bucket = blocks.GradBucket(N_WEIGHT_SETS * blocks.MlpBlock.grad_numel(HIDDEN, INTER), dev)
     layers = [blocks.MlpBlock(HIDDEN, INTER, seed=100 + i, device=dev, lora=True, bucket=bucket) for i in range(N_WEIGHT_SETS)]
     per_layer = blocks.MlpBlock.grad_numel(HIDDEN, INTER)
+    if args.no_coop:
+        h.nf4ll_tune_override(0, 0, 0, 1)
     if not args.no_grad_stream:
         # the dA/dB kernels of a backward run on a side stream beside the dX GEMMs (forked and joined inside the step)
         grad_stream = torch.cuda.Stream(dev)
@@ -781,6 +783,9 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip benchmark configurations 0, 2 and 3")
     ap.add_argument("--no-graphs", action="store_true", help="issue every step from Python instead of replaying CUDA graphs")
     ap.add_argument("--no-grad-stream", action="store_true", help="issue the LoRA gradient kernels on the step's own stream instead of a side stream")
+    ap.add_argument("--no-coop", action="store_true",
+                    help="keep split contractions off the cooperative reduction (tuning flag bit 0): for a profiler that "
+                         "replays kernels one at a time; the kernel choice is otherwise unchanged")
     ap.add_argument("--profile-leg", default="step", choices=("step", "stream"),
                     help="which leg cudaProfilerStart/Stop brackets (for `ncu --profile-from-start off`): the timed "
                          "steps, or the small-batch weight-stream measurements")
