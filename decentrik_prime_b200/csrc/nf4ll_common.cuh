@@ -176,6 +176,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// try_wait with a suspend-time hint (nanoseconds): the hardware parks the thread until the phase completes or the
+// time is up, so a long wait costs a handful of instructions instead of a polling loop's issue slots
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -188,8 +202,8 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Every wait on an mbarrier is bounded twice over: after kSpinLimit failed polls (each poll itself
-// suspends for a hardware-chosen interval) or after kWaitLimitNs of wall time, whichever comes first,
+// Every wait on an mbarrier is bounded twice over: after kSpinLimit failed polls (each poll parks the thread
+// for at most kParkNs) or after kWaitLimitNs of wall time, whichever comes first,
 // the waiter gives up, and the kernel reports it through the status word instead of hanging the GPU. `abort_flag` (shared memory) makes all other waiters of
 // the CTA give up quickly too.
 // The first polls use the non-blocking test_wait: try_wait costs a few hundred cycles even when the
@@ -198,6 +212,7 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr uint32_t kFastPolls = 32;
 constexpr uint64_t kWaitLimitNs = 1000000000ull;      // and never longer than one second of wall time
+constexpr uint32_t kParkNs = 20000;                    // one parked poll: at most 20 us, so an abort is seen quickly
 
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
@@ -211,11 +226,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   const uint64_t t0 = global_timer_ns();
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 63u) {
-      if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) break;     // a failed poll can itself take microseconds
-    }
+    if (mbar_try_wait_hint(bar, parity, kParkNs)) return true;
+    if (*abort_flag) return false;
+    if (global_timer_ns() - t0 > kWaitLimitNs) break;
   }
   *abort_flag = 1;
   return false;

@@ -105,8 +105,9 @@ __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
 }
 // a wait for the threads on the kernel's critical path: polls without the slow path's bookkeeping until the limit
 __device__ __forceinline__ bool swap_wait(uint32_t bar, uint32_t parity, const Abort& ab, int code) {
-  for (uint32_t i = 0; i < 4096u; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_test_wait(bar, parity)) return true;
+  for (uint32_t i = 0; i < 16u; ++i)
+    if (mbar_try_wait_hint(bar, parity, kParkNs)) return true;
   return wait_or_abort(bar, parity, ab, code);
 }
 
