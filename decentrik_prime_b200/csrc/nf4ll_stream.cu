@@ -95,6 +95,7 @@ nf4_stream_kernel(const StreamParams p) {
   __shared__ uint32_t s_lv[16];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
+  const float code2_mine = threadIdx.x < 256 ? p.code2[threadIdx.x] : 0.f;     // in flight while the table is built
   {
     constexpr float lv[16] = {NF4LL_LEVELS};
     if (threadIdx.x < 16) {
@@ -104,16 +105,18 @@ nf4_stream_kernel(const StreamParams p) {
       s_lv[threadIdx.x] = __half_as_ushort(__float2half_rn(v));
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < 256 * 32; idx += kStreamWarps * 32) {
-      const int v = idx >> 5;                       // byte value: even element in the high nibble
-      s_tbl[idx] = s_lv[v >> 4] | (s_lv[v & 15] << 16);
+    // four lanes' copies of an entry per 16-byte store
+    for (int idx = threadIdx.x; idx < 256 * 8; idx += kStreamWarps * 32) {
+      const int v = idx >> 3;                       // byte value: even element in the high nibble
+      const uint32_t e = s_lv[v >> 4] | (s_lv[v & 15] << 16);
+      reinterpret_cast<uint4*>(s_tbl)[idx] = make_uint4(e, e, e, e);
     }
   }
   // x, the weights and code2 may be read at once: what precedes this kernel on the stream is either the
   // rank-16 projection kernel, itself started only after all earlier work had finished, or the memset of the
   // counters, which orders this kernel after everything before it
   bool waited = false;
-  if (threadIdx.x < 256) s_code2[threadIdx.x] = p.code2[threadIdx.x];
+  if (threadIdx.x < 256) s_code2[threadIdx.x] = code2_mine;
   __syncthreads();
 
   const uint32_t table = smem_u32(s_tbl), lane_off = lane * 4;

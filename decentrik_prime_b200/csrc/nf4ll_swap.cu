@@ -249,9 +249,10 @@ nf4_swap_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
   __syncwarp();
   __syncthreads();
   tc_fence_after();
-  for (int idx = threadIdx.x; idx < 256 * 32; idx += kSwapThreads) {
-    const int v = idx >> 5;                          // byte value: even element in the high nibble
-    sTbl[idx] = sLv[v >> 4] | (sLv[v & 15] << 16);
+  for (int idx = threadIdx.x; idx < 256 * 8; idx += kSwapThreads) {     // four lanes' copies of an entry per 16-byte store
+    const int v = idx >> 3;                          // byte value: even element in the high nibble
+    const uint32_t e = sLv[v >> 4] | (sLv[v & 15] << 16);
+    reinterpret_cast<uint4*>(sTbl)[idx] = make_uint4(e, e, e, e);
   }
   __syncthreads();
   const uint32_t tmem_base = *tmem_slot;
