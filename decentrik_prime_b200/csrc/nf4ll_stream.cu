@@ -84,7 +84,7 @@ __device__ __forceinline__ void decode8(uint32_t w, uint32_t table, uint32_t lan
 
 // NT = number of 8-token tiles (M <= 8 NT).
 template <int NT>
-__global__ void __launch_bounds__(kStreamWarps * 32, NT == 1 ? 4 : (NT == 2 ? 3 : (NT == 4 ? 2 : 1)))
+__global__ void __launch_bounds__(kStreamWarps * 32, NT == 1 ? 3 : (NT == 2 ? 3 : (NT == 4 ? 2 : 1)))
 nf4_stream_kernel(const StreamParams p) {
   // Launched as a programmatic dependent of the kernel before it (the rank-16 projection T = x . A^T when
   // there is a LoRA branch, which also clears this launch's counters): the table build and the first unit's
