@@ -422,6 +422,7 @@ def run_ours(args):
         if world == 1:
             extra["config0_q_proj"] = config0_numbers(dev)
             extra["config2_stack1.5b"] = stack_numbers("stack1.5b", dev, world, rank, args)
+            extra["config2_decoder_stack"] = decoder_stack_numbers(dev, args)
 
     # ---------------- max over ranks
     if world > 1:
@@ -665,6 +666,76 @@ def run_stack(args):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def decoder_stack_numbers(dev, args):
+    """Benchmark configuration 2 as a real model step: 28 Qwen2.5-1.5B decoder layers (RMSNorm + residual kernels
+    of this library, Q|K|V / O / gate|up / down through the fused NF4 + LoRA linear, rotary embedding and causal
+    grouped-query attention through PyTorch's kernels), the same 4 packed sequences, forward and the hand-written
+    backward called as one autograd node. 28 distinct weight sets; issued eagerly."""
+    import torch
+    from decentrik_prime_b200 import linear, stack
+    hidden, inter, kv, layers, heads = 1536, 8960, 256, 28, 12
+    lens, M = stack.pack_lengths(4, 64, 512, seed=2)
+    ns = stack.NormedStack(hidden, inter, kv, layers, dev, seed=7, n_heads=heads)
+    for t in ns.lora_masters():
+        t.requires_grad_(True)
+    gen = torch.Generator().manual_seed(100)
+    x = torch.randn(M, hidden, generator=gen).to(dev)
+    dres = (torch.randn(M, hidden, generator=gen) * 0.1).to(dev)
+    gdev = torch.Generator(device=dev).manual_seed(5)
+    mask_sets = [{n: (torch.rand(M, hidden, device=dev, generator=gdev) >= P_DROP).to(torch.uint8) for n in ("q_proj", "v_proj")}
+                 for _ in range(4)]
+    masks = [mask_sets[i % 4] for i in range(layers)]
+    keep_scale = 1.0 / float(torch.tensor(1.0 - P_DROP, dtype=torch.float32))
+
+    def step():
+        out = ns.apply(x, masks, keep_scale, lens)
+        out.backward(dres)
+        for t in ns.lora_masters():
+            t.grad = None
+
+    steps, warmup = min(args.steps, 10), 3
+    side = torch.cuda.Stream(dev)
+    graph = None
+    with torch.cuda.stream(side):
+        for _ in range(warmup):
+            step()
+        torch.cuda.synchronize()
+        linear.check_status(dev)
+        if not args.no_graphs:
+            # forward and backward (the autograd engine included) of the whole stack as one CUDA graph
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    step()
+                torch.cuda.synchronize()
+                graph.replay()
+                torch.cuda.synchronize()
+            except Exception as exc:
+                graph = None
+                torch.cuda.synchronize()
+                print(f"[bench] CUDA graph capture of the decoder stack failed ({type(exc).__name__}: {exc}); running eagerly", file=sys.stderr)
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(side)
+        for _ in range(steps):
+            if graph is not None:
+                graph.replay()
+            else:
+                step()
+        t1.record(side)
+        torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1)
+    linear.check_status(dev)
+    res = {"workload": "decoder stack 1.5b: norms + projections + rotary/causal attention, one autograd node",
+           "rows": M, "layers": layers, "heads": heads, "kv_heads": 2, "lengths": lens,
+           "tokens_per_s": M * steps / (ms * 1e-3), "projection_tflops": float(ns.flops(M)) * steps / (ms * 1e-3) / 1e12,
+           "ms_per_step": ms / steps, "steps": steps, "warmup": warmup,
+           "launch": ("cuda graph of the whole step, replayed" if graph is not None else "eager") +
+                     "; attention through torch.nn.functional.scaled_dot_product_attention per sequence"}
+    del ns, graph
+    torch.cuda.empty_cache()
+    return res
 
 
 def weight_stream_numbers(dev, peak_gbs, only=None, rows=(1, 8, 64, 16, 32)):

@@ -254,22 +254,81 @@ class ProjectionStack:
         return acts[-1], d
 
 
+class PackedAttention:
+    """Rotary embedding + causal grouped-query attention over packed varlen rows, forward and backward, through
+    PyTorch's own kernels (scaled_dot_product_attention per sequence, autograd for the backward). Attention is not
+    on this library's path (the reference has kernels of its own for it, solution/k_rope.py, k_attn.py); this is
+    the glue that makes the layer runner a real Qwen2 decoder layer. Rotary embedding as in Qwen2: the two halves
+    of a head rotate against each other, positions restart at every sequence."""
+
+    def __init__(self, n_heads, n_kv_heads, head_dim, theta=1.0e6):
+        self.nh, self.nkv, self.hd, self.theta = n_heads, n_kv_heads, head_dim, theta
+        self._tables = {}
+
+    def _cos_sin(self, seq_lens, device):
+        key = (tuple(seq_lens), str(device))
+        if key not in self._tables:
+            pos = torch.cat([torch.arange(n, dtype=torch.float32) for n in seq_lens]).to(device)
+            inv = self.theta ** (-torch.arange(0, self.hd, 2, dtype=torch.float32, device=device) / self.hd)
+            ang = pos[:, None] * inv[None, :]
+            emb = torch.cat([ang, ang], dim=1)
+            self._tables = {key: (emb.cos()[:, None, :], emb.sin()[:, None, :])}
+        return self._tables[key]
+
+    @staticmethod
+    def _rotate(x, cos, sin):
+        half = x.shape[-1] // 2
+        rot = torch.cat([-x[..., half:], x[..., :half]], dim=-1)
+        return (x.float() * cos + rot.float() * sin).to(x.dtype)
+
+    def forward(self, qkv, seq_lens):
+        """qkv fp16 [M, (nh + 2 nkv) hd] -> (a fp16 [M, nh hd], state for backward)."""
+        import torch.nn.functional as F
+        H, KV = self.nh * self.hd, self.nkv * self.hd
+        if sum(seq_lens) != qkv.shape[0]:
+            raise ValueError(f"sequence lengths {seq_lens} do not add up to {qkv.shape[0]} rows")
+        leaf = qkv.detach().requires_grad_(True)
+        cos, sin = self._cos_sin(seq_lens, qkv.device)
+        with torch.enable_grad():
+            q = self._rotate(leaf[:, :H].view(-1, self.nh, self.hd), cos, sin)
+            k = self._rotate(leaf[:, H:H + KV].view(-1, self.nkv, self.hd), cos, sin)
+            v = leaf[:, H + KV:].view(-1, self.nkv, self.hd)
+            outs, at = [], 0
+            for n in seq_lens:
+                sl = slice(at, at + n)
+                o = F.scaled_dot_product_attention(q[sl].transpose(0, 1)[None], k[sl].transpose(0, 1)[None],
+                                                   v[sl].transpose(0, 1)[None], is_causal=True, enable_gqa=self.nkv != self.nh)
+                outs.append(o[0].transpose(0, 1).reshape(n, H))
+                at += n
+            a = torch.cat(outs, dim=0)
+        return a.detach(), (leaf, a)
+
+    @staticmethod
+    def backward(state, da):
+        leaf, a = state
+        (dqkv,) = torch.autograd.grad(a, leaf, da)
+        return dqkv
+
+
 class NormedDecoderLayer:
     """The projections of one decoder layer between REAL fused residual + RMSNorm kernels, driven the way the
     reference drives its layer loop (solution/fast_qwen.py:1017-1123 forward, 1232-1384 backward): an fp32 residual
     stream, each norm adding the fp16 output of the GEMM before it (`delta`), norm 1 producing y16 AND the rank-16
     LoRA products of q and v, one stacked launch for Q|K|V forward and ONE for its backward (the LoRA input
     gradients are folded into norm 1's backward, as in solution/k_norm.py:64-71), one for gate|up each way.
-    Attention itself (RoPE, softmax) stays the stand-in of DecoderLayerProjections: it is not on this path.
+    Attention itself (RoPE, softmax) is not on this path: with `attention` (a PackedAttention) and the batch's
+    sequence lengths it runs through PyTorch's kernels, otherwise the stand-in of DecoderLayerProjections is used.
 
         forward(x32, delta16)  -> (x32', delta16')     with x_next = x32' + delta16'
         backward(dres32, d16)  -> (dres32', d16')      gradients w.r.t. x_next in, w.r.t. this layer's input out
     """
 
-    def __init__(self, base: DecoderLayerProjections, eps=1e-6, norm_weights=None, seed=0):
+    def __init__(self, base: DecoderLayerProjections, eps=1e-6, norm_weights=None, seed=0, attention=None):
         from . import k_norm
         self.k_norm = k_norm
-        self.base, self.eps = base, eps
+        self.base, self.eps, self.attention = base, eps, attention
+        if attention is not None and (attention.nh * attention.hd != base.hidden or attention.nkv * attention.hd != base.kv):
+            raise ValueError("attention head layout does not match the projection widths")
         dev = base.layer.flat.device
         if norm_weights is None:
             gen = torch.Generator().manual_seed(seed * 16 + 15)
@@ -282,7 +341,7 @@ class NormedDecoderLayer:
             raise ValueError("projection widths must be multiples of 128")
         self._saved = None
 
-    def forward(self, x32, delta16, masks, keep_scale):
+    def forward(self, x32, delta16, masks, keep_scale, seq_lens=None):
         b, kn, P = self.base, self.k_norm, self.base.proj
         M, H, KV = x32.shape[0], b.hidden, b.kv
         dev = x32.device
@@ -296,16 +355,20 @@ class NormedDecoderLayer:
         qkv = torch.empty(M, H + 2 * KV, dtype=torch.float16, device=dev)
         linear.forward_multi(b.w_qkv, y1, [(H, P["q_proj"].lora, mq, keep_scale, tq), (KV, None, None, 1.0),
                                            (KV, P["v_proj"].lora, mv, keep_scale, tv)], bias=b.bias_qkv, out=qkv)
-        a = qkv[:, :H].clone()                                 # attention stand-in (see DecoderLayerProjections)
-        a[:, :KV] += qkv[:, H:H + KV]
-        a[:, KV:2 * KV] += qkv[:, H + KV:]
+        att = None
+        if self.attention is not None and seq_lens is not None:
+            a, att = self.attention.forward(qkv, seq_lens)
+        else:
+            a = qkv[:, :H].clone()                             # attention stand-in (see DecoderLayerProjections)
+            a[:, :KV] += qkv[:, H:H + KV]
+            a[:, KV:2 * KV] += qkv[:, H + KV:]
         o, _ = linear.forward(P["o_proj"].w, a)
         y2 = torch.empty(M, H, dtype=torch.float16, device=dev)
         x2, rstd2 = torch.empty(M, H, **f32), torch.empty(M, **f32)
         kn.rms_forward(x1, self.w_post, y2, rstd2, self.eps, delta=o, xout=x2)
         g, u, h, _, _ = linear.forward_gate_up(b.w_gu, y2)
         dn, _ = linear.forward(P["down_proj"].w, h)
-        self._saved = (x1, rstd1, y1, tq, tv, mq, mv, keep_scale, a, o, rstd2, g, u, h)
+        self._saved = (x1, rstd1, y1, tq, tv, mq, mv, keep_scale, att, o, rstd2, g, u, h)
         return x2, dn
 
     def backward(self, dres, d16, need_dx=True):
@@ -313,7 +376,7 @@ class NormedDecoderLayer:
         autocast copy does). Returns the same pair for this layer's input, or (None, None) when need_dx is False
         (the first layer: only its LoRA gradients are wanted, solution/fast_qwen.py:1363-1364)."""
         b, kn, P = self.base, self.k_norm, self.base.proj
-        x1, rstd1, y1, tq, tv, mq, mv, ks, a, o, rstd2, g, u, h = self._saved
+        x1, rstd1, y1, tq, tv, mq, mv, ks, att, o, rstd2, g, u, h = self._saved
         H, KV, M = b.hidden, b.kv, dres.shape[0]
         dev = dres.device
         if b._grad_slice is not None:
@@ -326,10 +389,13 @@ class NormedDecoderLayer:
         # norm 2's input is x1 + o: recomputed inside the kernel from the two saved tensors
         kn.rms_backward(dy2, 1.0, x1, self.w_post, rstd2, dres2, dres=dres, out16=do16, delta=o)
         da, _ = linear.backward_dx(P["o_proj"].w, do16)
-        dqkv = torch.empty(M, H + 2 * KV, dtype=torch.float16, device=dev)
-        dqkv[:, :H] = da
-        dqkv[:, H:H + KV] = da[:, :KV]
-        dqkv[:, H + KV:] = da[:, KV:2 * KV]
+        if att is not None:
+            dqkv = PackedAttention.backward(att, da)
+        else:
+            dqkv = torch.empty(M, H + 2 * KV, dtype=torch.float16, device=dev)
+            dqkv[:, :H] = da
+            dqkv[:, H:H + KV] = da[:, :KV]
+            dqkv[:, H + KV:] = da[:, KV:2 * KV]
         pq, pv = P["q_proj"], P["v_proj"]
         uq = linear.lora_u(dqkv[:, :H], pq.B16t, pq.scale)
         uv = linear.lora_u(dqkv[:, H + KV:], pv.B16t, pv.scale)
@@ -350,24 +416,65 @@ class NormedStack:
     """n_layers NormedDecoderLayers over one LoRA gradient bucket: `run_step` is the whole forward and the
     hand-written backward of the decoder stack (embedding, attention proper and the LM head are outside the path)."""
 
-    def __init__(self, hidden, inter, kv, n_layers, device, seed=0, eps=1e-6, layer_parts=None):
+    def __init__(self, hidden, inter, kv, n_layers, device, seed=0, eps=1e-6, layer_parts=None, n_heads=None, rope_theta=1.0e6):
+        """`n_heads`: run real rotary + causal grouped-query attention (PackedAttention; head_dim = hidden / n_heads,
+        kv / head_dim key-value heads) between the projections when `run_step` / `apply` get the sequence lengths."""
         self.stack = ProjectionStack(hidden, inter, kv, n_layers, device, seed=seed, layer_parts=layer_parts)
         norms = [None] * self.stack.n_layers if layer_parts is None else [p.get("norm") for p in layer_parts]
-        self.layers = [NormedDecoderLayer(l, eps if nw is None else nw[2], nw, seed=seed * 1000 + i)
+        self.attention = None
+        if n_heads is not None:
+            hd = hidden // n_heads
+            self.attention = PackedAttention(n_heads, kv // hd, hd, rope_theta)
+        self.layers = [NormedDecoderLayer(l, eps if nw is None else nw[2], nw, seed=seed * 1000 + i, attention=self.attention)
                        for i, (l, nw) in enumerate(zip(self.stack.layers, norms))]
         self.bucket = self.stack.bucket
 
     def flops(self, M):
         return self.stack.flops(M)
 
-    def run_step(self, x32, dres, masks_per_layer, keep_scale):
-        """x32 fp32 [M, hidden]: the embedded tokens; dres fp32: the gradient of the loss w.r.t. the stack's output.
-        Returns (output fp32 = residual stream after the last layer, gradient w.r.t. layer 1's input or None)."""
+    def forward(self, x32, masks_per_layer, keep_scale, seq_lens=None):
         x, delta = x32, None
         for layer, masks in zip(self.layers, masks_per_layer):
-            x, delta = layer.forward(x, delta, masks, keep_scale)
-        out = x + delta.float()
+            x, delta = layer.forward(x, delta, masks, keep_scale, seq_lens)
+        return x + delta.float()
+
+    def backward(self, dres, need_input_grad=False):
         d, d16 = dres, dres.half()
         for i in reversed(range(len(self.layers))):
-            d, d16 = self.layers[i].backward(d, d16, need_dx=i > 0)
-        return out, d
+            d, d16 = self.layers[i].backward(d, d16, need_dx=i > 0 or need_input_grad)
+        return d
+
+    def run_step(self, x32, dres, masks_per_layer, keep_scale, seq_lens=None):
+        """x32 fp32 [M, hidden]: the embedded tokens; dres fp32: the gradient of the loss w.r.t. the stack's output.
+        Returns (output fp32 = residual stream after the last layer, gradient w.r.t. layer 1's input or None)."""
+        out = self.forward(x32, masks_per_layer, keep_scale, seq_lens)
+        return out, self.backward(dres)
+
+    def lora_masters(self):
+        """The fp32 LoRA masters of every distinct layer, in the order `apply` returns their gradients."""
+        return [t for l in self.stack._distinct for n in ("q_proj", "v_proj") for t in (l.proj[n].A, l.proj[n].B)]
+
+    def apply(self, x32, masks_per_layer, keep_scale, seq_lens=None):
+        """The whole decoder stack as ONE autograd node (the counterpart of the reference's fused runner,
+        solution/fast_qwen.py:1527-1548): the output carries a grad_fn whose backward is the hand-written one and
+        hands PyTorch the gradients of the LoRA masters (`lora_masters()`, which must be leaf tensors that require
+        grad for an optimiser to see them) and, if x32 requires grad, of the input."""
+        if self.stack._shared:
+            raise ValueError("a stack that reuses weight sets cannot keep the activations of a whole forward pass")
+        return _StackStep.apply(self, x32, masks_per_layer, keep_scale, seq_lens, *self.lora_masters())
+
+
+class _StackStep(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ns, x32, masks_per_layer, keep_scale, seq_lens, *masters):
+        for l in ns.stack._distinct:
+            l.refresh16()                                      # fp16 shadows follow the masters (fast_qwen.py:686-692)
+        ctx.ns, ctx.need_dx = ns, x32.requires_grad
+        return ns.forward(x32.detach(), masks_per_layer, keep_scale, seq_lens)
+
+    @staticmethod
+    def backward(ctx, dout):
+        ns = ctx.ns
+        dx = ns.backward(dout.contiguous().float(), need_input_grad=ctx.need_dx)
+        grads = [g for l in ns.stack._distinct for n in ("q_proj", "v_proj") for g in (l.proj[n].dA, l.proj[n].dB)]
+        return (None, dx if ctx.need_dx else None, None, None, None, *grads)

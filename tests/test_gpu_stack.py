@@ -229,3 +229,92 @@ def test_normed_stack_matches_oracle():
     assert rel <= 3e-3, (err, rel)
     err, rel = nf4_oracle.errors(got16, want16.float())
     assert rel <= 3e-3, (err, rel)
+
+
+def _reference_decoder_stack(ns, x32, masks, ks, seq_lens, theta):
+    """The same decoder stack in plain PyTorch (fp64 on the CPU, autograd for the backward): dequantised weights
+    from the oracle, the fp16 LoRA shadows as leaves, explicit rotary embedding and causal softmax attention with
+    grouped key-value heads. Returns (output, leaves) with leaves[i][name] = (A, B)."""
+    dt = torch.float64
+    att = ns.attention
+    nh, nkv, hd = att.nh, att.nkv, att.hd
+    pos = torch.cat([torch.arange(n, dtype=dt) for n in seq_lens])
+    inv = theta ** (-torch.arange(0, hd, 2, dtype=dt) / hd)
+    ang = pos[:, None] * inv[None, :]
+    cos, sin = torch.cat([ang, ang], 1).cos()[:, None, :], torch.cat([ang, ang], 1).sin()[:, None, :]
+
+    def rot(t):
+        half = hd // 2
+        return t * cos + torch.cat([-t[..., half:], t[..., :half]], -1) * sin
+
+    def rms(t, w, eps):
+        return t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps) * w
+
+    x, leaves = x32.to(dt), []
+    for nl, ms in zip(ns.layers, masks):
+        b, P = nl.base, nl.base.proj
+        H, KV = b.hidden, b.kv
+        W = {n: nf4_oracle.dequant_weight(b.layer, n, b.code2).to(dt) for n in k_nf4.LAYER_WEIGHTS}
+        lv = {n: (P[n].A16.cpu().to(dt).requires_grad_(True), P[n].B16.cpu().to(dt).requires_grad_(True)) for n in ("q_proj", "v_proj")}
+        leaves.append(lv)
+        y1 = rms(x, nl.w_in.cpu().to(dt), nl.eps)
+        bias = b.bias_qkv.cpu().to(dt)
+        outs = []
+        for n, sl in (("q_proj", slice(0, H)), ("k_proj", slice(H, H + KV)), ("v_proj", slice(H + KV, H + 2 * KV))):
+            o = y1 @ W[n].t() + bias[sl]
+            if n in lv:
+                A, B = lv[n]
+                o = o + P[n].scale * ((y1 * ms[n].to(dt) * ks) @ A.t()) @ B.t()
+            outs.append(o)
+        q, k, v = rot(outs[0].view(-1, nh, hd)), rot(outs[1].view(-1, nkv, hd)), outs[2].view(-1, nkv, hd)
+        rows, at = [], 0
+        for n in seq_lens:
+            qs, ks_, vs = q[at:at + n], k[at:at + n].repeat_interleave(nh // nkv, 1), v[at:at + n].repeat_interleave(nh // nkv, 1)
+            sc = torch.einsum("ihd,jhd->hij", qs, ks_) / hd ** 0.5
+            sc = sc.masked_fill(torch.triu(torch.ones(n, n, dtype=torch.bool), 1), float("-inf"))
+            rows.append(torch.einsum("hij,jhd->ihd", sc.softmax(-1), vs).reshape(n, H))
+            at += n
+        x = x + torch.cat(rows) @ W["o_proj"].t()
+        y2 = rms(x, nl.w_post.cpu().to(dt), nl.eps)
+        h = F.silu(y2 @ W["gate_proj"].t()) * (y2 @ W["up_proj"].t())
+        x = x + h @ W["down_proj"].t()
+    return x, leaves
+
+
+def test_decoder_stack_with_attention_is_one_autograd_node():
+    """NormedStack with real rotary + causal grouped-query attention between the projections, called as ONE autograd
+    node: output, LoRA gradients (through the masters' .grad) and the input gradient against a plain PyTorch fp64
+    model of the same two layers. Tolerances cover the path's fp16 rounding points (activations between kernels)."""
+    dev = torch.device("cuda")
+    H, I, KV, NH = 256, 512, 128, 4
+    seq_lens = [70, 130]
+    M = sum(seq_lens)
+    ns = stack.NormedStack(H, I, KV, 2, dev, seed=11, n_heads=NH, rope_theta=1.0e4)
+    gen = torch.Generator().manual_seed(5)
+    x32 = torch.randn(M, H, generator=gen)
+    dres = torch.randn(M, H, generator=gen) * 0.5
+    ks = 1.0 / float(torch.tensor(0.95, dtype=torch.float32))
+    masks = [{n: (torch.rand(M, H, generator=gen) >= 0.05).to(torch.uint8) for n in ("q_proj", "v_proj")} for _ in range(2)]
+    masters = ns.lora_masters()
+    for t in masters:
+        t.requires_grad_(True)
+    xin = x32.to(dev).requires_grad_(True)
+    out = ns.apply(xin, [{n: m.to(dev) for n, m in ms.items()} for ms in masks], ks, seq_lens)
+    assert out.grad_fn is not None
+    (out * dres.to(dev)).sum().backward()
+    linear.check_status()
+
+    xr = x32.to(torch.float64).requires_grad_(True)
+    ref, leaves = _reference_decoder_stack(ns, xr, masks, ks, seq_lens, 1.0e4)
+    (ref * dres.to(torch.float64)).sum().backward()
+    err, rel = nf4_oracle.errors(out.detach(), ref.detach())
+    assert rel <= 3e-3, (err, rel)
+    err, rel = nf4_oracle.errors(xin.grad, xr.grad)
+    assert rel <= 1e-2, (err, rel)
+    it = iter(masters)
+    for i in range(2):
+        for n in ("q_proj", "v_proj"):
+            for ref_leaf in leaves[i][n]:
+                got = next(it).grad
+                err, rel = nf4_oracle.errors(got, ref_leaf.grad)
+                assert rel <= 1e-2, (i, n, err, rel)
