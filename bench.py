@@ -48,6 +48,7 @@ CPU_BUDGET_S = 100.0
 # step is issued from Python instead of replayed from its graph, which costs host time (0.5 ms here, 2 ms on a slow
 # host core): rare enough that the timed region stays GPU-bound wherever it runs
 ROOFLINE_EVERY = 49
+ROOFLINE_FIRST = 7     # the first instrumented step: not the first of the timed region
 
 
 def block_flops(M):
@@ -262,7 +263,7 @@ def run_ours(args):
 
     def step(i, inp, masks, out, timed=False):
         blk = layers[i % N_WEIGHT_SETS]
-        hooked = timed and i % ROOFLINE_EVERY == 0
+        hooked = (timed and args.steps > ROOFLINE_FIRST and i % ROOFLINE_EVERY == ROOFLINE_FIRST) or timed == "hooked"
         if timed:
             # every ROOFLINE_EVERY-th timed step has its tensor-core launches bracketed by events: the
             # event records cost ~3 % of a step, so the other steps run without them
@@ -295,6 +296,9 @@ def run_ours(args):
                     with torch.cuda.graph(g, stream=side):
                         run_block(blk, inp, masks, out)
                     graphs[(i, inp.data_ptr())] = g
+                # a graph's first launch uploads it to the device: done here, outside every timed region
+                for g in graphs.values():
+                    g.replay()
             torch.cuda.synchronize()
         except Exception as exc:      # capture is an optimisation, never a requirement
             graphs.clear()
@@ -339,6 +343,14 @@ def run_ours(args):
         torch.cuda.profiler.stop()
     ms = t0.elapsed_time(t1)
     linear.check_status(dev)
+    events_where = "inside the timed region"
+    if not ev_pairs:
+        # too few timed steps to hide an eagerly issued one behind queued work: the tensor-core launches are timed in
+        # two extra steps right after the region instead (same inputs, same weights)
+        for i in range(2):
+            step(i, dev_in[i % N_INPUT_SETS], mask_sets[i % N_INPUT_SETS], dev_out[i % N_INPUT_SETS], timed="hooked")
+        barrier()
+        events_where = "two extra steps right after the timed region (fewer than 8 timed steps)"
     for blk in layers:
         blk._ev_sink = None
     kern_ms = sum(a.elapsed_time(b) for a, b, _ in ev_pairs)
@@ -461,6 +473,7 @@ def run_ours(args):
                              "algorithmic_bytes_per_launch": (6 * INTER * HIDDEN * 0.516113
                                                               + 2 * M * (6 * HIDDEN + 7 * INTER)) / 5,
                              "kernel": "nf4_gemm_kernel / nf4_gemm_pair_kernel (forward and backward-dX launches)",
+                             "events": events_where,
                              "launches_timed": n_kern, "avg_launch_us": kern_ms * 1e3 / max(n_kern, 1)},
                 "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "ms_per_step": e2e_ms / args.steps, "copies_per_step": 2,
