@@ -253,6 +253,9 @@ def run_ours(args):
 
     ev_pairs = []      # (start, stop, flops) of tensor-core kernels inside the timed region
     graphs = {}        # (weight set, id of the input buffer) -> CUDAGraph: whole steps captured once, replayed afterwards
+    hooked_graphs = {}     # the same key -> (CUDAGraph with event-record nodes around the tensor-core launches, its event pairs)
+    hooked_graphs_made = [False]
+    kept_graphs = []
     launches_per_step = [None]
 
     def run_block(blk, inp, masks, out):
@@ -272,15 +275,24 @@ def run_ours(args):
         if sync is not None:
             sync.wait_slot(slot)          # this layer's gradients of 8 steps ago have been exchanged
         g = None if hooked else graphs.get((slot, inp.data_ptr()))
-        if g is not None:
+        hg = hooked_graphs.pop((slot, inp.data_ptr()), None) if hooked and timed is True else None
+        if hg is not None:
+            # an instrumented copy of the step's graph: the event records are nodes of the graph, so the step costs the
+            # host what any replay costs; each copy is replayed once, its events then hold this step's launch times
+            hg[0].replay()
+            ev_pairs.extend(hg[1])
+            kept_graphs.append(hg[0])
+        elif g is not None:
             g.replay()                    # the same launches, issued by the GPU front end instead of Python
+        elif hooked and timed is True and hooked_graphs_made[0]:
+            graphs[(slot, inp.data_ptr())].replay()      # all instrumented copies are used up: an ordinary step
         else:
             run_block(blk, inp, masks, out)
         if sync is not None:
             # the exchange runs on a side stream under the next step's compute
             sync.launch(slot, bucket.flat[slot * per_layer:(slot + 1) * per_layer])
 
-    def capture_steps(inputs, outs):
+    def capture_steps(inputs, outs, instrumented=False):
         """One CUDA graph per (weight set, input buffer) pair the loops below use: the step's launches are
         fixed, so the ~0.5 ms of Python per step need not race the GPU. Falls back to eager on failure."""
         if args.no_graphs:
@@ -296,12 +308,25 @@ def run_ours(args):
                     with torch.cuda.graph(g, stream=side):
                         run_block(blk, inp, masks, out)
                     graphs[(i, inp.data_ptr())] = g
+                    if instrumented:
+                        mine = []
+                        _hook_block(blk, mine, M)
+                        hg = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(hg, stream=side):
+                            run_block(blk, inp, masks, out)
+                        blk._ev_sink = None
+                        hooked_graphs[(i, inp.data_ptr())] = (hg, mine)
+                hooked_graphs_made[0] = bool(hooked_graphs)
                 # a graph's first launch uploads it to the device: done here, outside every timed region
                 for g in graphs.values():
                     g.replay()
+                for hg, _ in hooked_graphs.values():
+                    hg.replay()
             torch.cuda.synchronize()
         except Exception as exc:      # capture is an optimisation, never a requirement
             graphs.clear()
+            hooked_graphs.clear()
+            hooked_graphs_made[0] = False
             torch.cuda.synchronize()
             print(f"[bench] CUDA graph capture failed ({type(exc).__name__}: {exc}); running eagerly", file=sys.stderr)
 
@@ -325,8 +350,8 @@ def run_ours(args):
             launches_per_step[0] = int(h.nf4ll_launch_count() - n0) + 1
     barrier()
     linear.check_status(dev)
-    capture_steps(dev_in, dev_out)
-    _fill_event_pool(6 * args.steps + 6)
+    _fill_event_pool(6 * N_WEIGHT_SETS + 6 * (args.steps // ROOFLINE_EVERY + 4) + 12)
+    capture_steps(dev_in, dev_out, instrumented=True)
     torch.cuda.synchronize()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -455,8 +480,9 @@ def run_ours(args):
                 "vs_baseline": None, "dtype": "f16", "data": "synthetic",
                 "config": block_config(world),
                 "tokens_per_s": world * M * args.steps / (ms * 1e-3),
-                "launch": ("cuda graphs: one captured step per weight set, replayed; every 49th timed step "
-                           "of the value loop issued eagerly with event hooks") if not args.no_graphs
+                "launch": ("cuda graphs: one captured step per weight set, replayed; every 49th timed step of the value "
+                           "loop (eight at most) replays a copy of its graph with event-record nodes around the "
+                           "tensor-core launches") if not args.no_graphs
                 else "eager: every launch issued from python",
                 "grad_stream": not args.no_grad_stream,
                 "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",

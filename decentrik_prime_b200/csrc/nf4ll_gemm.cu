@@ -1039,6 +1039,16 @@ static thread_local Tune g_tune;
 static thread_local uint32_t g_expire_polls = 0;      // nf4ll_test_expire_wait: one-shot
 static thread_local cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;
 
+// Record a measurement event on `stream`; inside a stream capture the record becomes a node of the graph that is
+// executed (and timed) at every replay
+static int record_event(cudaEvent_t ev, cudaStream_t stream) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  NF4LL_CUDA(cudaStreamIsCapturing(stream, &st));
+  if (st == cudaStreamCaptureStatusActive) NF4LL_CUDA(cudaEventRecordWithFlags(ev, stream, cudaEventRecordExternal));
+  else NF4LL_CUDA(cudaEventRecord(ev, stream));
+  return NF4LL_OK;
+}
+
 static int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
 
 static Plan make_plan(int mode, int64_t M, int64_t NO, int64_t KC, int r, int sms, const Tune& tune) {
@@ -1357,7 +1367,7 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
   cudaEvent_t ev0 = g_ev_start, ev1 = g_ev_stop;
   g_ev_start = g_ev_stop = nullptr;
   if (kind != kTiles) {
-    if (ev0) NF4LL_CUDA(cudaEventRecord(ev0, stream));
+    if (ev0) { if (int rce = record_event(ev0, stream)) return rce; }
     const float* t32 = lora ? p.lora_left : nullptr;
     const void* lb = lora ? lora->B : nullptr;
     const float ls = lora ? lora->scale : 0.f;
@@ -1366,7 +1376,7 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
                                                force_slices, stream)
                        : swap_forward_launch(W, act, ldact, bias, t32, lb, ls, M, out, ldo, counters, lora != nullptr,
                                              force_slices, status, stream);
-    if (rc == NF4LL_OK && ev1) NF4LL_CUDA(cudaEventRecord(ev1, stream));
+    if (rc == NF4LL_OK && ev1) { if (int rce = record_event(ev1, stream)) return rce; }
     return rc;
   }
   if (pl.splits > 1) {
@@ -1384,12 +1394,12 @@ static int run_gemm(int mode, const nf4ll_mat* W, const void* act, int64_t ldact
   }
   CUtensorMap nib_map;
   if (int rc = make_nib_map(&nib_map, W->nib, W->N, W->K, mode, pl.pair ? 128 : pl.bn)) return rc;
-  if (ev0) NF4LL_CUDA(cudaEventRecord(ev0, stream));
+  if (ev0) { if (int rce = record_event(ev0, stream)) return rce; }
   const int rc = pl.pair ? launch_pair(mode, pl.bm_tiles, map, nib_map, out_map, p, pl.tiles_o, pl.tiles_m, pl.splits,
                                        pl.launch_splits, stream)
                  : (mode == kFwd ? launch<kFwd>(map, nib_map, out_map, p, pl, stream)
                                  : launch<kBwd>(map, nib_map, out_map, p, pl, stream));
-  if (rc == NF4LL_OK && ev1) NF4LL_CUDA(cudaEventRecord(ev1, stream));
+  if (rc == NF4LL_OK && ev1) { if (int rce = record_event(ev1, stream)) return rce; }
   return rc;
 }
 
@@ -1460,9 +1470,9 @@ static int run_gate_up(const nf4ll_mat* W, const void* x, int64_t ldx, const nf4
   if (int rc = make_tile_map(&mh, h, M, I, ldh, false)) return rc;
   cudaEvent_t ev0 = g_ev_start, ev1 = g_ev_stop;
   g_ev_start = g_ev_stop = nullptr;
-  if (ev0) NF4LL_CUDA(cudaEventRecord(ev0, stream));
+  if (ev0) { if (int rce = record_event(ev0, stream)) return rce; }
   const int rc = launch_cfg<kFwd, 2, 256>(map, nib_map, mg, mu, mh, p, pl, stream);
-  if (rc == NF4LL_OK && ev1) NF4LL_CUDA(cudaEventRecord(ev1, stream));
+  if (rc == NF4LL_OK && ev1) { if (int rce = record_event(ev1, stream)) return rce; }
   return rc;
 }
 

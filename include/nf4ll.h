@@ -249,7 +249,8 @@ void nf4ll_tune_override(int32_t bm_tiles, int32_t bn, int32_t splits, int32_t f
 /* Measurement hook; no counterpart in the reference. The calling thread's NEXT nf4ll_forward /
  * nf4ll_backward_dx / nf4ll_forward_gate_up records the CUDA events `start` / `stop` (cudaEvent_t as
  * void*) right before / after the kernel that computes its product on the call's stream, leaving the
- * small rank-16 prologue kernel outside the pair. One-shot: the pair is forgotten after that call. */
+ * small rank-16 prologue kernel outside the pair. One-shot: the pair is forgotten after that call. On a stream
+ * that is being captured the records become nodes of the graph (recorded, and timeable, at every replay). */
 void nf4ll_kernel_events(void* start, void* stop);
 
 /* Measurement hook; no counterpart in the reference. Number of kernels the calling thread has launched
